@@ -1,0 +1,795 @@
+// C-ABI implementation (include/fr_b200.h): model memory, tensor upload + repacking, the phase
+// table, decode launches, recurrent-state access.  No PyTorch types, no exceptions across the ABI.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/fr_b200.h"
+#include "internal.h"
+
+using namespace frb;
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const std::string &msg) {
+  g_err = msg;
+  return code;
+}
+#define CU(call)                                                                                   \
+  do {                                                                                             \
+    cudaError_t e_ = (call);                                                                       \
+    if (e_ != cudaSuccess)                                                                         \
+      return fail(FR_B200_E_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_) + " (" __FILE__ ":" + \
+                                      std::to_string(__LINE__) + ")");                             \
+  } while (0)
+
+struct MatrixSlot {       // where a projection matrix lives inside the packed weight blob
+  size_t tile_off = 0;    // byte offset of its first row block
+  size_t item_stride = 0; // bytes between consecutive row blocks
+  size_t rscale_off = 0;  // element offset into the row-scale array (int8)
+  size_t rscale_stride = 0;
+  int K = 0, N = 0;
+  bool set = false;
+};
+
+struct VecSlot {
+  size_t off = 0;  // float offset into the vector blob
+  int n = 0;
+  bool set = false;
+};
+
+}  // namespace
+
+struct fr_b200_model {
+  fr_b200_config cfg;
+  int C, F, V, Vpad, L, H, fmt;
+  bool v5 = false, gate = false;
+  int device = 0;
+  // device memory
+  uint8_t *d_weights = nullptr;  size_t weights_bytes = 0;
+  __half *d_rscale = nullptr;    size_t rscale_n = 0;
+  float *d_vecs = nullptr;       size_t vecs_n = 0;
+  __half *d_emb = nullptr;
+  uint8_t *d_state = nullptr;    size_t state_stride = 0, layer_stride = 0;
+  float *d_x = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;
+  float *d_v5buf = nullptr;      // k5, v5, r5, g5, o5
+  float *d_out = nullptr;        // [B][Vpad] logits, then [B] argmax ints, then status int
+  unsigned *d_sync = nullptr;
+  LayerDev *d_layers = nullptr;
+  PhaseDev *d_phases = nullptr;
+  uint8_t *h_out = nullptr;      // pinned mirror of d_out
+  int32_t *d_hist = nullptr;     size_t hist_n = 0;   // sampled ids of decode_greedy
+  // scratch for uploads
+  void *d_scratch[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t scratch_bytes[4] = {0, 0, 0, 0};
+  // bookkeeping
+  std::map<std::string, MatrixSlot> mats;
+  std::map<std::string, VecSlot> vecs;
+  std::vector<char> emb_rows_set;
+  bool emb_set = false;
+  std::vector<PhaseDev> phases;
+  bool finalized = false;
+  int n_stages = 0, n_stages8 = 0, grid = 0;
+  size_t smem1 = 0, smem8 = 0;
+  long long launches = 0;
+  long long stream_bytes = 0;
+
+  int32_t *out_argmax() const { return reinterpret_cast<int32_t *>(d_out + (size_t)cfg.max_batch * Vpad); }
+  int *out_status() const { return reinterpret_cast<int *>(out_argmax() + cfg.max_batch); }
+  size_t out_bytes() const { return ((size_t)cfg.max_batch * Vpad + cfg.max_batch + 1) * 4; }
+};
+
+namespace {
+
+int ensure_scratch(fr_b200_model *m, int idx, size_t bytes) {
+  if (m->scratch_bytes[idx] >= bytes) return 0;
+  if (m->d_scratch[idx]) cudaFree(m->d_scratch[idx]);
+  m->d_scratch[idx] = nullptr;
+  m->scratch_bytes[idx] = 0;
+  CU(cudaMalloc(&m->d_scratch[idx], bytes));
+  m->scratch_bytes[idx] = bytes;
+  return 0;
+}
+
+void free_scratch(fr_b200_model *m) {
+  for (int i = 0; i < 4; ++i) {
+    if (m->d_scratch[i]) cudaFree(m->d_scratch[i]);
+    m->d_scratch[i] = nullptr;
+    m->scratch_bytes[i] = 0;
+  }
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Lay out every matrix / vector of the model.  Per layer the weight blob holds the phases in the
+// order the kernel streams them.
+void plan(fr_b200_model *m) {
+  const int C = m->C, F = m->F, fmt = m->fmt;
+  size_t woff = 0, roff = 0, voff = 0;
+  auto mat = [&](const std::string &name, int K, int N, size_t tile_off, size_t item_stride, size_t rs_off,
+                 size_t rs_stride) {
+    MatrixSlot s;
+    s.K = K; s.N = N; s.tile_off = tile_off; s.item_stride = item_stride; s.rscale_off = rs_off; s.rscale_stride = rs_stride;
+    m->mats[name] = s;
+  };
+  auto vec = [&](const std::string &name, int n) {
+    VecSlot s; s.off = voff; s.n = n; voff += (size_t)(n + 3) / 4 * 4;
+    m->vecs[name] = s;
+  };
+  const size_t rbC = rowblock_bytes(fmt, C), rbF = rowblock_bytes(fmt, F);
+  const int nbC = C / ROWS, nbF = F / ROWS;
+  m->phases.clear();
+  int pi = 0;
+  auto phase = [&](int kind, int layer, int K, int n_items, int n_sub, size_t w_off, size_t rs_off) {
+    PhaseDev p;
+    memset(&p, 0, sizeof(p));
+    p.w = reinterpret_cast<const uint8_t *>(w_off);        // patched to a pointer in finalize
+    p.rscale = reinterpret_cast<const __half *>(rs_off);   // element offset, patched in finalize
+    p.kind = kind; p.layer = layer; p.K = K; p.n_items = n_items; p.n_sub = n_sub;
+    p.rot = (pi * 37) % 148;
+    ++pi;
+    m->phases.push_back(p);
+  };
+  for (int l = 0; l < m->L; ++l) {
+    const std::string b = "blocks." + std::to_string(l) + ".", a = b + "att.", f = b + "ffn.";
+    vec(b + "ln1.weight", C); vec(b + "ln1.bias", C); vec(b + "ln2.weight", C); vec(b + "ln2.bias", C);
+    vec(a + "time_mix_k", C); vec(a + "time_mix_v", C); vec(a + "time_mix_r", C);
+    if (m->gate) vec(a + "time_mix_g", C);
+    vec(f + "time_mix_k", C); vec(f + "time_mix_r", C);
+    const int nd = m->cfg.version == FR_B200_V5_0 ? m->H : C;
+    vec(a + "time_decay", nd); vec(a + "time_first", nd);
+    if (m->v5) { vec(a + "ln_x.weight", C); vec(a + "ln_x.bias", C); }
+    if (!m->v5) {
+      // K,V,R of the same 16 channels sit next to each other: item = [K tile][V tile][R tile]
+      mat(a + "key.weight", C, C, woff, 3 * rbC, roff, 3 * ROWS);
+      mat(a + "value.weight", C, C, woff + rbC, 3 * rbC, roff + ROWS, 3 * ROWS);
+      mat(a + "receptance.weight", C, C, woff + 2 * rbC, 3 * rbC, roff + 2 * ROWS, 3 * ROWS);
+      phase(PH_ATT_KVR, l, C, nbC, 3, woff, roff);
+      woff += (size_t)nbC * 3 * rbC; roff += (size_t)nbC * 3 * ROWS;
+    } else {
+      const int ncls = m->gate ? 4 : 3;
+      const char *names[4] = {"key.weight", "value.weight", "receptance.weight", "gate.weight"};
+      phase(PH5_KVRG, l, C, nbC * ncls, 1, woff, roff);
+      for (int c = 0; c < ncls; ++c) {
+        mat(a + names[c], C, C, woff, rbC, roff, ROWS);
+        woff += (size_t)nbC * rbC; roff += (size_t)nbC * ROWS;
+      }
+      phase(PH5_WKV, l, 0, 0, 0, 0, 0);
+    }
+    mat(a + "output.weight", C, C, woff, rbC, roff, ROWS);
+    phase(PH_ATT_O, l, C, nbC, 1, woff, roff);
+    woff += (size_t)nbC * rbC; roff += (size_t)nbC * ROWS;
+    // ffn key rows then ffn receptance rows, both read C inputs
+    mat(f + "key.weight", C, F, woff, rbC, roff, ROWS);
+    mat(f + "receptance.weight", C, C, woff + (size_t)nbF * rbC, rbC, roff + (size_t)nbF * ROWS, ROWS);
+    phase(PH_FFN_KR, l, C, nbF + nbC, 1, woff, roff);
+    m->phases.back().split[0] = nbF;
+    woff += (size_t)(nbF + nbC) * rbC; roff += (size_t)(nbF + nbC) * ROWS;
+    mat(f + "value.weight", F, C, woff, rbF, roff, ROWS);
+    phase(PH_FFN_V, l, F, nbC, 1, woff, roff);
+    woff += (size_t)nbC * rbF; roff += (size_t)nbC * ROWS;
+  }
+  vec("ln_out.weight", C); vec("ln_out.bias", C);
+  const int nbV = m->Vpad / ROWS;
+  mat("head.weight", C, m->V, woff, rbC, roff, ROWS);
+  phase(PH_HEAD, 0, C, nbV, 1, woff, roff);
+  woff += (size_t)nbV * rbC; roff += (size_t)nbV * ROWS;
+  m->weights_bytes = woff; m->rscale_n = roff; m->vecs_n = voff;
+  m->stream_bytes = (long long)woff + (fmt == FMT_INT8 ? (long long)roff * 2 : 0);
+}
+
+bool is_host_ptr(const void *p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return true; }
+  return a.type == cudaMemoryTypeUnregistered || a.type == cudaMemoryTypeHost;
+}
+
+int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int dtype) {
+  const size_t n = (size_t)s.K * s.N;
+  const size_t in_bytes = n * (dtype == FR_B200_T_F16 ? 2 : 4);
+  int rc;
+  if ((rc = ensure_scratch(m, 0, in_bytes))) return rc;
+  CU(cudaMemcpy(m->d_scratch[0], data, in_bytes, cudaMemcpyDefault));
+  uint8_t *dst = m->d_weights + s.tile_off;
+  if (m->fmt == FMT_FP16) {
+    const __half *src = reinterpret_cast<const __half *>(m->d_scratch[0]);
+    if (dtype == FR_B200_T_F32) {
+      if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
+      CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]), n, 0));
+      src = reinterpret_cast<const __half *>(m->d_scratch[1]);
+    }
+    CU(launch_pack(FMT_FP16, src, nullptr, s.K, s.N, dst, s.item_stride, nullptr, 0, 0));
+  } else {
+    const float *w32 = reinterpret_cast<const float *>(m->d_scratch[0]);
+    if (dtype == FR_B200_T_F16) {
+      if ((rc = ensure_scratch(m, 1, n * 4))) return rc;
+      CU(launch_f16_to_f32(reinterpret_cast<const __half *>(m->d_scratch[0]), reinterpret_cast<float *>(m->d_scratch[1]), n, 0));
+      w32 = reinterpret_cast<const float *>(m->d_scratch[1]);
+    }
+    if (m->fmt == FMT_INT8) {
+      if ((rc = ensure_scratch(m, 2, n))) return rc;
+      if ((rc = ensure_scratch(m, 3, (size_t)s.N * 2))) return rc;
+      CU(launch_quant_int8(w32, s.K, s.N, reinterpret_cast<int8_t *>(m->d_scratch[2]), reinterpret_cast<__half *>(m->d_scratch[3]), 0));
+      CU(launch_pack(FMT_INT8, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
+                     s.item_stride, m->d_rscale + s.rscale_off, s.rscale_stride, 0));
+    } else {
+      if ((rc = ensure_scratch(m, 2, n / 2))) return rc;
+      if ((rc = ensure_scratch(m, 3, (size_t)s.N * (s.K / 32) * 2))) return rc;
+      CU(launch_quant_int4(w32, s.K, s.N, reinterpret_cast<uint8_t *>(m->d_scratch[2]), reinterpret_cast<__half *>(m->d_scratch[3]), 0));
+      CU(launch_pack(FMT_INT4, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
+                     s.item_stride, nullptr, 0, 0));
+    }
+  }
+  CU(cudaDeviceSynchronize());
+  return 0;
+}
+
+// small tensors: bring to host, convert to fp32
+int to_host_f32(const void *data, int dtype, size_t n, std::vector<float> &out) {
+  out.resize(n);
+  if (dtype == FR_B200_T_F32) {
+    CU(cudaMemcpy(out.data(), data, n * 4, cudaMemcpyDefault));
+  } else {
+    std::vector<__half> tmp(n);
+    CU(cudaMemcpy(tmp.data(), data, n * 2, cudaMemcpyDefault));
+    for (size_t i = 0; i < n; ++i) out[i] = __half2float(tmp[i]);
+  }
+  return 0;
+}
+
+int check_status(fr_b200_model *m, int st) {
+  if (st == 0) return 0;
+  // a bounded wait gave up: the barrier words may be inconsistent, clear them for the next launch
+  cudaMemset(m->d_sync, 0, 8);
+  cudaMemset(m->out_status(), 0, 4);
+  return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(st) + ")");
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *fr_b200_strerror(int status) {
+  switch (status) {
+    case FR_B200_OK: return "ok";
+    case FR_B200_E_ARG: return "bad argument";
+    case FR_B200_E_UNSUPPORTED: return "unsupported model shape, version or batch";
+    case FR_B200_E_CUDA: return "CUDA runtime error";
+    case FR_B200_E_STATE: return "call order violation";
+    case FR_B200_E_MISSING: return "model tensor missing at finalize";
+    case FR_B200_E_TIMEOUT: return "device-side wait timed out";
+    case FR_B200_E_NOMEM: return "out of memory";
+    default: return "unknown status";
+  }
+}
+const char *fr_b200_last_error(void) { return g_err.c_str(); }
+
+int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
+  if (!cfg || !out) return fail(FR_B200_E_ARG, "null argument");
+  *out = nullptr;
+  const int v = cfg->version;
+  if (v != FR_B200_V4 && v != FR_B200_V5_0 && v != FR_B200_V5_1 && v != FR_B200_V5_2)
+    return fail(FR_B200_E_UNSUPPORTED, "version must be 4, 50, 51 or 52");
+  if (cfg->n_layer <= 0 || cfg->vocab <= 0) return fail(FR_B200_E_ARG, "n_layer and vocab must be positive");
+  if (cfg->n_embd <= 0 || cfg->n_embd % 64 || cfg->n_ffn <= 0 || cfg->n_ffn % 64)
+    return fail(FR_B200_E_UNSUPPORTED, "n_embd and n_ffn must be positive multiples of 64");
+  if (cfg->weight_format < 0 || cfg->weight_format > 2) return fail(FR_B200_E_ARG, "bad weight_format");
+  if (cfg->max_batch < 1 || cfg->max_batch > MAX_B) return fail(FR_B200_E_UNSUPPORTED, "max_batch must be 1..8");
+  if (v != FR_B200_V4 && (cfg->n_head <= 0 || cfg->n_embd != cfg->n_head * 64))
+    return fail(FR_B200_E_UNSUPPORTED, "RWKV-5 needs n_embd == 64 * n_head");
+  int ndev = 0;
+  CU(cudaGetDeviceCount(&ndev));
+  if (cfg->device < 0 || cfg->device >= ndev) return fail(FR_B200_E_ARG, "no such CUDA device");
+  CU(cudaSetDevice(cfg->device));
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, cfg->device));
+  if (prop.major != 10) return fail(FR_B200_E_UNSUPPORTED, "this library is built for sm_100a (B200) only");
+
+  fr_b200_model *m = new (std::nothrow) fr_b200_model();
+  if (!m) return fail(FR_B200_E_NOMEM, "host allocation failed");
+  m->cfg = *cfg;
+  m->C = cfg->n_embd; m->F = cfg->n_ffn; m->V = cfg->vocab; m->L = cfg->n_layer; m->H = cfg->n_head;
+  m->Vpad = (cfg->vocab + ROWS - 1) / ROWS * ROWS;
+  m->fmt = cfg->weight_format;
+  m->v5 = v != FR_B200_V4;
+  m->gate = v == FR_B200_V5_1 || v == FR_B200_V5_2;
+  m->device = cfg->device;
+  if ((m->C + prop.multiProcessorCount - 1) / prop.multiProcessorCount > 128) {
+    delete m;
+    return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the shift-state stash");
+  }
+  plan(m);
+  m->layer_stride = m->v5 ? v5_layer_bytes(m->C, m->H, cfg->act_fp16) : v4_layer_bytes(m->C, cfg->act_fp16);
+  m->state_stride = align256(m->layer_stride * m->L);
+  const int B = cfg->max_batch;
+  auto alloc = [&](void **p, size_t bytes) -> int {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 256);
+    if (e != cudaSuccess) return fail(e == cudaErrorMemoryAllocation ? FR_B200_E_NOMEM : FR_B200_E_CUDA,
+                                      std::string("cudaMalloc: ") + cudaGetErrorString(e));
+    return 0;
+  };
+  int rc = 0;
+  if (!rc) rc = alloc((void **)&m->d_weights, m->weights_bytes);
+  if (!rc) rc = alloc((void **)&m->d_rscale, m->rscale_n * 2);
+  if (!rc) rc = alloc((void **)&m->d_vecs, m->vecs_n * 4);
+  if (!rc) rc = alloc((void **)&m->d_emb, (size_t)m->V * m->C * 2);
+  if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
+  if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * 4);
+  if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * 4);
+  if (!rc) rc = alloc((void **)&m->d_kk, (size_t)B * m->F * 4);
+  if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * 4);
+  if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * 4);
+  if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
+  if (!rc) rc = alloc((void **)&m->d_sync, 8);
+  if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
+  if (!rc) rc = alloc((void **)&m->d_phases, sizeof(PhaseDev) * m->phases.size());
+  if (!rc && cudaMallocHost((void **)&m->h_out, m->out_bytes()) != cudaSuccess) rc = fail(FR_B200_E_NOMEM, "cudaMallocHost failed");
+  if (rc) { fr_b200_destroy(m); return rc; }
+  cudaMemset(m->d_weights, 0, m->weights_bytes);
+  cudaMemset(m->d_rscale, 0, m->rscale_n * 2 + 2);
+  cudaMemset(m->d_out, 0, m->out_bytes());
+  cudaMemset(m->d_sync, 0, 8);
+  m->emb_rows_set.assign(m->V, 0);
+  *out = m;
+  return FR_B200_OK;
+}
+
+void fr_b200_destroy(fr_b200_model *m) {
+  if (!m) return;
+  cudaSetDevice(m->device);
+  free_scratch(m);
+  void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_rwkv, m->d_kk, m->d_rr,
+                  m->d_v5buf, m->d_out, m->d_sync, m->d_layers, m->d_phases};
+  for (void *p : ptrs)
+    if (p) cudaFree(p);
+  if (m->h_out) cudaFreeHost(m->h_out);
+  if (m->d_hist) cudaFree(m->d_hist);
+  delete m;
+}
+
+int fr_b200_set_tensor(fr_b200_model *m, const char *name, const void *data, int dtype, const int64_t *shape, int ndim) {
+  if (!m || !name || !data || (ndim > 0 && !shape)) return fail(FR_B200_E_ARG, "null argument");
+  if (dtype != FR_B200_T_F16 && dtype != FR_B200_T_F32) return fail(FR_B200_E_ARG, "dtype must be f16 or f32");
+  if (m->finalized) return fail(FR_B200_E_STATE, "model already finalized");
+  CU(cudaSetDevice(m->device));
+  size_t numel = 1;
+  for (int i = 0; i < ndim; ++i) {
+    if (shape[i] <= 0) return fail(FR_B200_E_ARG, "non-positive dimension");
+    numel *= (size_t)shape[i];
+  }
+  const std::string nm(name);
+  if (nm == "emb.weight" || nm.rfind("emb.", 0) == 0 || nm.rfind("embd_", 0) == 0) {
+    size_t row0 = 0, rows = 0;
+    if (nm == "emb.weight") {
+      if (ndim != 2 || shape[0] != m->V || shape[1] != m->C) return fail(FR_B200_E_ARG, "emb.weight must be [vocab, n_embd]");
+      rows = m->V;
+    } else {
+      const char *num = nm.c_str() + (nm[3] == '.' ? 4 : 5);
+      char *end = nullptr;
+      long r = strtol(num, &end, 10);
+      if (end == num || *end || r < 0 || r >= m->V) return fail(FR_B200_E_ARG, "bad embedding row name " + nm);
+      if (numel != (size_t)m->C) return fail(FR_B200_E_ARG, "embedding row must have n_embd elements");
+      row0 = (size_t)r; rows = 1;
+    }
+    __half *dst = m->d_emb + row0 * m->C;
+    if (dtype == FR_B200_T_F16) {
+      CU(cudaMemcpy(dst, data, rows * m->C * 2, cudaMemcpyDefault));
+    } else {
+      int rc = ensure_scratch(m, 0, rows * m->C * 4);
+      if (rc) return rc;
+      CU(cudaMemcpy(m->d_scratch[0], data, rows * m->C * 4, cudaMemcpyDefault));
+      CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), dst, rows * m->C, 0));
+      CU(cudaDeviceSynchronize());
+    }
+    for (size_t r = row0; r < row0 + rows; ++r) m->emb_rows_set[r] = 1;
+    return FR_B200_OK;
+  }
+  auto mi = m->mats.find(nm);
+  if (mi != m->mats.end()) {
+    MatrixSlot &s = mi->second;
+    if (ndim != 2 || shape[0] != s.K || shape[1] != s.N)
+      return fail(FR_B200_E_ARG, nm + ": expected [" + std::to_string(s.K) + ", " + std::to_string(s.N) + "] (in, out)");
+    int rc = upload_matrix(m, s, data, dtype);
+    if (rc) return rc;
+    s.set = true;
+    return FR_B200_OK;
+  }
+  auto vi = m->vecs.find(nm);
+  if (vi != m->vecs.end()) {
+    VecSlot &s = vi->second;
+    if (numel != (size_t)s.n) return fail(FR_B200_E_ARG, nm + ": expected " + std::to_string(s.n) + " elements");
+    std::vector<float> h;
+    int rc = to_host_f32(data, dtype, numel, h);
+    if (rc) return rc;
+    CU(cudaMemcpy(m->d_vecs + s.off, h.data(), numel * 4, cudaMemcpyHostToDevice));
+    s.set = true;
+    return FR_B200_OK;
+  }
+  return fail(FR_B200_E_ARG, "unknown tensor name " + nm);
+}
+
+int fr_b200_finalize(fr_b200_model *m) {
+  if (!m) return fail(FR_B200_E_ARG, "null model");
+  if (m->finalized) return FR_B200_OK;
+  CU(cudaSetDevice(m->device));
+  for (auto &kv : m->mats) if (!kv.second.set) return fail(FR_B200_E_MISSING, "missing tensor " + kv.first);
+  for (auto &kv : m->vecs) if (!kv.second.set) return fail(FR_B200_E_MISSING, "missing tensor " + kv.first);
+  for (int r = 0; r < m->V; ++r) if (!m->emb_rows_set[r]) return fail(FR_B200_E_MISSING, "missing embedding row " + std::to_string(r));
+  free_scratch(m);
+  // layer table
+  std::vector<LayerDev> layers(m->L);
+  auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
+  for (int l = 0; l < m->L; ++l) {
+    const std::string b = "blocks." + std::to_string(l) + ".", a = b + "att.", f = b + "ffn.";
+    LayerDev &d = layers[l];
+    memset(&d, 0, sizeof(d));
+    d.ln1_w = vp(b + "ln1.weight"); d.ln1_b = vp(b + "ln1.bias"); d.ln2_w = vp(b + "ln2.weight"); d.ln2_b = vp(b + "ln2.bias");
+    d.att_mix[0] = vp(a + "time_mix_k"); d.att_mix[1] = vp(a + "time_mix_v"); d.att_mix[2] = vp(a + "time_mix_r");
+    d.att_mix[3] = m->gate ? vp(a + "time_mix_g") : nullptr;
+    d.ffn_mix[0] = vp(f + "time_mix_k"); d.ffn_mix[1] = vp(f + "time_mix_r");
+    d.decay = vp(a + "time_decay"); d.first = vp(a + "time_first");
+    if (m->v5) { d.lnx_w = vp(a + "ln_x.weight"); d.lnx_b = vp(a + "ln_x.bias"); }
+  }
+  CU(cudaMemcpy(m->d_layers, layers.data(), sizeof(LayerDev) * m->L, cudaMemcpyHostToDevice));
+  // kernel geometry: as many ring stages as shared memory allows (capped), one CTA per SM
+  int optin = 0;
+  CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
+  int want = 8;
+  if (const char *e = getenv("FR_B200_STAGES")) want = atoi(e);
+  if (want < 2) want = 2;
+  if (want > MAX_STAGES) want = MAX_STAGES;
+  const int ver = m->v5 ? 5 : 4;
+  auto fit = [&](int NB) -> int {
+    for (int s = want; s >= 2; --s)
+      if (decode_smem_bytes(m->fmt, NB, m->C, m->F, ver, s) <= (size_t)optin) return s;
+    return 0;
+  };
+  const int s1 = fit(1), s8 = m->cfg.max_batch > 1 ? fit(8) : s1;
+  if (s1 == 0 || s8 == 0) return fail(FR_B200_E_UNSUPPORTED, "model too wide for shared memory at this batch size");
+  m->n_stages = s1;
+  m->n_stages8 = s8;
+  m->smem1 = decode_smem_bytes(m->fmt, 1, m->C, m->F, ver, s1);
+  m->smem8 = decode_smem_bytes(m->fmt, 8, m->C, m->F, ver, s8);
+  int g1 = 0, g8 = 0;
+  CU(decode_max_grid(m->fmt, 1, m->smem1, m->device, &g1));
+  CU(decode_max_grid(m->fmt, 8, m->smem8, m->device, &g8));
+  if (g1 == 0 || g8 == 0) return fail(FR_B200_E_UNSUPPORTED, "decode kernel does not fit on an SM");
+  m->grid = g1;
+  // stash capacity: ceil(C / grid) channels per CTA
+  if ((m->C + m->grid - 1) / m->grid > 128) return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the shift-state stash");
+  // phase table with real pointers; rotate item ownership from phase to phase
+  std::vector<PhaseDev> ph = m->phases;
+  for (size_t i = 0; i < ph.size(); ++i) {
+    ph[i].w = m->d_weights + reinterpret_cast<size_t>(ph[i].w);
+    ph[i].rscale = m->fmt == FMT_INT8 ? m->d_rscale + reinterpret_cast<size_t>(ph[i].rscale) : nullptr;
+    ph[i].rot = (int)((i * 37) % (size_t)m->grid);
+  }
+  CU(cudaMemcpy(m->d_phases, ph.data(), sizeof(PhaseDev) * ph.size(), cudaMemcpyHostToDevice));
+  m->finalized = true;
+  return fr_b200_state_reset(m, -1);
+}
+
+static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t *ids_dev, int batch, cudaStream_t st,
+                       bool want_argmax) {
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.version = m->cfg.version == FR_B200_V4 ? 4 : m->cfg.version;
+  p.L = m->L; p.C = m->C; p.F = m->F; p.V = m->V; p.Vpad = m->Vpad; p.H = m->H;
+  p.fmt = m->fmt; p.act_fp16 = m->cfg.act_fp16; p.rescale_every = m->cfg.act_fp16 ? 6 : 0;
+  p.B = batch;
+  p.n_phases = (int)m->phases.size();
+  const int NB = batch == 1 ? 1 : 8;
+  size_t smem = NB == 1 ? m->smem1 : m->smem8;
+  // stages that fit for this NB
+  p.n_stages = NB == 1 ? m->n_stages : m->n_stages8;
+  if (ids_host)
+    for (int b = 0; b < batch; ++b) {
+      if (ids_host[b] < 0 || ids_host[b] >= m->V) return fail(FR_B200_E_ARG, "token id out of range");
+      p.ids_val[b] = ids_host[b];
+    }
+  p.ids_dev = ids_dev;
+  p.emb = m->d_emb; p.layers = m->d_layers; p.phases = m->d_phases;
+  p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
+  p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
+  p.x = m->d_x; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
+  const size_t bc = (size_t)m->cfg.max_batch * m->C;
+  p.k5 = m->d_v5buf; p.v5 = p.k5 + bc; p.r5 = p.v5 + bc; p.g5 = p.r5 + bc; p.o5 = p.g5 + bc;
+  p.state = m->d_state; p.state_stride = m->state_stride; p.layer_stride = m->layer_stride;
+  p.sync = m->d_sync; p.status = m->out_status();
+  CU(launch_decode(p, NB, m->grid, smem, st));
+  m->launches++;
+  if (want_argmax) {
+    CU(launch_argmax(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), st));
+    m->launches++;
+  }
+  return 0;
+}
+
+int fr_b200_decode(fr_b200_model *m, const int32_t *ids, int batch, float *logits, int32_t *argmax, void *stream) {
+  if (!m || !ids) return fail(FR_B200_E_ARG, "null argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  if (batch < 1 || batch > m->cfg.max_batch) return fail(FR_B200_E_ARG, "batch must be 1..max_batch");
+  CU(cudaSetDevice(m->device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = decode_impl(m, ids, nullptr, batch, st, argmax != nullptr);
+  if (rc) return rc;
+  const bool lh = logits && is_host_ptr(logits), ah = argmax && is_host_ptr(argmax);
+  if (logits && !lh)
+    CU(cudaMemcpy2DAsync(logits, (size_t)m->V * 4, m->d_out, (size_t)m->Vpad * 4, (size_t)m->V * 4, batch, cudaMemcpyDeviceToDevice, st));
+  if (argmax && !ah) CU(cudaMemcpyAsync(argmax, m->out_argmax(), (size_t)batch * 4, cudaMemcpyDeviceToDevice, st));
+  if (lh || ah) {
+    // one D2H of [logits rows used][argmax][status] into the pinned mirror, then hand out
+    const size_t tail_off = (size_t)m->cfg.max_batch * m->Vpad * 4;
+    if (lh) CU(cudaMemcpyAsync(m->h_out, m->d_out, (size_t)batch * m->Vpad * 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaMemcpyAsync(m->h_out + tail_off, reinterpret_cast<uint8_t *>(m->d_out) + tail_off, (size_t)(m->cfg.max_batch + 1) * 4,
+                       cudaMemcpyDeviceToHost, st));
+    CU(cudaStreamSynchronize(st));
+    const int status = *reinterpret_cast<int *>(m->h_out + tail_off + (size_t)m->cfg.max_batch * 4);
+    if ((rc = check_status(m, status))) return rc;
+    if (lh)
+      for (int b = 0; b < batch; ++b)
+        memcpy(logits + (size_t)b * m->V, m->h_out + (size_t)b * m->Vpad * 4, (size_t)m->V * 4);
+    if (ah) memcpy(argmax, m->h_out + tail_off, (size_t)batch * 4);
+  }
+  return FR_B200_OK;
+}
+
+int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch, int n_tokens, int32_t *out_ids,
+                          void *stream) {
+  if (!m || !first_ids || !out_ids) return fail(FR_B200_E_ARG, "null argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  if (batch < 1 || batch > m->cfg.max_batch || n_tokens < 1) return fail(FR_B200_E_ARG, "bad batch or n_tokens");
+  CU(cudaSetDevice(m->device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t need = (size_t)n_tokens * batch;
+  if (m->hist_n < need) {
+    CU(cudaStreamSynchronize(st));
+    if (m->d_hist) cudaFree(m->d_hist);
+    m->d_hist = nullptr; m->hist_n = 0;
+    CU(cudaMalloc((void **)&m->d_hist, need * 4));
+    m->hist_n = need;
+  }
+  for (int t = 0; t < n_tokens; ++t) {
+    int rc = decode_impl(m, t == 0 ? first_ids : nullptr, t == 0 ? nullptr : m->d_hist + (size_t)(t - 1) * batch, batch, st, false);
+    if (rc) return rc;
+    CU(launch_argmax(m->d_out, batch, m->V, m->Vpad, m->d_hist + (size_t)t * batch, st));
+    m->launches++;
+  }
+  if (is_host_ptr(out_ids)) {
+    CU(cudaMemcpyAsync(out_ids, m->d_hist, need * 4, cudaMemcpyDeviceToHost, st));
+    int status = 0;
+    CU(cudaMemcpyAsync(&status, m->out_status(), 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaStreamSynchronize(st));
+    return check_status(m, status);
+  }
+  CU(cudaMemcpyAsync(out_ids, m->d_hist, need * 4, cudaMemcpyDeviceToDevice, st));
+  return FR_B200_OK;
+}
+
+int fr_b200_logits_device(fr_b200_model *m, float **ptr) {
+  if (!m || !ptr) return fail(FR_B200_E_ARG, "null argument");
+  *ptr = m->d_out;
+  return FR_B200_OK;
+}
+int fr_b200_vocab_padded(const fr_b200_model *m) { return m ? m->Vpad : FR_B200_E_ARG; }
+
+int fr_b200_run_seq(fr_b200_model *m, int slot, const int32_t *ids, int n, float *last_logits, void *stream) {
+  if (!m || !ids || n < 1) return fail(FR_B200_E_ARG, "bad argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  if (slot != 0) return fail(FR_B200_E_UNSUPPORTED, "run_seq uses stream slot 0");
+  for (int i = 0; i < n; ++i) {
+    int rc = fr_b200_decode(m, ids + i, 1, i == n - 1 ? last_logits : nullptr, nullptr, stream);
+    if (rc) return rc;
+  }
+  if (!last_logits) {
+    CU(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+    int status = 0;
+    CU(cudaMemcpy(&status, m->out_status(), 4, cudaMemcpyDeviceToHost));
+    return check_status(m, status);
+  }
+  return FR_B200_OK;
+}
+
+// ---- state ---------------------------------------------------------------------------------------
+
+int fr_b200_state_count(const fr_b200_model *m) { return m ? (m->v5 ? 3 : 5) : FR_B200_E_ARG; }
+size_t fr_b200_state_bytes(const fr_b200_model *m) { return m ? m->layer_stride * m->L : 0; }
+
+int fr_b200_state_tensor(fr_b200_model *m, int slot, int layer, int index, void **dev_ptr, int *dtype, int64_t *numel) {
+  if (!m) return fail(FR_B200_E_ARG, "null model");
+  if (slot < 0 || slot >= m->cfg.max_batch || layer < 0 || layer >= m->L || index < 0 || index >= fr_b200_state_count(m))
+    return fail(FR_B200_E_ARG, "state index out of range");
+  const size_t ab = act_bytes(m->cfg.act_fp16), C = m->C;
+  uint8_t *base = m->d_state + (size_t)slot * m->state_stride + (size_t)layer * m->layer_stride;
+  size_t off = 0; int64_t n = C; int dt = m->cfg.act_fp16 ? FR_B200_T_F16 : FR_B200_T_F32;
+  if (!m->v5) {
+    if (index >= 1 && index <= 3) { off = C * ab + (size_t)(index - 1) * C * 4; dt = FR_B200_T_F32; }
+    else if (index == 4) off = C * ab + 3 * C * 4;
+  } else {
+    if (index == 1) { off = C * ab; n = (int64_t)m->H * 4096; dt = FR_B200_T_F32; }
+    else if (index == 2) off = C * ab + (size_t)m->H * 4096 * 4;
+  }
+  if (dev_ptr) *dev_ptr = base + off;
+  if (dtype) *dtype = dt;
+  if (numel) *numel = n;
+  return FR_B200_OK;
+}
+
+int fr_b200_state_reset(fr_b200_model *m, int slot) {
+  if (!m) return fail(FR_B200_E_ARG, "null model");
+  if (slot < -1 || slot >= m->cfg.max_batch) return fail(FR_B200_E_ARG, "slot out of range");
+  CU(cudaSetDevice(m->device));
+  const size_t per = m->layer_stride * m->L;
+  std::vector<uint8_t> h(per, 0);
+  if (!m->v5) {
+    // pp = -1e30 (model.cpp:157-158)
+    for (int l = 0; l < m->L; ++l) {
+      float *pp = reinterpret_cast<float *>(h.data() + (size_t)l * m->layer_stride + (size_t)m->C * act_bytes(m->cfg.act_fp16) + 2 * (size_t)m->C * 4);
+      for (int i = 0; i < m->C; ++i) pp[i] = -1e30f;
+    }
+  }
+  for (int s = 0; s < m->cfg.max_batch; ++s)
+    if (slot < 0 || slot == s) CU(cudaMemcpy(m->d_state + (size_t)s * m->state_stride, h.data(), per, cudaMemcpyHostToDevice));
+  return FR_B200_OK;
+}
+
+int fr_b200_state_export(fr_b200_model *m, int slot, void *dst, size_t dst_bytes) {
+  if (!m || !dst) return fail(FR_B200_E_ARG, "null argument");
+  if (slot < 0 || slot >= m->cfg.max_batch) return fail(FR_B200_E_ARG, "slot out of range");
+  if (dst_bytes < fr_b200_state_bytes(m)) return fail(FR_B200_E_ARG, "destination too small");
+  CU(cudaSetDevice(m->device));
+  CU(cudaMemcpy(dst, m->d_state + (size_t)slot * m->state_stride, fr_b200_state_bytes(m), cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+
+int fr_b200_state_import(fr_b200_model *m, int slot, const void *src, size_t src_bytes) {
+  if (!m || !src) return fail(FR_B200_E_ARG, "null argument");
+  if (slot < 0 || slot >= m->cfg.max_batch) return fail(FR_B200_E_ARG, "slot out of range");
+  if (src_bytes != fr_b200_state_bytes(m)) return fail(FR_B200_E_ARG, "state size mismatch");
+  CU(cudaSetDevice(m->device));
+  CU(cudaMemcpy(m->d_state + (size_t)slot * m->state_stride, src, src_bytes, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+
+// ---- quantisers -----------------------------------------------------------------------------------
+
+namespace {
+struct DevBuf {
+  void *p = nullptr;
+  ~DevBuf() { if (p) cudaFree(p); }
+  cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 256); }
+};
+}  // namespace
+
+int fr_b200_quantize_int8(const float *W, int K, int N, int8_t *q, uint16_t *scales, int device) {
+  if (!W || !q || !scales || K <= 0 || N <= 0) return fail(FR_B200_E_ARG, "bad argument");
+  CU(cudaSetDevice(device));
+  DevBuf dw, dq, ds;
+  CU(dw.alloc((size_t)K * N * 4)); CU(dq.alloc((size_t)K * N)); CU(ds.alloc((size_t)N * 2));
+  CU(cudaMemcpy(dw.p, W, (size_t)K * N * 4, cudaMemcpyDefault));
+  CU(launch_quant_int8((const float *)dw.p, K, N, (int8_t *)dq.p, (__half *)ds.p, 0));
+  CU(cudaMemcpy(q, dq.p, (size_t)K * N, cudaMemcpyDefault));
+  CU(cudaMemcpy(scales, ds.p, (size_t)N * 2, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+int fr_b200_quantize_int4(const float *W, int K, int N, uint8_t *packed, uint16_t *scales, int device) {
+  if (!W || !packed || !scales || K <= 0 || N <= 0 || K % 32) return fail(FR_B200_E_ARG, "bad argument (K must be a multiple of 32)");
+  CU(cudaSetDevice(device));
+  DevBuf dw, dq, ds;
+  CU(dw.alloc((size_t)K * N * 4)); CU(dq.alloc((size_t)K * N / 2)); CU(ds.alloc((size_t)N * (K / 32) * 2));
+  CU(cudaMemcpy(dw.p, W, (size_t)K * N * 4, cudaMemcpyDefault));
+  CU(launch_quant_int4((const float *)dw.p, K, N, (uint8_t *)dq.p, (__half *)ds.p, 0));
+  CU(cudaMemcpy(packed, dq.p, (size_t)K * N / 2, cudaMemcpyDefault));
+  CU(cudaMemcpy(scales, ds.p, (size_t)N * (K / 32) * 2, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+int fr_b200_dequantize_int8(const int8_t *q, const uint16_t *scales, int K, int N, float *W, int device) {
+  if (!W || !q || !scales || K <= 0 || N <= 0) return fail(FR_B200_E_ARG, "bad argument");
+  CU(cudaSetDevice(device));
+  DevBuf dw, dq, ds;
+  CU(dw.alloc((size_t)K * N * 4)); CU(dq.alloc((size_t)K * N)); CU(ds.alloc((size_t)N * 2));
+  CU(cudaMemcpy(dq.p, q, (size_t)K * N, cudaMemcpyDefault));
+  CU(cudaMemcpy(ds.p, scales, (size_t)N * 2, cudaMemcpyDefault));
+  CU(launch_dequant_int8((const int8_t *)dq.p, (const __half *)ds.p, K, N, (float *)dw.p, 0));
+  CU(cudaMemcpy(W, dw.p, (size_t)K * N * 4, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+int fr_b200_dequantize_int4(const uint8_t *packed, const uint16_t *scales, int K, int N, float *W, int device) {
+  if (!W || !packed || !scales || K <= 0 || N <= 0 || K % 32) return fail(FR_B200_E_ARG, "bad argument");
+  CU(cudaSetDevice(device));
+  DevBuf dw, dq, ds;
+  CU(dw.alloc((size_t)K * N * 4)); CU(dq.alloc((size_t)K * N / 2)); CU(ds.alloc((size_t)N * (K / 32) * 2));
+  CU(cudaMemcpy(dq.p, packed, (size_t)K * N / 2, cudaMemcpyDefault));
+  CU(cudaMemcpy(ds.p, scales, (size_t)N * (K / 32) * 2, cudaMemcpyDefault));
+  CU(launch_dequant_int4((const uint8_t *)dq.p, (const __half *)ds.p, K, N, (float *)dw.p, 0));
+  CU(cudaMemcpy(W, dw.p, (size_t)K * N * 4, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+
+int fr_b200_unpack_matrix(fr_b200_model *m, const char *name, float *W, int K, int N) {
+  if (!m || !name || !W) return fail(FR_B200_E_ARG, "null argument");
+  auto it = m->mats.find(name);
+  if (it == m->mats.end()) return fail(FR_B200_E_ARG, std::string("unknown matrix ") + name);
+  const MatrixSlot &s = it->second;
+  if (!s.set) return fail(FR_B200_E_STATE, "matrix not uploaded yet");
+  if (K != s.K || N != s.N) return fail(FR_B200_E_ARG, "shape mismatch");
+  CU(cudaSetDevice(m->device));
+  DevBuf dw;
+  CU(dw.alloc((size_t)K * N * 4));
+  CU(launch_unpack(m->fmt, m->d_weights + s.tile_off, s.item_stride, m->d_rscale + s.rscale_off, s.rscale_stride, K, N,
+                   (float *)dw.p, 0));
+  CU(cudaMemcpy(W, dw.p, (size_t)K * N * 4, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+
+int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float *x, int batch, float *y, int device) {
+  if (!W || !x || !y || K <= 0 || N <= 0 || K % 64) return fail(FR_B200_E_ARG, "bad argument (K must be a positive multiple of 64)");
+  if (weight_format < 0 || weight_format > 2) return fail(FR_B200_E_ARG, "bad weight_format");
+  if (batch < 1 || batch > MAX_B) return fail(FR_B200_E_ARG, "batch must be 1..8");
+  CU(cudaSetDevice(device));
+  const int fmt = weight_format, Npad = (N + ROWS - 1) / ROWS * ROWS, nb = Npad / ROWS;
+  const size_t rb = rowblock_bytes(fmt, K), n = (size_t)K * N;
+  DevBuf dW, dW16, dq, ds, dt, drs, dx, dy, dsync, dph;
+  CU(dW.alloc(n * 4)); CU(dt.alloc(rb * nb)); CU(drs.alloc((size_t)Npad * 2)); CU(dx.alloc((size_t)batch * K * 4));
+  CU(dy.alloc(((size_t)batch * Npad + 1) * 4)); CU(dsync.alloc(8)); CU(dph.alloc(sizeof(PhaseDev)));
+  CU(cudaMemcpy(dW.p, W, n * 4, cudaMemcpyDefault));
+  CU(cudaMemcpy(dx.p, x, (size_t)batch * K * 4, cudaMemcpyDefault));
+  CU(cudaMemset(dsync.p, 0, 8));
+  CU(cudaMemset(dy.p, 0, ((size_t)batch * Npad + 1) * 4));
+  CU(cudaMemset(drs.p, 0, (size_t)Npad * 2));
+  if (fmt == FMT_FP16) {
+    CU(dW16.alloc(n * 2));
+    CU(launch_f32_to_f16((const float *)dW.p, (__half *)dW16.p, n, 0));
+    CU(launch_pack(fmt, dW16.p, nullptr, K, N, (uint8_t *)dt.p, rb, nullptr, 0, 0));
+  } else if (fmt == FMT_INT8) {
+    CU(dq.alloc(n)); CU(ds.alloc((size_t)N * 2));
+    CU(launch_quant_int8((const float *)dW.p, K, N, (int8_t *)dq.p, (__half *)ds.p, 0));
+    CU(launch_pack(fmt, dq.p, (const __half *)ds.p, K, N, (uint8_t *)dt.p, rb, (__half *)drs.p, ROWS, 0));
+  } else {
+    CU(dq.alloc(n / 2)); CU(ds.alloc((size_t)N * (K / 32) * 2));
+    CU(launch_quant_int4((const float *)dW.p, K, N, (uint8_t *)dq.p, (__half *)ds.p, 0));
+    CU(launch_pack(fmt, dq.p, (const __half *)ds.p, K, N, (uint8_t *)dt.p, rb, nullptr, 0, 0));
+  }
+  PhaseDev ph;
+  memset(&ph, 0, sizeof(ph));
+  ph.w = (const uint8_t *)dt.p; ph.rscale = (const __half *)drs.p; ph.kind = PH_MATVEC; ph.K = K; ph.n_items = nb; ph.n_sub = 1;
+  CU(cudaMemcpy(dph.p, &ph, sizeof(ph), cudaMemcpyHostToDevice));
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.version = 4; p.L = 0; p.C = 64; p.F = K; p.V = N;  // operand space is max(3*C, F) * batch p.Vpad = Npad; p.fmt = fmt; p.B = batch; p.n_phases = 1;
+  p.phases = (const PhaseDev *)dph.p; p.kk = (float *)dx.p; p.logits = (float *)dy.p;
+  p.sync = (unsigned *)dsync.p; p.status = (int *)((float *)dy.p + (size_t)batch * Npad);
+  const int NB = batch == 1 ? 1 : 8;
+  int optin = 0, grid = 0;
+  CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  int stages = 0;
+  for (int s = 6; s >= 2; --s)
+    if (decode_smem_bytes(fmt, NB, 64, K, 4, s) <= (size_t)optin) { stages = s; break; }
+  if (!stages) return fail(FR_B200_E_UNSUPPORTED, "K too large for shared memory");
+  p.n_stages = stages;
+  const size_t smem = decode_smem_bytes(fmt, NB, 64, K, 4, stages);
+  CU(decode_max_grid(fmt, NB, smem, device, &grid));
+  if (!grid) return fail(FR_B200_E_UNSUPPORTED, "kernel does not fit");
+  CU(launch_decode(p, NB, grid, smem, 0));
+  CU(cudaDeviceSynchronize());
+  int status = 0;
+  CU(cudaMemcpy(&status, p.status, 4, cudaMemcpyDeviceToHost));
+  if (status) return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(status) + ")");
+  CU(cudaMemcpy2D(y, (size_t)N * 4, dy.p, (size_t)Npad * 4, (size_t)N * 4, batch, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+
+int fr_b200_get_info(const fr_b200_model *m, fr_b200_info *info) {
+  if (!m || !info) return fail(FR_B200_E_ARG, "null argument");
+  info->n_ctas = m->grid; info->n_threads = NTHREADS; info->smem_bytes = (int)m->smem1; info->n_stages = m->n_stages;
+  info->stage_bytes = (int)stage_bytes(m->fmt, kt_max(m->fmt)); info->n_phases = (int)m->phases.size();
+  info->weight_stream_bytes = m->stream_bytes; info->launches = m->launches;
+  return FR_B200_OK;
+}
+
+}  // extern "C"

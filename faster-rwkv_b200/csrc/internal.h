@@ -1,0 +1,104 @@
+// Structures shared by the C-ABI implementation (api.cu), the packers (pack.cu) and the persistent
+// decode kernel (decode.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "layout.h"
+
+namespace frb {
+
+constexpr int NW = 8;                       // consumer warps per CTA
+constexpr int NCONS = NW * 32;              // consumer threads
+constexpr int NTHREADS = NCONS + 32;        // + one producer warp
+constexpr int MAX_STAGES = 12;
+constexpr int MAX_B = 8;
+
+// What a phase does around its matvecs.
+enum PhaseKind {
+  PH_ATT_KVR = 0,   // v4: LN1 + mix -> K,V,R row blocks of the same 16 channels -> WKV update -> r*wkv
+  PH_ATT_O = 1,     // v4/v5: output projection + residual
+  PH_FFN_KR = 2,    // LN2 + mix -> ffn key (relu^2) and ffn receptance (sigmoid)
+  PH_FFN_V = 3,     // ffn value, gated residual, optional x/2
+  PH_HEAD = 4,      // ln_out + vocabulary head
+  PH5_KVRG = 5,     // v5: LN1 + mix -> K,V,R(,G) row blocks, raw sums (gate through SiLU)
+  PH5_WKV = 6,      // v5: per-head state update + readout (no weights)
+  PH_MATVEC = 7,    // stand-alone y = W x (unit tests): input vector from kk, output to logits
+};
+
+struct PhaseDev {
+  const uint8_t *w;        // packed tiles: [item][sub][stage]
+  const __half *rscale;    // int8: per-row scales in (item, sub, row) order; else null
+  int kind;
+  int layer;
+  int K;                   // inputs of every matvec of the phase
+  int n_items;             // row blocks (all classes together); 0 for PH5_WKV
+  int n_sub;               // matrices fused per item (3 for PH_ATT_KVR, else 1)
+  int split[3];            // item index where class 1, 2, 3 start (PH_FFN_KR, PH5_KVRG)
+  int rot;                 // item i runs on CTA (i + rot) % gridDim.x
+  int pad;
+};
+
+// Per-layer vectors (all fp32 on the device) and state offsets.
+struct LayerDev {
+  const float *ln1_w, *ln1_b, *ln2_w, *ln2_b;
+  const float *att_mix[4];   // k, v, r, (g)
+  const float *ffn_mix[2];   // k, r
+  const float *decay, *first;
+  const float *lnx_w, *lnx_b;  // v5
+};
+
+struct DecodeParams {
+  int version, L, C, F, V, Vpad, H;
+  int fmt, act_fp16, rescale_every;
+  int B;
+  int n_phases;
+  int n_stages;
+  int ids_val[MAX_B];
+  const int32_t *ids_dev;      // when non-null the ids are read from here
+  const __half *emb;           // [V][C]
+  const LayerDev *layers;
+  const float *lnout_w, *lnout_b;
+  const PhaseDev *phases;
+  float *x, *rwkv, *kk, *rr, *logits;   // [B][C], [B][C], [B][F], [B][C], [B][Vpad]
+  float *k5, *v5, *r5, *g5, *o5;        // v5 exchange vectors [B][C]
+  uint8_t *state;                       // stream slot b at state + b * state_stride
+  size_t state_stride, layer_stride;    // bytes
+  unsigned *sync;                       // [0] grid barrier counter, [1] exit counter
+  int *status;                          // 0 = ok, else first failure code
+};
+
+// status codes written by the kernel
+constexpr int ST_TIMEOUT_FULL = 101, ST_TIMEOUT_EMPTY = 102, ST_TIMEOUT_GRID = 103;
+
+// state byte offsets inside one layer of one stream slot
+FRB_HD size_t act_bytes(int act_fp16) { return act_fp16 ? 2 : 4; }
+FRB_HD size_t v4_layer_bytes(int C, int act_fp16) { return 2 * C * act_bytes(act_fp16) + 3 * (size_t)C * 4; }
+FRB_HD size_t v5_layer_bytes(int C, int H, int act_fp16) {
+  return 2 * C * act_bytes(act_fp16) + (size_t)H * 64 * 64 * 4;
+}
+
+// ---- launchers implemented in the .cu files ------------------------------------------------------
+size_t decode_smem_bytes(int fmt, int NB, int C, int F, int version, int n_stages);
+cudaError_t launch_decode(const DecodeParams &p, int NB, int grid, size_t smem, cudaStream_t st);
+cudaError_t decode_max_grid(int fmt, int NB, size_t smem, int device, int *grid);
+cudaError_t launch_argmax(const float *logits, int B, int V, int Vpad, int32_t *out, cudaStream_t st);
+
+// quantise / pack (pack.cu); all pointers device
+cudaError_t launch_f16_to_f32(const __half *src, float *dst, size_t n, cudaStream_t st);
+cudaError_t launch_f32_to_f16(const float *src, __half *dst, size_t n, cudaStream_t st);
+cudaError_t launch_quant_int8(const float *W, int K, int N, int8_t *q, __half *scales, cudaStream_t st);
+cudaError_t launch_quant_int4(const float *W, int K, int N, uint8_t *packed, __half *scales, cudaStream_t st);
+cudaError_t launch_dequant_int8(const int8_t *q, const __half *scales, int K, int N, float *W, cudaStream_t st);
+cudaError_t launch_dequant_int4(const uint8_t *packed, const __half *scales, int K, int N, float *W, cudaStream_t st);
+// Pack one matrix into tiles.  src depends on fmt: fp16 -> __half W[K][N]; int8 -> q[N][K] (+scales[N]);
+// int4 -> packed[N][K/2] (+scales[N][K/32]).  Row block rb of the matrix goes to dst + rb * item_stride.
+// rscale_dst (int8): per-row scales, row r of block rb at rscale_dst[rb * rscale_stride + r].
+cudaError_t launch_pack(int fmt, const void *src, const __half *scales, int K, int N, uint8_t *dst,
+                        size_t item_stride, __half *rscale_dst, size_t rscale_stride, cudaStream_t st);
+// Inverse of launch_pack: tiles -> dequantised fp32 W[K][N].
+cudaError_t launch_unpack(int fmt, const uint8_t *tiles, size_t item_stride, const __half *rscale,
+                          size_t rscale_stride, int K, int N, float *W, cudaStream_t st);
+
+}  // namespace frb
