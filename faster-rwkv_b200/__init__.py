@@ -18,7 +18,7 @@ import numpy as np
 from . import synth  # noqa: F401  (re-exported: synthetic `.fr` generator)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libfr_b200.so")
+LIB_PATH = os.environ.get("FR_B200_LIB") or os.path.join(_HERE, "csrc", "libfr_b200.so")
 
 W_FP16, W_INT8, W_INT4 = 0, 1, 2
 T_F16, T_F32 = 0, 1

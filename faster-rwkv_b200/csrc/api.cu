@@ -54,7 +54,7 @@ struct fr_b200_model {
   uint8_t *d_weights = nullptr;  size_t weights_bytes = 0;
   __half *d_rscale = nullptr;    size_t rscale_n = 0;
   float *d_vecs = nullptr;       size_t vecs_n = 0;
-  __half *d_emb = nullptr;
+  uint8_t *d_emb = nullptr;      int emb_dtype = -1;   // rows kept in the dtype they arrive in
   uint8_t *d_state = nullptr;    size_t state_stride = 0, layer_stride = 0;
   float *d_x = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;
   float *d_v5buf = nullptr;      // k5, v5, r5, g5, o5
@@ -74,8 +74,8 @@ struct fr_b200_model {
   bool emb_set = false;
   std::vector<PhaseDev> phases;
   bool finalized = false;
-  int n_stages = 0, n_stages8 = 0, grid = 0;
-  size_t smem1 = 0, smem8 = 0;
+  int n_stages[3] = {0, 0, 0}, grid = 0;   // per decode mode (1, <=4, <=8 streams)
+  size_t smem[3] = {0, 0, 0};
   long long launches = 0;
   long long stream_bytes = 0;
 
@@ -317,7 +317,6 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_weights, m->weights_bytes);
   if (!rc) rc = alloc((void **)&m->d_rscale, m->rscale_n * 2);
   if (!rc) rc = alloc((void **)&m->d_vecs, m->vecs_n * 4);
-  if (!rc) rc = alloc((void **)&m->d_emb, (size_t)m->V * m->C * 2);
   if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
   if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * 4);
   if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * 4);
@@ -331,7 +330,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc && cudaMallocHost((void **)&m->h_out, m->out_bytes()) != cudaSuccess) rc = fail(FR_B200_E_NOMEM, "cudaMallocHost failed");
   if (rc) { fr_b200_destroy(m); return rc; }
   cudaMemset(m->d_weights, 0, m->weights_bytes);
-  cudaMemset(m->d_rscale, 0, m->rscale_n * 2 + 2);
+  cudaMemset(m->d_rscale, 0, m->rscale_n * 2);
   cudaMemset(m->d_out, 0, m->out_bytes());
   cudaMemset(m->d_sync, 0, 8);
   m->emb_rows_set.assign(m->V, 0);
@@ -376,16 +375,15 @@ int fr_b200_set_tensor(fr_b200_model *m, const char *name, const void *data, int
       if (numel != (size_t)m->C) return fail(FR_B200_E_ARG, "embedding row must have n_embd elements");
       row0 = (size_t)r; rows = 1;
     }
-    __half *dst = m->d_emb + row0 * m->C;
-    if (dtype == FR_B200_T_F16) {
-      CU(cudaMemcpy(dst, data, rows * m->C * 2, cudaMemcpyDefault));
-    } else {
-      int rc = ensure_scratch(m, 0, rows * m->C * 4);
-      if (rc) return rc;
-      CU(cudaMemcpy(m->d_scratch[0], data, rows * m->C * 4, cudaMemcpyDefault));
-      CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), dst, rows * m->C, 0));
-      CU(cudaDeviceSynchronize());
+    if (m->emb_dtype < 0) {
+      m->emb_dtype = dtype;
+      cudaError_t e = cudaMalloc((void **)&m->d_emb, (size_t)m->V * m->C * (dtype == FR_B200_T_F16 ? 2 : 4));
+      if (e != cudaSuccess) return fail(FR_B200_E_NOMEM, std::string("cudaMalloc(emb): ") + cudaGetErrorString(e));
+    } else if (m->emb_dtype != dtype) {
+      return fail(FR_B200_E_ARG, "embedding rows must all have the same dtype");
     }
+    const size_t es = dtype == FR_B200_T_F16 ? 2 : 4;
+    CU(cudaMemcpy(m->d_emb + row0 * m->C * es, data, rows * m->C * es, cudaMemcpyDefault));
     for (size_t r = row0; r < row0 + rows; ++r) m->emb_rows_set[r] = 1;
     return FR_B200_OK;
   }
@@ -444,22 +442,21 @@ int fr_b200_finalize(fr_b200_model *m) {
   if (want < 2) want = 2;
   if (want > MAX_STAGES) want = MAX_STAGES;
   const int ver = m->v5 ? 5 : 4;
-  auto fit = [&](int NB) -> int {
+  const int max_mode = decode_mode(m->cfg.max_batch);
+  for (int mode = 0; mode <= max_mode; ++mode) {
+    int st = 0;
     for (int s = want; s >= 2; --s)
-      if (decode_smem_bytes(m->fmt, NB, m->C, m->F, ver, s) <= (size_t)optin) return s;
-    return 0;
-  };
-  const int s1 = fit(1), s8 = m->cfg.max_batch > 1 ? fit(8) : s1;
-  if (s1 == 0 || s8 == 0) return fail(FR_B200_E_UNSUPPORTED, "model too wide for shared memory at this batch size");
-  m->n_stages = s1;
-  m->n_stages8 = s8;
-  m->smem1 = decode_smem_bytes(m->fmt, 1, m->C, m->F, ver, s1);
-  m->smem8 = decode_smem_bytes(m->fmt, 8, m->C, m->F, ver, s8);
-  int g1 = 0, g8 = 0;
-  CU(decode_max_grid(m->fmt, 1, m->smem1, m->device, &g1));
-  CU(decode_max_grid(m->fmt, 8, m->smem8, m->device, &g8));
-  if (g1 == 0 || g8 == 0) return fail(FR_B200_E_UNSUPPORTED, "decode kernel does not fit on an SM");
-  m->grid = g1;
+      if (decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, s) <= (size_t)optin) { st = s; break; }
+    if (st == 0)
+      return fail(FR_B200_E_UNSUPPORTED, "model too wide for shared memory at this batch size (max_batch " +
+                                             std::to_string(m->cfg.max_batch) + ")");
+    m->n_stages[mode] = st;
+    m->smem[mode] = decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, st);
+    int g = 0;
+    CU(decode_max_grid(m->fmt, mode, m->smem[mode], m->device, &g));
+    if (g == 0) return fail(FR_B200_E_UNSUPPORTED, "decode kernel does not fit on an SM");
+    m->grid = g;
+  }
   // stash capacity: ceil(C / grid) channels per CTA
   if ((m->C + m->grid - 1) / m->grid > 128) return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the shift-state stash");
   // phase table with real pointers; rotate item ownership from phase to phase
@@ -483,17 +480,16 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t 
   p.fmt = m->fmt; p.act_fp16 = m->cfg.act_fp16; p.rescale_every = m->cfg.act_fp16 ? 6 : 0;
   p.B = batch;
   p.n_phases = (int)m->phases.size();
-  const int NB = batch == 1 ? 1 : 8;
-  size_t smem = NB == 1 ? m->smem1 : m->smem8;
-  // stages that fit for this NB
-  p.n_stages = NB == 1 ? m->n_stages : m->n_stages8;
+  const int mode = decode_mode(batch);
+  const size_t smem = m->smem[mode];
+  p.n_stages = m->n_stages[mode];
   if (ids_host)
     for (int b = 0; b < batch; ++b) {
       if (ids_host[b] < 0 || ids_host[b] >= m->V) return fail(FR_B200_E_ARG, "token id out of range");
       p.ids_val[b] = ids_host[b];
     }
   p.ids_dev = ids_dev;
-  p.emb = m->d_emb; p.layers = m->d_layers; p.phases = m->d_phases;
+  p.emb = m->d_emb; p.emb_f32 = m->emb_dtype == FR_B200_T_F32; p.layers = m->d_layers; p.phases = m->d_phases;
   p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
   p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
   p.x = m->d_x; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
@@ -501,7 +497,7 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t 
   p.k5 = m->d_v5buf; p.v5 = p.k5 + bc; p.r5 = p.v5 + bc; p.g5 = p.r5 + bc; p.o5 = p.g5 + bc;
   p.state = m->d_state; p.state_stride = m->state_stride; p.layer_stride = m->layer_stride;
   p.sync = m->d_sync; p.status = m->out_status();
-  CU(launch_decode(p, NB, m->grid, smem, st));
+  CU(launch_decode(p, mode, m->grid, smem, st));
   m->launches++;
   if (want_argmax) {
     CU(launch_argmax(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), st));
@@ -761,21 +757,22 @@ int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float 
   CU(cudaMemcpy(dph.p, &ph, sizeof(ph), cudaMemcpyHostToDevice));
   DecodeParams p;
   memset(&p, 0, sizeof(p));
-  p.version = 4; p.L = 0; p.C = 64; p.F = K; p.V = N;  // operand space is max(3*C, F) * batch p.Vpad = Npad; p.fmt = fmt; p.B = batch; p.n_phases = 1;
+  // C only sizes the operand space, max(3*C, F) * batch halfs
+  p.version = 4; p.L = 0; p.C = 64; p.F = K; p.V = N; p.Vpad = Npad; p.fmt = fmt; p.B = batch; p.n_phases = 1;
   p.phases = (const PhaseDev *)dph.p; p.kk = (float *)dx.p; p.logits = (float *)dy.p;
   p.sync = (unsigned *)dsync.p; p.status = (int *)((float *)dy.p + (size_t)batch * Npad);
-  const int NB = batch == 1 ? 1 : 8;
+  const int mode = decode_mode(batch);
   int optin = 0, grid = 0;
   CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   int stages = 0;
   for (int s = 6; s >= 2; --s)
-    if (decode_smem_bytes(fmt, NB, 64, K, 4, s) <= (size_t)optin) { stages = s; break; }
+    if (decode_smem_bytes(fmt, mode, 64, K, 4, s) <= (size_t)optin) { stages = s; break; }
   if (!stages) return fail(FR_B200_E_UNSUPPORTED, "K too large for shared memory");
   p.n_stages = stages;
-  const size_t smem = decode_smem_bytes(fmt, NB, 64, K, 4, stages);
-  CU(decode_max_grid(fmt, NB, smem, device, &grid));
+  const size_t smem = decode_smem_bytes(fmt, mode, 64, K, 4, stages);
+  CU(decode_max_grid(fmt, mode, smem, device, &grid));
   if (!grid) return fail(FR_B200_E_UNSUPPORTED, "kernel does not fit");
-  CU(launch_decode(p, NB, grid, smem, 0));
+  CU(launch_decode(p, mode, grid, smem, 0));
   CU(cudaDeviceSynchronize());
   int status = 0;
   CU(cudaMemcpy(&status, p.status, 4, cudaMemcpyDeviceToHost));
@@ -786,7 +783,7 @@ int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float 
 
 int fr_b200_get_info(const fr_b200_model *m, fr_b200_info *info) {
   if (!m || !info) return fail(FR_B200_E_ARG, "null argument");
-  info->n_ctas = m->grid; info->n_threads = NTHREADS; info->smem_bytes = (int)m->smem1; info->n_stages = m->n_stages;
+  info->n_ctas = m->grid; info->n_threads = NTHREADS; info->smem_bytes = (int)m->smem[0]; info->n_stages = m->n_stages[0];
   info->stage_bytes = (int)stage_bytes(m->fmt, kt_max(m->fmt)); info->n_phases = (int)m->phases.size();
   info->weight_stream_bytes = m->stream_bytes; info->launches = m->launches;
   return FR_B200_OK;

@@ -8,9 +8,12 @@
 //     consumers sit in a grid barrier;
 //   * the consumers stage the phase's input vectors in shared memory as fp16 tensor-core operands
 //     (LayerNorm + token-shift mix fused here), then for every 16-row block multiply the streamed
-//     tile with mma.sync.m16n8k16 (weights = A operand, up to 8 streams = B operand columns, fp32
+//     tile with mma.sync.m16n8k16 (weights = A operand, streams = B operand columns, fp32
 //     accumulation, int8/int4 dequantised in registers), reduce across the warps that split K, and
 //     apply the phase's epilogue (WKV state update + sigmoid gate, residual add, squared ReLU, ...).
+//     Each activation is fed as two fp16 columns, hi = fp16(x) and lo = fp16(x - hi), whose results
+//     are added: the operand keeps ~22 mantissa bits at no extra MMA for one stream (7 of the 8
+//     columns are idle anyway) and 4 streams share one MMA.
 // Phases are separated by a grid barrier (release/acquire counter in global memory).  Every wait
 // is bounded: after WAIT_LIMIT_NS it records a status and the CTA drains without hanging.
 #include "common.cuh"
@@ -34,16 +37,18 @@ struct Smem {
 };
 constexpr int STASH_N = 128;
 
-template <int NB> __host__ __device__ constexpr int red_n() { return NB == 1 ? 16 : 128; }
+// NB = operand columns kept per n-tile (2: one stream as hi/lo; 8: four streams as hi/lo), NT = n-tiles.
+template <int NB, int NT> __host__ __device__ constexpr int n_streams() { return NB == 2 ? 1 : 4 * NT; }
+template <int NB, int NT> __host__ __device__ constexpr int red_n() { return ROWS * n_streams<NB, NT>(); }
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-template <int NB>
+template <int NB, int NT>
 __host__ __device__ inline size_t smem_layout(size_t xs_halfs, int n_stages, size_t *off_stash, size_t *off_red,
                                               size_t *off_xs, size_t *off_ring) {
   size_t o = 1024;  // barriers + flags + LN scratch
-  *off_stash = o; o += sizeof(float) * NB * STASH_N;
-  *off_red = o;   o += sizeof(float) * 2 * 3 * NW * red_n<NB>();
+  *off_stash = o; o += sizeof(float) * n_streams<NB, NT>() * STASH_N;
+  *off_red = o;   o += sizeof(float) * 2 * 3 * NW * red_n<NB, NT>();
   o = align_up(o, 128);
   *off_xs = o;    o += xs_halfs * 2;
   o = align_up(o, 1024);
@@ -51,44 +56,66 @@ __host__ __device__ inline size_t smem_layout(size_t xs_halfs, int n_stages, siz
   return o;
 }
 
-__host__ __device__ inline size_t xs_halfs_needed(int C, int F, int version, int NB) {
+__host__ __device__ inline size_t xs_halfs_needed(int C, int F, int version, int NB, int NT) {
   size_t a = (size_t)(version == 4 ? 3 : 4) * C;
   size_t b = F;
-  return (a > b ? a : b) * NB;
+  return (a > b ? a : b) * NB * NT;
 }
 
 // ------------------------------------------------------------------------------------------------
-// stage x operand -> accumulators
-template <int FMT, int NB>
-__device__ __forceinline__ void process_stage(const uint8_t *st, int nch, const __half *xv, int chunk0, int warp,
-                                              int lane, float acc[2][4]) {
+// stage x operand -> accumulators.  acc[e][t]: two interleaved accumulator sets e (breaks the MMA
+// dependency chain), n-tile t.
+template <int FMT, int NB, int NT>
+__device__ __forceinline__ void process_stage(const uint8_t *st, int nch, const __half *xv, size_t plane_u4, int chunk0,
+                                              int warp, int lane, float acc[2][NT][4]) {
   const int g = lane >> 2, q = lane & 3;
-  const int n = NB == 1 ? 0 : g;
+  const int n = NB == 2 ? (g & 1) : g;   // operand column this lane feeds
   const uint4 *xb = reinterpret_cast<const uint4 *>(xv);
   for (int c = warp; c < nch; c += NW) {
     const size_t xo = ((size_t)(chunk0 + c) * 2 * NB + n) * 4 + q;
-    const uint4 b01 = xb[xo];            // MMAs 0,1 of the chunk
-    const uint4 b23 = xb[xo + NB * 4];   // MMAs 2,3
+    uint4 b01[NT], b23[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      b01[t] = xb[xo + t * plane_u4];            // MMAs 0,1 of the chunk
+      b23[t] = xb[xo + t * plane_u4 + NB * 4];   // MMAs 2,3
+    }
     if (FMT == FMT_FP16) {
       const uint4 *A = reinterpret_cast<const uint4 *>(st + (size_t)c * 2048) + lane;
       const uint4 a0 = A[0], a1 = A[32], a2 = A[64], a3 = A[96];
-      mma16816(acc[0], a0.x, a0.y, a0.z, a0.w, b01.x, b01.y);
-      mma16816(acc[1], a1.x, a1.y, a1.z, a1.w, b01.z, b01.w);
-      mma16816(acc[0], a2.x, a2.y, a2.z, a2.w, b23.x, b23.y);
-      mma16816(acc[1], a3.x, a3.y, a3.z, a3.w, b23.z, b23.w);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        mma16816(acc[0][t], a0.x, a0.y, a0.z, a0.w, b01[t].x, b01[t].y);
+        mma16816(acc[1][t], a1.x, a1.y, a1.z, a1.w, b01[t].z, b01[t].w);
+        mma16816(acc[0][t], a2.x, a2.y, a2.z, a2.w, b23[t].x, b23[t].y);
+        mma16816(acc[1][t], a3.x, a3.y, a3.z, a3.w, b23[t].z, b23[t].w);
+      }
     } else if (FMT == FMT_INT8) {
       const uint4 *A = reinterpret_cast<const uint4 *>(st + (size_t)c * 1024) + lane;
       const uint4 w01 = A[0], w23 = A[32];
       const uint32_t M = 0x64646464u, OFF = 0x64806480u;  // 1024 + byte, minus 1152 -> byte - 128
 #define FRB_I8(w, sel) hsub2_u32(prmt(w, M, sel), OFF)
-      mma16816(acc[0], FRB_I8(w01.x, 0x4140), FRB_I8(w01.x, 0x4342), FRB_I8(w01.y, 0x4140), FRB_I8(w01.y, 0x4342),
-               b01.x, b01.y);
-      mma16816(acc[1], FRB_I8(w01.z, 0x4140), FRB_I8(w01.z, 0x4342), FRB_I8(w01.w, 0x4140), FRB_I8(w01.w, 0x4342),
-               b01.z, b01.w);
-      mma16816(acc[0], FRB_I8(w23.x, 0x4140), FRB_I8(w23.x, 0x4342), FRB_I8(w23.y, 0x4140), FRB_I8(w23.y, 0x4342),
-               b23.x, b23.y);
-      mma16816(acc[1], FRB_I8(w23.z, 0x4140), FRB_I8(w23.z, 0x4342), FRB_I8(w23.w, 0x4140), FRB_I8(w23.w, 0x4342),
-               b23.z, b23.w);
+      {
+        const uint32_t p0 = FRB_I8(w01.x, 0x4140), p1 = FRB_I8(w01.x, 0x4342), p2 = FRB_I8(w01.y, 0x4140),
+                       p3 = FRB_I8(w01.y, 0x4342);
+        const uint32_t r0 = FRB_I8(w01.z, 0x4140), r1 = FRB_I8(w01.z, 0x4342), r2 = FRB_I8(w01.w, 0x4140),
+                       r3 = FRB_I8(w01.w, 0x4342);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          mma16816(acc[0][t], p0, p1, p2, p3, b01[t].x, b01[t].y);
+          mma16816(acc[1][t], r0, r1, r2, r3, b01[t].z, b01[t].w);
+        }
+      }
+      {
+        const uint32_t p0 = FRB_I8(w23.x, 0x4140), p1 = FRB_I8(w23.x, 0x4342), p2 = FRB_I8(w23.y, 0x4140),
+                       p3 = FRB_I8(w23.y, 0x4342);
+        const uint32_t r0 = FRB_I8(w23.z, 0x4140), r1 = FRB_I8(w23.z, 0x4342), r2 = FRB_I8(w23.w, 0x4140),
+                       r3 = FRB_I8(w23.w, 0x4342);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          mma16816(acc[0][t], p0, p1, p2, p3, b23[t].x, b23[t].y);
+          mma16816(acc[1][t], r0, r1, r2, r3, b23[t].z, b23[t].w);
+        }
+      }
 #undef FRB_I8
     } else {
       const uint4 w = (reinterpret_cast<const uint4 *>(st + (size_t)c * 512))[lane];
@@ -103,20 +130,28 @@ __device__ __forceinline__ void process_stage(const uint8_t *st, int nch, const 
   const uint32_t t2 = hsub2_u32(lop3_and_or((wd) >> 8, LO, M0), O0); \
   const uint32_t t3 = hsub2_u32(lop3_and_or((wd) >> 8, HI, M1), O1);
       {
-        float t[4] = {0.f, 0.f, 0.f, 0.f};
         FRB_I4(w.x, p0, p1, p2, p3)
-        mma16816(t, p0, p1, p2, p3, b01.x, b01.y);
         FRB_I4(w.y, r0, r1, r2, r3)
-        mma16816(t, r0, r1, r2, r3, b01.z, b01.w);
-        acc[0][0] += s0.x * t[0]; acc[0][1] += s0.x * t[1]; acc[0][2] += s0.y * t[2]; acc[0][3] += s0.y * t[3];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          float s[4] = {0.f, 0.f, 0.f, 0.f};
+          mma16816(s, p0, p1, p2, p3, b01[t].x, b01[t].y);
+          mma16816(s, r0, r1, r2, r3, b01[t].z, b01[t].w);
+          acc[0][t][0] += s0.x * s[0]; acc[0][t][1] += s0.x * s[1];
+          acc[0][t][2] += s0.y * s[2]; acc[0][t][3] += s0.y * s[3];
+        }
       }
       {
-        float t[4] = {0.f, 0.f, 0.f, 0.f};
         FRB_I4(w.z, p0, p1, p2, p3)
-        mma16816(t, p0, p1, p2, p3, b23.x, b23.y);
         FRB_I4(w.w, r0, r1, r2, r3)
-        mma16816(t, r0, r1, r2, r3, b23.z, b23.w);
-        acc[1][0] += s1.x * t[0]; acc[1][1] += s1.x * t[1]; acc[1][2] += s1.y * t[2]; acc[1][3] += s1.y * t[3];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          float s[4] = {0.f, 0.f, 0.f, 0.f};
+          mma16816(s, p0, p1, p2, p3, b23[t].x, b23[t].y);
+          mma16816(s, r0, r1, r2, r3, b23[t].z, b23[t].w);
+          acc[1][t][0] += s1.x * s[0]; acc[1][t][1] += s1.x * s[1];
+          acc[1][t][2] += s1.y * s[2]; acc[1][t][3] += s1.y * s[3];
+        }
       }
 #undef FRB_I4
     }
@@ -194,18 +229,36 @@ __device__ __forceinline__ float4 load_act4(const uint8_t *base, int i4, int act
   return __ldcg(reinterpret_cast<const float4 *>(base) + i4);
 }
 
-__device__ __forceinline__ void store_half4(__half *dst, float a, float b, float c, float d) {
-  __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+// Operand position of stream b inside a vector: n-tile plane and the hi / lo columns.
+template <int NB>
+__device__ __forceinline__ void operand_cols(int b, int &tile, int &col_hi, int &col_lo) {
+  if (NB == 2) { tile = 0; col_hi = 0; col_lo = 1; }
+  else { tile = b >> 2; col_hi = b & 3; col_lo = 4 + (b & 3); }
+}
+
+// Write 4 consecutive inputs k..k+3 of stream b into operand vector `vec` as hi + lo fp16 columns.
+template <int NB>
+__device__ __forceinline__ void store_operand4(__half *vec, size_t plane_halfs, int k, int b, float a, float bb, float c,
+                                               float dd) {
+  int tile, ch, cl;
+  operand_cols<NB>(b, tile, ch, cl);
+  __half *pl = vec + (size_t)tile * plane_halfs;
+  const __half2 h0 = __floats2half2_rn(a, bb), h1 = __floats2half2_rn(c, dd);
+  const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+  const __half2 l0 = __floats2half2_rn(a - f0.x, bb - f0.y), l1 = __floats2half2_rn(c - f1.x, dd - f1.y);
   uint2 u;
-  u.x = *reinterpret_cast<uint32_t *>(&lo);
-  u.y = *reinterpret_cast<uint32_t *>(&hi);
-  *reinterpret_cast<uint2 *>(dst) = u;
+  u.x = *reinterpret_cast<const uint32_t *>(&h0); u.y = *reinterpret_cast<const uint32_t *>(&h1);
+  *reinterpret_cast<uint2 *>(pl + xs_index(k, ch, NB)) = u;
+  u.x = *reinterpret_cast<const uint32_t *>(&l0); u.y = *reinterpret_cast<const uint32_t *>(&l1);
+  *reinterpret_cast<uint2 *>(pl + xs_index(k, cl, NB)) = u;
 }
 
 // Residual stream column b, float4 index i4: the embedding row at layer 0, else x.
 __device__ __forceinline__ float4 load_x4(const DecodeParams &p, int layer0, int b, int i4) {
   if (layer0) {
-    const __half *row = p.emb + (size_t)token_id(p, b) * p.C;
+    if (p.emb_f32)
+      return __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * p.C) + i4);
+    const __half *row = reinterpret_cast<const __half *>(p.emb) + (size_t)token_id(p, b) * p.C;
     const uint2 u = __ldg(reinterpret_cast<const uint2 *>(row) + i4);
     const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
     const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
@@ -216,8 +269,9 @@ __device__ __forceinline__ float4 load_x4(const DecodeParams &p, int layer0, int
 
 // LayerNorm statistics of the residual stream for all B columns -> sm.stats (mean[b], rstd[b]).
 // Shifted single pass: sums of (x - x[0]) and (x - x[0])^2 in fp32.
-template <int NB>
+template <int SB>
 __device__ __forceinline__ void ln_stats(Ctx &cx, int layer0) {
+  constexpr int NB = SB;  // one slot per stream
   const DecodeParams &p = *cx.p;
   const int n4 = p.C >> 2;
   float s1[NB], s2[NB], piv[NB];
@@ -272,13 +326,15 @@ __device__ __forceinline__ void ln_stats(Ctx &cx, int layer0) {
 
 // LayerNorm + token-shift mix: writes nvec operand vectors (fp16) into sm.xs, stashes LN output of
 // the owned channels for the deferred shift-state write.  nvec == 0: plain LayerNorm -> xs[0].
-template <int NB>
+template <int NB, int NT>
 __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, int layer0, const float *ln_w, const float *ln_b,
                                                 const float *const *mix, int nvec, const uint8_t *sx_state) {
+  constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
-  ln_stats<NB>(cx, layer0);
+  ln_stats<SB>(cx, layer0);
   const int n4 = p.C >> 2;
-  const size_t vstride = (size_t)p.C * NB;  // halfs per operand vector
+  const size_t plane = (size_t)p.C * NB;   // halfs per (vector, n-tile)
+  const size_t vstride = plane * NT;       // halfs per operand vector
   for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
     const float4 gw = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4);
     const float4 gb = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4);
@@ -287,7 +343,7 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, int layer0, const float
     for (int v = 0; v < 4; ++v)
       if (v < nvec) mx[v] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4);
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
       const float mean = cx.sm.stats[2 * b], rstd = cx.sm.stats[2 * b + 1];
       const float4 xv = load_x4(p, layer0, b, i4);
@@ -296,9 +352,8 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, int layer0, const float
       xx.y = (xv.y - mean) * rstd * gw.y + gb.y;
       xx.z = (xv.z - mean) * rstd * gw.z + gb.z;
       xx.w = (xv.w - mean) * rstd * gw.w + gb.w;
-      const int xi = xs_index(i4 * 4, b, NB);
       if (nvec == 0) {
-        store_half4(cx.sm.xs + xi, xx.x, xx.y, xx.z, xx.w);
+        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, xx.x, xx.y, xx.z, xx.w);
         continue;
       }
       const float4 sx = load_act4(sx_state + (size_t)b * p.state_stride, i4, p.act_fp16);
@@ -306,8 +361,9 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, int layer0, const float
       for (int v = 0; v < 4; ++v) {
         if (v < nvec) {
           const float4 m = mx[v];
-          store_half4(cx.sm.xs + v * vstride + xi, xx.x * m.x + sx.x * (1.f - m.x), xx.y * m.y + sx.y * (1.f - m.y),
-                      xx.z * m.z + sx.z * (1.f - m.z), xx.w * m.w + sx.w * (1.f - m.w));
+          store_operand4<NB>(cx.sm.xs + v * vstride, plane, i4 * 4, b, xx.x * m.x + sx.x * (1.f - m.x),
+                             xx.y * m.y + sx.y * (1.f - m.y), xx.z * m.z + sx.z * (1.f - m.z),
+                             xx.w * m.w + sx.w * (1.f - m.w));
         }
       }
       const int c = i4 * 4 - cx.own0;
@@ -324,31 +380,35 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, int layer0, const float
 }
 
 // fp32 vector [B][K] in global memory -> operand vector 0
-template <int NB>
+template <int NB, int NT>
 __device__ __forceinline__ void prologue_vec(Ctx &cx, const float *src, int K) {
+  constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
   const int n4 = K >> 2;
+  const size_t plane = (size_t)K * NB;
   for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
       const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)b * K) + i4);
-      store_half4(cx.sm.xs + xs_index(i4 * 4, b, NB), v.x, v.y, v.z, v.w);
+      store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v.x, v.y, v.z, v.w);
     }
   }
   bar_sync(BAR_CONS, NCONS);
 }
 
 // v5 output projection input: GroupNorm over each head's 64 readout values, times the gate
-template <int NB>
+template <int NB, int NT>
 __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly) {
+  constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
+  const size_t plane = (size_t)p.C * NB;
   const int n4 = p.C >> 2;  // 16 float4 per head -> 16 consecutive threads share a head
   for (int base = 0; base < n4; base += NCONS) {
     const int i4 = base + cx.tid;
     const bool ok = i4 < n4;
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
       float4 v = ok ? __ldcg(reinterpret_cast<const float4 *>(p.o5 + (size_t)b * p.C) + i4) : make_float4(0, 0, 0, 0);
       float s = (v.x + v.y) + (v.z + v.w);
@@ -369,7 +429,7 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly) {
           const float4 g = __ldcg(reinterpret_cast<const float4 *>(p.g5 + (size_t)b * p.C) + i4);
           y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w;
         }
-        store_half4(cx.sm.xs + xs_index(i4 * 4, b, NB), y.x, y.y, y.z, y.w);
+        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, y.x, y.y, y.z, y.w);
       }
     }
   }
@@ -408,7 +468,9 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
     case PH_ATT_O: {
       const int c = it * ROWS + row;
       float xin;
-      if (ph.layer == 0) xin = __half2float(p.emb[(size_t)token_id(p, b) * C + c]);
+      if (ph.layer == 0)
+        xin = p.emb_f32 ? __ldg(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * C + c)
+                        : __half2float(reinterpret_cast<const __half *>(p.emb)[(size_t)token_id(p, b) * C + c]);
       else xin = __ldcg(p.x + (size_t)b * C + c);
       p.x[(size_t)b * C + c] = xin + val[0];
       break;
@@ -451,22 +513,27 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
 }
 
 // ---- all row blocks of a phase that belong to this CTA ----------------------------------------------
-template <int FMT, int NB>
+template <int FMT, int NB, int NT>
 __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const LayerDev *ly) {
+  constexpr int SB = n_streams<NB, NT>();
+  constexpr int RN = red_n<NB, NT>();
   const DecodeParams &p = *cx.p;
   const int KT = kt_max(FMT);
   const int nst = num_stages(FMT, ph.K);
-  const size_t vstride = (size_t)ph.K * NB;
+  const size_t plane = (size_t)ph.K * NB;   // halfs per (vector, n-tile)
+  const size_t vstride = plane * NT;
   int buf = 0;
   const int first = (cx.cta + cx.G - ph.rot) % cx.G;
   for (int it = first; it < ph.n_items; it += cx.G) {
-    float acc[3][2][4];
+    float acc[3][2][NT][4];
 #pragma unroll
     for (int u = 0; u < 3; ++u)
 #pragma unroll
       for (int e = 0; e < 2; ++e)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[u][e][i] = 0.f;
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[u][e][t][i] = 0.f;
 #pragma unroll
     for (int u = 0; u < 3; ++u) {
       if (u < ph.n_sub) {
@@ -478,34 +545,47 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
         for (int s = 0; s < nst; ++s) {
           const int kt = min(KT, ph.K - s * KT);
           mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
-          process_stage<FMT, NB>(cx.sm.ring + (size_t)cx.slot * SLOT_BYTES, kt / CHUNK_K, xv, s * (KT / CHUNK_K),
-                                 cx.warp, cx.lane, acc[u]);
+          process_stage<FMT, NB, NT>(cx.sm.ring + (size_t)cx.slot * SLOT_BYTES, kt / CHUNK_K, xv, plane / 8,
+                                     s * (KT / CHUNK_K), cx.warp, cx.lane, acc[u]);
           __syncwarp();
           if (cx.lane == 0) mbar_arrive(&cx.sm.empty[cx.slot]);
           if (++cx.slot == p.n_stages) { cx.slot = 0; cx.parity ^= 1u; }
         }
       }
     }
-    // cross-warp reduction of the K split
-    float *red = cx.sm.red + (size_t)buf * 3 * NW * red_n<NB>();
+    // hi + lo columns, then the cross-warp reduction of the K split.  Accumulator c0,c1 = row g,
+    // columns 2q, 2q+1; c2,c3 = row g+8.
+    float *red = cx.sm.red + (size_t)buf * 3 * NW * RN;
     const int g = cx.lane >> 2, q = cx.lane & 3;
 #pragma unroll
     for (int u = 0; u < 3; ++u) {
       if (u < ph.n_sub) {
-        float *r = red + ((size_t)u * NW + cx.warp) * red_n<NB>();
-        const float c0 = acc[u][0][0] + acc[u][1][0], c1 = acc[u][0][1] + acc[u][1][1];
-        const float c2 = acc[u][0][2] + acc[u][1][2], c3 = acc[u][0][3] + acc[u][1][3];
-        if (NB == 1) {
-          if (q == 0) { r[g] = c0; r[g + 8] = c2; }
-        } else {
-          r[g * 8 + 2 * q] = c0; r[g * 8 + 2 * q + 1] = c1;
-          r[(g + 8) * 8 + 2 * q] = c2; r[(g + 8) * 8 + 2 * q + 1] = c3;
+        float *r = red + ((size_t)u * NW + cx.warp) * RN;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          float c0 = acc[u][0][t][0] + acc[u][1][t][0], c1 = acc[u][0][t][1] + acc[u][1][t][1];
+          float c2 = acc[u][0][t][2] + acc[u][1][t][2], c3 = acc[u][0][t][3] + acc[u][1][t][3];
+          if (NB == 2) {
+            // columns 0 (hi) and 1 (lo) of the q == 0 lanes
+            if (q == 0) { r[g] = c0 + c1; r[g + 8] = c2 + c3; }
+          } else {
+            // columns 0..3 = hi of streams 0..3 (lanes q = 0,1), columns 4..7 = lo (lanes q = 2,3)
+            c0 += __shfl_xor_sync(0xffffffffu, c0, 2);
+            c1 += __shfl_xor_sync(0xffffffffu, c1, 2);
+            c2 += __shfl_xor_sync(0xffffffffu, c2, 2);
+            c3 += __shfl_xor_sync(0xffffffffu, c3, 2);
+            if (q < 2) {
+              const int sb = t * 4 + 2 * q;
+              r[g * SB + sb] = c0; r[g * SB + sb + 1] = c1;
+              r[(g + 8) * SB + sb] = c2; r[(g + 8) * SB + sb + 1] = c3;
+            }
+          }
         }
       }
     }
     bar_sync(BAR_CONS, NCONS);
-    if (cx.tid < ROWS * NB) {
-      const int row = cx.tid / NB, b = cx.tid % NB;
+    if (cx.tid < ROWS * SB) {
+      const int row = cx.tid / SB, b = cx.tid % SB;
       if (b < p.B) {
         float val[3] = {0.f, 0.f, 0.f};
 #pragma unroll
@@ -513,7 +593,7 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
           if (u < ph.n_sub) {
             float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < NW; ++w) s += red[((size_t)u * NW + w) * red_n<NB>() + cx.tid];
+            for (int w = 0; w < NW; ++w) s += red[((size_t)u * NW + w) * RN + cx.tid];
             if (FMT == FMT_INT8) s *= __half2float(__ldg(ph.rscale + ((size_t)it * ph.n_sub + u) * ROWS + row));
             val[u] = s;
           }
@@ -571,7 +651,7 @@ __device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const La
 }
 
 // ------------------------------------------------------------------------------------------------
-template <int FMT, int NB>
+template <int FMT, int NB, int NT>
 __device__ __forceinline__ void consumer(Ctx &cx) {
   const DecodeParams &p = *cx.p;
   for (int pi = 0; pi < p.n_phases; ++pi) {
@@ -584,28 +664,28 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
       case PH_ATT_KVR:
       case PH5_KVRG: {
         const int nvec = p.version == 4 || p.version == 50 ? 3 : 4;
-        prologue_ln_mix<NB>(cx, ph.layer == 0, ly->ln1_w, ly->ln1_b, ly->att_mix, nvec, st0);
+        prologue_ln_mix<NB, NT>(cx, ph.layer == 0, ly->ln1_w, ly->ln1_b, ly->att_mix, nvec, st0);
         cx.stash_dst = st0;
         break;
       }
       case PH_ATT_O:
-        if (p.version == 4) prologue_vec<NB>(cx, p.rwkv, p.C);
-        else prologue_gn_gate<NB>(cx, *ly);
+        if (p.version == 4) prologue_vec<NB, NT>(cx, p.rwkv, p.C);
+        else prologue_gn_gate<NB, NT>(cx, *ly);
         break;
       case PH_FFN_KR: {
         const size_t off = p.version == 4 ? (size_t)p.C * act_bytes(p.act_fp16) + 3 * (size_t)p.C * 4
                                           : (size_t)p.C * act_bytes(p.act_fp16) + (size_t)p.H * 4096 * 4;
-        prologue_ln_mix<NB>(cx, 0, ly->ln2_w, ly->ln2_b, ly->ffn_mix, 2, st0 + off);
+        prologue_ln_mix<NB, NT>(cx, 0, ly->ln2_w, ly->ln2_b, ly->ffn_mix, 2, st0 + off);
         cx.stash_dst = st0 + off;
         break;
       }
-      case PH_FFN_V: prologue_vec<NB>(cx, p.kk, p.F); break;
-      case PH_HEAD: prologue_ln_mix<NB>(cx, 0, p.lnout_w, p.lnout_b, nullptr, 0, nullptr); break;
-      case PH_MATVEC: prologue_vec<NB>(cx, p.kk, ph.K); break;
+      case PH_FFN_V: prologue_vec<NB, NT>(cx, p.kk, p.F); break;
+      case PH_HEAD: prologue_ln_mix<NB, NT>(cx, 0, p.lnout_w, p.lnout_b, nullptr, 0, nullptr); break;
+      case PH_MATVEC: prologue_vec<NB, NT>(cx, p.kk, ph.K); break;
       default: break;
     }
     if (ph.kind == PH5_WKV) phase_wkv5(cx, ph, *ly);
-    else run_items<FMT, NB>(cx, ph, ly);
+    else run_items<FMT, NB, NT>(cx, ph, ly);
     if (pi + 1 < p.n_phases) grid_barrier(cx);
   }
 }
@@ -649,7 +729,7 @@ __device__ __forceinline__ void producer(Ctx &cx) {
   }
 }
 
-template <int FMT, int NB>
+template <int FMT, int NB, int NT>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   Ctx cx;
@@ -658,7 +738,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   cx.cta = blockIdx.x; cx.G = gridDim.x;
   cx.slot = 0; cx.parity = 0; cx.epoch = 0; cx.stash_dst = nullptr;
   size_t o_stash, o_red, o_xs, o_ring;
-  smem_layout<NB>(xs_halfs_needed(p.C, p.F, p.version, NB), p.n_stages, &o_stash, &o_red, &o_xs, &o_ring);
+  smem_layout<NB, NT>(xs_halfs_needed(p.C, p.F, p.version, NB, NT), p.n_stages, &o_stash, &o_red, &o_xs, &o_ring);
   cx.sm.full = reinterpret_cast<uint64_t *>(smem);
   cx.sm.empty = cx.sm.full + MAX_STAGES;
   cx.sm.abort_flag = reinterpret_cast<volatile int *>(smem + 256);
@@ -685,7 +765,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   if (cx.warp == NW) {
     if (cx.lane == 0) producer<FMT>(cx);
   } else {
-    consumer<FMT, NB>(cx);
+    consumer<FMT, NB, NT>(cx);
     // last arrival resets the barrier words for the next launch
     bar_sync(BAR_CONS, NCONS);
     if (cx.tid == 0) {
@@ -732,20 +812,20 @@ __global__ void argmax_kernel(const float *logits, int V, int Vpad, int32_t *out
   }
 }
 
-template <int FMT, int NB>
+template <int FMT, int NB, int NT>
 cudaError_t launch_t(const DecodeParams &p, int grid, size_t smem, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(decode_kernel<FMT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(decode_kernel<FMT, NB, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   void *args[] = {const_cast<DecodeParams *>(&p)};
-  return cudaLaunchCooperativeKernel((void *)decode_kernel<FMT, NB>, dim3(grid), dim3(NTHREADS), args, smem, st);
+  return cudaLaunchCooperativeKernel((void *)decode_kernel<FMT, NB, NT>, dim3(grid), dim3(NTHREADS), args, smem, st);
 }
 
-template <int FMT, int NB>
+template <int FMT, int NB, int NT>
 cudaError_t max_grid_t(size_t smem, int device, int *grid) {
-  cudaError_t e = cudaFuncSetAttribute(decode_kernel<FMT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(decode_kernel<FMT, NB, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   int per_sm = 0, sms = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_kernel<FMT, NB>, NTHREADS, smem);
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_kernel<FMT, NB, NT>, NTHREADS, smem);
   if (e != cudaSuccess) return e;
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (e != cudaSuccess) return e;
@@ -755,30 +835,37 @@ cudaError_t max_grid_t(size_t smem, int device, int *grid) {
 
 }  // namespace
 
-size_t decode_smem_bytes(int fmt, int NB, int C, int F, int version, int n_stages) {
+// mode: 0 = one stream, 1 = up to 4 streams, 2 = up to 8 streams
+size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages) {
   (void)fmt;
   size_t a, b, c, d;
-  return NB == 1 ? smem_layout<1>(xs_halfs_needed(C, F, version, 1), n_stages, &a, &b, &c, &d)
-                 : smem_layout<8>(xs_halfs_needed(C, F, version, 8), n_stages, &a, &b, &c, &d);
+  switch (mode) {
+    case 0: return smem_layout<2, 1>(xs_halfs_needed(C, F, version, 2, 1), n_stages, &a, &b, &c, &d);
+    case 1: return smem_layout<8, 1>(xs_halfs_needed(C, F, version, 8, 1), n_stages, &a, &b, &c, &d);
+    default: return smem_layout<8, 2>(xs_halfs_needed(C, F, version, 8, 2), n_stages, &a, &b, &c, &d);
+  }
 }
 
-#define FRB_DISPATCH(fn, ...)                                                     \
-  switch (fmt * 2 + (NB == 1 ? 0 : 1)) {                                          \
-    case 0: return fn<FMT_FP16, 1>(__VA_ARGS__);                                  \
-    case 1: return fn<FMT_FP16, 8>(__VA_ARGS__);                                  \
-    case 2: return fn<FMT_INT8, 1>(__VA_ARGS__);                                  \
-    case 3: return fn<FMT_INT8, 8>(__VA_ARGS__);                                  \
-    case 4: return fn<FMT_INT4, 1>(__VA_ARGS__);                                  \
-    case 5: return fn<FMT_INT4, 8>(__VA_ARGS__);                                  \
-    default: return cudaErrorInvalidValue;                                        \
+#define FRB_DISPATCH(fn, ...)                                     \
+  switch (fmt * 3 + mode) {                                       \
+    case 0: return fn<FMT_FP16, 2, 1>(__VA_ARGS__);               \
+    case 1: return fn<FMT_FP16, 8, 1>(__VA_ARGS__);               \
+    case 2: return fn<FMT_FP16, 8, 2>(__VA_ARGS__);               \
+    case 3: return fn<FMT_INT8, 2, 1>(__VA_ARGS__);               \
+    case 4: return fn<FMT_INT8, 8, 1>(__VA_ARGS__);               \
+    case 5: return fn<FMT_INT8, 8, 2>(__VA_ARGS__);               \
+    case 6: return fn<FMT_INT4, 2, 1>(__VA_ARGS__);               \
+    case 7: return fn<FMT_INT4, 8, 1>(__VA_ARGS__);               \
+    case 8: return fn<FMT_INT4, 8, 2>(__VA_ARGS__);               \
+    default: return cudaErrorInvalidValue;                        \
   }
 
-cudaError_t launch_decode(const DecodeParams &p, int NB, int grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_decode(const DecodeParams &p, int mode, int grid, size_t smem, cudaStream_t st) {
   const int fmt = p.fmt;
   FRB_DISPATCH(launch_t, p, grid, smem, st)
 }
 
-cudaError_t decode_max_grid(int fmt, int NB, size_t smem, int device, int *grid) {
+cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *grid) {
   FRB_DISPATCH(max_grid_t, smem, device, grid)
 }
 

@@ -57,7 +57,8 @@ struct DecodeParams {
   int n_stages;
   int ids_val[MAX_B];
   const int32_t *ids_dev;      // when non-null the ids are read from here
-  const __half *emb;           // [V][C]
+  const void *emb;             // [V][C], fp32 when emb_f32 else fp16 (the file's dtype)
+  int emb_f32;
   const LayerDev *layers;
   const float *lnout_w, *lnout_b;
   const PhaseDev *phases;
@@ -80,9 +81,11 @@ FRB_HD size_t v5_layer_bytes(int C, int H, int act_fp16) {
 }
 
 // ---- launchers implemented in the .cu files ------------------------------------------------------
-size_t decode_smem_bytes(int fmt, int NB, int C, int F, int version, int n_stages);
-cudaError_t launch_decode(const DecodeParams &p, int NB, int grid, size_t smem, cudaStream_t st);
-cudaError_t decode_max_grid(int fmt, int NB, size_t smem, int device, int *grid);
+// mode = how many streams one launch carries: 0 -> 1, 1 -> up to 4, 2 -> up to 8
+inline int decode_mode(int batch) { return batch == 1 ? 0 : batch <= 4 ? 1 : 2; }
+size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages);
+cudaError_t launch_decode(const DecodeParams &p, int mode, int grid, size_t smem, cudaStream_t st);
+cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *grid);
 cudaError_t launch_argmax(const float *logits, int B, int V, int Vpad, int32_t *out, cudaStream_t st);
 
 // quantise / pack (pack.cu); all pointers device

@@ -28,7 +28,7 @@ def build(force: bool = False) -> str:
 
 class _Cfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in
-                ("version", "n_layer", "n_embd", "n_ffn", "n_head", "vocab", "rescale_every")]
+                ("version", "n_layer", "n_embd", "n_ffn", "n_head", "vocab", "rescale_every", "state_fp16")]
 
 
 def lib() -> ctypes.CDLL:
@@ -124,15 +124,17 @@ class OracleModel:
 
     rescale_every=6 reproduces the fp16 strategy's x /= 2 every 6 layers
     (kernels/default/model_forward.cpp:173-175) for files whose weights were pre-divided.
+    state_fp16=True stores the token-shift states rounded to fp16, as the "cuda fp16" strategy does
+    (its state tensors have the activation dtype, model.cpp:149-151).
     weight_format "int8" / "int4" replaces every projection matrix and the head by its
     quantise->dequantise image, which is what the quantised strategies multiply by.
     """
 
     def __init__(self, shape, tensors: Dict[str, np.ndarray], param_order: List[str], rescale_every: int = 0,
-                 weight_format: str = "fp16"):
+                 weight_format: str = "fp16", state_fp16: bool = False):
         self.shape = shape
         self.cfg = _Cfg(_version_code(shape.version), shape.n_layer, shape.n_embd, shape.n_ffn, shape.n_head,
-                        shape.vocab, rescale_every)
+                        shape.vocab, rescale_every, int(state_fp16))
         self._keep = []
         for name in param_order:
             a = np.ascontiguousarray(tensors[name], dtype=np.float32)

@@ -26,6 +26,8 @@ typedef struct {
   int version;        /* 4, 50 (v5.0), 51 (v5.1), 52 (v5.2) */
   int n_layer, n_embd, n_ffn, n_head, vocab;
   int rescale_every;  /* 6 when the activations are fp16 (model_forward.cpp:173), else 0 */
+  int state_fp16;     /* 1: token-shift states are stored as fp16, as under "cuda fp16" where the state
+                         tensors have the activation dtype (model.cpp:149-151, kernels/cuda/att.cu:337-359) */
 } orc_cfg;
 
 int orc_num_threads(void) {
@@ -43,6 +45,10 @@ void orc_set_threads(int n) {
   (void)n;
 #endif
 }
+
+static uint16_t f32_to_f16(float f);
+static float f16_to_f32(uint16_t h);
+static inline float state_round(float v, int state_fp16) { return state_fp16 ? f16_to_f32(f32_to_f16(v)) : v; }
 
 /* ---------------------------------------------------------------- primitives */
 
@@ -93,7 +99,7 @@ static void mix(const float *xx, const float *sx, const float *m, int n, float *
 
 /* RWKV-4 time mix, kernels/default/att.cpp:16-45 (same maths as WkvForwardOne,
  * kernels/cuda/att.cu:30-62).  state: sx, aa, bb, pp each [C], updated in place. */
-static void att_v4(int C, float *x, float *sx, float *aa, float *bb, float *pp, const float *const *p,
+static void att_v4(int C, int sf16, float *x, float *sx, float *aa, float *bb, float *pp, const float *const *p,
                    float *tmp) {
   const float *ln_w = p[0], *ln_b = p[1], *mk = p[2], *mv = p[3], *mr = p[4], *decay = p[5],
               *first = p[6], *kw = p[7], *vw = p[8], *rw = p[9], *ow = p[10];
@@ -122,14 +128,14 @@ static void att_v4(int C, float *x, float *sx, float *aa, float *bb, float *pp, 
     r[i] = rr * wkv;
   }
   matvec(r, ow, C, C, out);
-  for (int i = 0; i < C; ++i) { x[i] += out[i]; sx[i] = xx[i]; }
+  for (int i = 0; i < C; ++i) { x[i] += out[i]; sx[i] = state_round(xx[i], sf16); }
 }
 
 /* RWKV-5 / 5.1 / 5.2 one-token time mix: kernels/default/att.cpp:47-113 with the gate fed
  * by gx as the CUDA path does (kernels/cuda/att.cu:289).  State s is [H][S key][S value];
  * decay / first are indexed per head (v5.0, att.cu:242) or per (head, key) (v5.1/5.2,
  * att.cu:306).  GroupNorm with H groups, eps 1e-5 (kernels/cuda/group_norm.cu:322-357). */
-static void att_v5(int version, int C, int H, float *x, float *sx, float *s, const float *const *p,
+static void att_v5(int version, int C, int H, int sf16, float *x, float *sx, float *s, const float *const *p,
                    float *tmp) {
   const int S = C / H, gate = version >= 51;
   int q = 0;
@@ -170,11 +176,11 @@ static void att_v5(int version, int C, int H, float *x, float *sx, float *s, con
   }
   if (gate) for (int i = 0; i < C; ++i) out[i] *= g[i];
   matvec(out, ow, C, C, k /* reuse */);
-  for (int i = 0; i < C; ++i) { x[i] += k[i]; sx[i] = xx[i]; }
+  for (int i = 0; i < C; ++i) { x[i] += k[i]; sx[i] = state_round(xx[i], sf16); }
 }
 
 /* Channel mix, kernels/default/ffn.cpp:8-23. */
-static void ffn(int C, int F, float *x, float *sx, const float *const *p, float *tmp) {
+static void ffn(int C, int F, int sf16, float *x, float *sx, const float *const *p, float *tmp) {
   const float *ln_w = p[0], *ln_b = p[1], *mk = p[2], *mr = p[3], *kw = p[4], *vw = p[5], *rw = p[6];
   float *xx = tmp, *kx = tmp + C, *rx = tmp + 2 * C, *r = tmp + 3 * C, *out = tmp + 4 * C,
         *kk = tmp + 5 * C;
@@ -185,7 +191,7 @@ static void ffn(int C, int F, float *x, float *sx, const float *const *p, float 
   matvec(kx, kw, C, F, kk);
   for (int i = 0; i < F; ++i) { float t = kk[i] > 0.f ? kk[i] : 0.f; kk[i] = t * t; }
   matvec(kk, vw, F, C, out);
-  for (int i = 0; i < C; ++i) { x[i] += sigmoidf_(r[i]) * out[i]; sx[i] = xx[i]; }
+  for (int i = 0; i < C; ++i) { x[i] += sigmoidf_(r[i]) * out[i]; sx[i] = state_round(xx[i], sf16); }
 }
 
 /* ---------------------------------------------------------------- whole model */
@@ -227,13 +233,13 @@ int orc_forward(const orc_cfg *c, const float *const *params, const float *emb, 
     const float *const *p = params + (size_t)l * ppl;
     if (c->version == 4) {
       float *st = state + (size_t)l * 5 * C;
-      att_v4(C, x, st, st + C, st + 2 * C, st + 3 * C, p, tmp);
-      ffn(C, F, x, st + 4 * C, p + natt, tmp);
+      att_v4(C, c->state_fp16, x, st, st + C, st + 2 * C, st + 3 * C, p, tmp);
+      ffn(C, F, c->state_fp16, x, st + 4 * C, p + natt, tmp);
     } else {
       size_t S = C / H, per = 2 * (size_t)C + (size_t)H * S * S;
       float *st = state + (size_t)l * per;
-      att_v5(c->version, C, H, x, st, st + C, p, tmp);
-      ffn(C, F, x, st + C + (size_t)H * S * S, p + natt, tmp);
+      att_v5(c->version, C, H, c->state_fp16, x, st, st + C, p, tmp);
+      ffn(C, F, c->state_fp16, x, st + C + (size_t)H * S * S, p + natt, tmp);
     }
     if (c->rescale_every > 0 && (l + 1) % c->rescale_every == 0)
       for (int i = 0; i < C; ++i) x[i] *= 0.5f;

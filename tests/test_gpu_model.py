@@ -16,7 +16,7 @@ def _pair(pkg, orc, synth, name, strat, seed=11, max_batch=1, ln_random=True):
     tensors = synth.to_file_dtypes(shape, synth.generate(shape, seed=seed, ln_random=ln_random), file_dtype)
     m = pkg.Model(tensors, strategy, shape=shape, max_batch=max_batch)
     ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6 if fmt == "fp16" else 0,
-                          weight_format=fmt)
+                          weight_format=fmt, state_fp16=fmt == "fp16")
     return shape, tensors, m, ref
 
 
@@ -154,7 +154,7 @@ def test_fr_file_load(pkg, orc, synth, tmp_path):
     p = str(tmp_path / "tiny4-fp16.fr")
     synth.write_fr(p, shape, tensors)
     m = pkg.Model(p, "cuda fp16")
-    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6)
+    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6, state_fp16=True)
     _close(m.run(0), ref.run(0))
     _close(m.run(0), ref.run(0))
     m.close()
