@@ -74,6 +74,7 @@ SIGNATURES = {
     "fr_b200_unpack_matrix": (_i, [_vp, ctypes.c_char_p, _vp, _i, _i]),
     "fr_b200_matvec": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i]),
     "fr_b200_get_info": (_i, [_vp, ctypes.POINTER(Info)]),
+    "fr_b200_decode_profile": (_i, [_vp, _vp, _i, _vp, _i]),
     "fr_b200_strerror": (ctypes.c_char_p, [_i]),
     "fr_b200_last_error": (ctypes.c_char_p, []),
 }
@@ -193,6 +194,16 @@ class Model:
         check(lib().fr_b200_decode_greedy(self._h, _np_ptr(ids), len(ids), n_tokens, _np_ptr(out), None),
               "fr_b200_decode_greedy")
         return out
+
+    def decode_profile(self, ids: Sequence[int]) -> np.ndarray:
+        """One decode step; returns the [n_ctas, n_phases, 8] trace described at fr_b200_decode_profile in include/fr_b200.h."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        inf = self.info()
+        n, g = inf["n_phases"], inf["n_ctas"]
+        st = np.zeros((g, n, 8), np.uint64)
+        check(lib().fr_b200_decode_profile(self._h, _np_ptr(ids), len(ids), _np_ptr(st), g * n * 8),
+              "fr_b200_decode_profile")
+        return st
 
     # -- state -------------------------------------------------------------------------------
     def reset_states(self, slot: int = -1) -> None:

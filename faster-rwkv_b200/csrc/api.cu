@@ -56,10 +56,11 @@ struct fr_b200_model {
   float *d_vecs = nullptr;       size_t vecs_n = 0;
   uint8_t *d_emb = nullptr;      int emb_dtype = -1;   // rows kept in the dtype they arrive in
   uint8_t *d_state = nullptr;    size_t state_stride = 0, layer_stride = 0;
-  float *d_x = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;
-  float *d_v5buf = nullptr;      // k5, v5, r5, g5, o5
+  exch_t *d_x = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;   // tagged exchange vectors
+  exch_t *d_v5buf = nullptr;     // k5, v5, r5, g5, o5
+  unsigned seq = 0;              // phases launched so far (tags continue across launches)
+  unsigned par[MAX_B] = {0, 0, 0, 0, 0, 0, 0, 0};   // which copy of the token-shift states each slot reads next
   float *d_out = nullptr;        // [B][Vpad] logits, then [B] argmax ints, then status int
-  unsigned *d_sync = nullptr;
   LayerDev *d_layers = nullptr;
   PhaseDev *d_phases = nullptr;
   uint8_t *h_out = nullptr;      // pinned mirror of d_out
@@ -77,6 +78,7 @@ struct fr_b200_model {
   int n_stages[3] = {0, 0, 0}, grid = 0;   // per decode mode (1, <=4, <=8 streams)
   size_t smem[3] = {0, 0, 0};
   long long launches = 0;
+  int l2_prefetch = 384 * 1024;  // bytes per CTA the producer keeps requested from L2 ahead of the ring
   long long stream_bytes = 0;
 
   int32_t *out_argmax() const { return reinterpret_cast<int32_t *>(d_out + (size_t)cfg.max_batch * Vpad); }
@@ -244,12 +246,19 @@ int to_host_f32(const void *data, int dtype, size_t n, std::vector<float> &out) 
 
 int check_status(fr_b200_model *m, int st) {
   if (st == 0) return 0;
-  // a bounded wait gave up: the barrier words may be inconsistent, clear them for the next launch
-  cudaMemset(m->d_sync, 0, 8);
+  // a bounded wait gave up: clear the status word for the next launch
   cudaMemset(m->out_status(), 0, 4);
   return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(st) + ")");
 }
 
+}  // namespace
+
+namespace {
+struct DevBuf {
+  void *p = nullptr;
+  ~DevBuf() { if (p) cudaFree(p); }
+  cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 256); }
+};
 }  // namespace
 
 extern "C" {
@@ -304,7 +313,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
     return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the shift-state stash");
   }
   plan(m);
-  m->layer_stride = m->v5 ? v5_layer_bytes(m->C, m->H, cfg->act_fp16) : v4_layer_bytes(m->C, cfg->act_fp16);
+  m->layer_stride = layer_bytes(m->C, m->H, m->v5, cfg->act_fp16);
   m->state_stride = align256(m->layer_stride * m->L);
   const int B = cfg->max_batch;
   auto alloc = [&](void **p, size_t bytes) -> int {
@@ -318,13 +327,12 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_rscale, m->rscale_n * 2);
   if (!rc) rc = alloc((void **)&m->d_vecs, m->vecs_n * 4);
   if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
-  if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * 4);
-  if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * 4);
-  if (!rc) rc = alloc((void **)&m->d_kk, (size_t)B * m->F * 4);
-  if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * 4);
-  if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * 4);
+  if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * 8);
+  if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * 8);
+  if (!rc) rc = alloc((void **)&m->d_kk, (size_t)B * m->F * 8);
+  if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * 8);
+  if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * 8);
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
-  if (!rc) rc = alloc((void **)&m->d_sync, 8);
   if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
   if (!rc) rc = alloc((void **)&m->d_phases, sizeof(PhaseDev) * m->phases.size());
   if (!rc && cudaMallocHost((void **)&m->h_out, m->out_bytes()) != cudaSuccess) rc = fail(FR_B200_E_NOMEM, "cudaMallocHost failed");
@@ -332,7 +340,10 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   cudaMemset(m->d_weights, 0, m->weights_bytes);
   cudaMemset(m->d_rscale, 0, m->rscale_n * 2);
   cudaMemset(m->d_out, 0, m->out_bytes());
-  cudaMemset(m->d_sync, 0, 8);
+  // tag 0 is never expected by a reader
+  cudaMemset(m->d_x, 0, (size_t)B * m->C * 8); cudaMemset(m->d_rwkv, 0, (size_t)B * m->C * 8);
+  cudaMemset(m->d_kk, 0, (size_t)B * m->F * 8); cudaMemset(m->d_rr, 0, (size_t)B * m->C * 8);
+  cudaMemset(m->d_v5buf, 0, (size_t)5 * B * m->C * 8);
   m->emb_rows_set.assign(m->V, 0);
   *out = m;
   return FR_B200_OK;
@@ -343,7 +354,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   cudaSetDevice(m->device);
   free_scratch(m);
   void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_rwkv, m->d_kk, m->d_rr,
-                  m->d_v5buf, m->d_out, m->d_sync, m->d_layers, m->d_phases};
+                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases};
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);
@@ -437,8 +448,9 @@ int fr_b200_finalize(fr_b200_model *m) {
   // kernel geometry: as many ring stages as shared memory allows (capped), one CTA per SM
   int optin = 0;
   CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
-  int want = 8;
+  int want = MAX_STAGES;
   if (const char *e = getenv("FR_B200_STAGES")) want = atoi(e);
+  if (const char *e = getenv("FR_B200_L2_PREFETCH_KB")) m->l2_prefetch = atoi(e) * 1024;
   if (want < 2) want = 2;
   if (want > MAX_STAGES) want = MAX_STAGES;
   const int ver = m->v5 ? 5 : 4;
@@ -472,7 +484,7 @@ int fr_b200_finalize(fr_b200_model *m) {
 }
 
 static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t *ids_dev, int batch, cudaStream_t st,
-                       bool want_argmax) {
+                       bool want_argmax, unsigned long long *prof = nullptr) {
   DecodeParams p;
   memset(&p, 0, sizeof(p));
   p.version = m->cfg.version == FR_B200_V4 ? 4 : m->cfg.version;
@@ -493,12 +505,22 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t 
   p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
   p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
   p.x = m->d_x; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
+  p.seq_base = m->seq;
+  p.par_mask = 0;
+  for (int b = 0; b < batch; ++b) {
+    if (m->par[b] != m->par[0]) return fail(FR_B200_E_STATE, "streams decoded together must have seen the same number of tokens since their last reset");
+    p.par_mask |= m->par[b] << b;
+  }
   const size_t bc = (size_t)m->cfg.max_batch * m->C;
   p.k5 = m->d_v5buf; p.v5 = p.k5 + bc; p.r5 = p.v5 + bc; p.g5 = p.r5 + bc; p.o5 = p.g5 + bc;
   p.state = m->d_state; p.state_stride = m->state_stride; p.layer_stride = m->layer_stride;
-  p.sync = m->d_sync; p.status = m->out_status();
+  p.status = m->out_status();
+  p.prof = prof;
+  p.l2_prefetch_bytes = m->l2_prefetch;
   CU(launch_decode(p, mode, m->grid, smem, st));
   m->launches++;
+  m->seq += (unsigned)m->phases.size();
+  for (int b = 0; b < batch; ++b) m->par[b] ^= 1u;
   if (want_argmax) {
     CU(launch_argmax(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), st));
     m->launches++;
@@ -567,6 +589,25 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
   return FR_B200_OK;
 }
 
+int fr_b200_decode_profile(fr_b200_model *m, const int32_t *ids, int batch, uint64_t *stamps, int n_stamps) {
+  if (!m || !ids || !stamps) return fail(FR_B200_E_ARG, "null argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  if (batch < 1 || batch > m->cfg.max_batch) return fail(FR_B200_E_ARG, "batch must be 1..max_batch");
+  const int need = (int)m->phases.size() * 8 * m->grid;
+  if (n_stamps < need) return fail(FR_B200_E_ARG, "stamps must hold 8 * n_phases * n_ctas entries");
+  CU(cudaSetDevice(m->device));
+  DevBuf buf;
+  CU(buf.alloc((size_t)need * 8));
+  CU(cudaMemset(buf.p, 0, (size_t)need * 8));
+  int rc = decode_impl(m, ids, nullptr, batch, 0, false, (unsigned long long *)buf.p);
+  if (rc) return rc;
+  CU(cudaDeviceSynchronize());
+  CU(cudaMemcpy(stamps, buf.p, (size_t)need * 8, cudaMemcpyDeviceToHost));
+  int status = 0;
+  CU(cudaMemcpy(&status, m->out_status(), 4, cudaMemcpyDeviceToHost));
+  return check_status(m, status);
+}
+
 int fr_b200_logits_device(fr_b200_model *m, float **ptr) {
   if (!m || !ptr) return fail(FR_B200_E_ARG, "null argument");
   *ptr = m->d_out;
@@ -594,26 +635,46 @@ int fr_b200_run_seq(fr_b200_model *m, int slot, const int32_t *ids, int n, float
 // ---- state ---------------------------------------------------------------------------------------
 
 int fr_b200_state_count(const fr_b200_model *m) { return m ? (m->v5 ? 3 : 5) : FR_B200_E_ARG; }
-size_t fr_b200_state_bytes(const fr_b200_model *m) { return m ? m->layer_stride * m->L : 0; }
 
 int fr_b200_state_tensor(fr_b200_model *m, int slot, int layer, int index, void **dev_ptr, int *dtype, int64_t *numel) {
   if (!m) return fail(FR_B200_E_ARG, "null model");
   if (slot < 0 || slot >= m->cfg.max_batch || layer < 0 || layer >= m->L || index < 0 || index >= fr_b200_state_count(m))
     return fail(FR_B200_E_ARG, "state index out of range");
-  const size_t ab = act_bytes(m->cfg.act_fp16), C = m->C;
+  const int af = m->cfg.act_fp16, C = m->C, par = (int)m->par[slot];
   uint8_t *base = m->d_state + (size_t)slot * m->state_stride + (size_t)layer * m->layer_stride;
-  size_t off = 0; int64_t n = C; int dt = m->cfg.act_fp16 ? FR_B200_T_F16 : FR_B200_T_F32;
-  if (!m->v5) {
-    if (index >= 1 && index <= 3) { off = C * ab + (size_t)(index - 1) * C * 4; dt = FR_B200_T_F32; }
-    else if (index == 4) off = C * ab + 3 * C * 4;
-  } else {
-    if (index == 1) { off = C * ab; n = (int64_t)m->H * 4096; dt = FR_B200_T_F32; }
-    else if (index == 2) off = C * ab + (size_t)m->H * 4096 * 4;
-  }
+  size_t off = 0; int64_t n = C; int dt = af ? FR_B200_T_F16 : FR_B200_T_F32;
+  const int last = m->v5 ? 2 : 4;
+  if (index == 0) off = off_sx(C, af, par);
+  else if (index == last) off = off_ffn_sx(C, m->H, m->v5, af, par);
+  else if (m->v5) { off = off_mid(C, af); n = (int64_t)m->H * 4096; dt = FR_B200_T_F32; }
+  else { off = off_mid(C, af) + (size_t)(index - 1) * C * 4; dt = FR_B200_T_F32; }
   if (dev_ptr) *dev_ptr = base + off;
   if (dtype) *dtype = dt;
   if (numel) *numel = n;
   return FR_B200_OK;
+}
+
+// logical state of one slot = the reference's tensors back to back (sx, aa, bb, pp, ffn_sx per layer, or
+// sx, s, ffn_sx), taken from / written to the copy of the token-shift states the next token will read
+static int state_copy(fr_b200_model *m, int slot, uint8_t *ext, bool to_ext) {
+  const int cnt = fr_b200_state_count(m);
+  size_t pos = 0;
+  for (int l = 0; l < m->L; ++l)
+    for (int i = 0; i < cnt; ++i) {
+      void *ptr; int dt; int64_t n;
+      int rc = fr_b200_state_tensor(m, slot, l, i, &ptr, &dt, &n);
+      if (rc) return rc;
+      const size_t bytes = (size_t)n * (dt == FR_B200_T_F16 ? 2 : 4);
+      if (to_ext) CU(cudaMemcpy(ext + pos, ptr, bytes, cudaMemcpyDefault));
+      else CU(cudaMemcpy(ptr, ext + pos, bytes, cudaMemcpyDefault));
+      pos += bytes;
+    }
+  return FR_B200_OK;
+}
+
+size_t fr_b200_state_bytes(const fr_b200_model *m) {
+  if (!m) return 0;
+  return (size_t)m->L * (2 * (size_t)m->C * act_bytes(m->cfg.act_fp16) + mid_bytes(m->C, m->H, m->v5));
 }
 
 int fr_b200_state_reset(fr_b200_model *m, int slot) {
@@ -625,12 +686,15 @@ int fr_b200_state_reset(fr_b200_model *m, int slot) {
   if (!m->v5) {
     // pp = -1e30 (model.cpp:157-158)
     for (int l = 0; l < m->L; ++l) {
-      float *pp = reinterpret_cast<float *>(h.data() + (size_t)l * m->layer_stride + (size_t)m->C * act_bytes(m->cfg.act_fp16) + 2 * (size_t)m->C * 4);
+      float *pp = reinterpret_cast<float *>(h.data() + (size_t)l * m->layer_stride + off_mid(m->C, m->cfg.act_fp16) + 2 * (size_t)m->C * 4);
       for (int i = 0; i < m->C; ++i) pp[i] = -1e30f;
     }
   }
   for (int s = 0; s < m->cfg.max_batch; ++s)
-    if (slot < 0 || slot == s) CU(cudaMemcpy(m->d_state + (size_t)s * m->state_stride, h.data(), per, cudaMemcpyHostToDevice));
+    if (slot < 0 || slot == s) {
+      CU(cudaMemcpy(m->d_state + (size_t)s * m->state_stride, h.data(), per, cudaMemcpyHostToDevice));
+      m->par[s] = 0;
+    }
   return FR_B200_OK;
 }
 
@@ -639,8 +703,8 @@ int fr_b200_state_export(fr_b200_model *m, int slot, void *dst, size_t dst_bytes
   if (slot < 0 || slot >= m->cfg.max_batch) return fail(FR_B200_E_ARG, "slot out of range");
   if (dst_bytes < fr_b200_state_bytes(m)) return fail(FR_B200_E_ARG, "destination too small");
   CU(cudaSetDevice(m->device));
-  CU(cudaMemcpy(dst, m->d_state + (size_t)slot * m->state_stride, fr_b200_state_bytes(m), cudaMemcpyDefault));
-  return FR_B200_OK;
+  CU(cudaDeviceSynchronize());
+  return state_copy(m, slot, static_cast<uint8_t *>(dst), true);
 }
 
 int fr_b200_state_import(fr_b200_model *m, int slot, const void *src, size_t src_bytes) {
@@ -648,19 +712,11 @@ int fr_b200_state_import(fr_b200_model *m, int slot, const void *src, size_t src
   if (slot < 0 || slot >= m->cfg.max_batch) return fail(FR_B200_E_ARG, "slot out of range");
   if (src_bytes != fr_b200_state_bytes(m)) return fail(FR_B200_E_ARG, "state size mismatch");
   CU(cudaSetDevice(m->device));
-  CU(cudaMemcpy(m->d_state + (size_t)slot * m->state_stride, src, src_bytes, cudaMemcpyDefault));
-  return FR_B200_OK;
+  CU(cudaDeviceSynchronize());
+  return state_copy(m, slot, const_cast<uint8_t *>(static_cast<const uint8_t *>(src)), false);
 }
 
 // ---- quantisers -----------------------------------------------------------------------------------
-
-namespace {
-struct DevBuf {
-  void *p = nullptr;
-  ~DevBuf() { if (p) cudaFree(p); }
-  cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 256); }
-};
-}  // namespace
 
 int fr_b200_quantize_int8(const float *W, int K, int N, int8_t *q, uint16_t *scales, int device) {
   if (!W || !q || !scales || K <= 0 || N <= 0) return fail(FR_B200_E_ARG, "bad argument");
@@ -730,12 +786,11 @@ int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float 
   CU(cudaSetDevice(device));
   const int fmt = weight_format, Npad = (N + ROWS - 1) / ROWS * ROWS, nb = Npad / ROWS;
   const size_t rb = rowblock_bytes(fmt, K), n = (size_t)K * N;
-  DevBuf dW, dW16, dq, ds, dt, drs, dx, dy, dsync, dph;
+  DevBuf dW, dW16, dq, ds, dt, drs, dx, dy, dph;
   CU(dW.alloc(n * 4)); CU(dt.alloc(rb * nb)); CU(drs.alloc((size_t)Npad * 2)); CU(dx.alloc((size_t)batch * K * 4));
-  CU(dy.alloc(((size_t)batch * Npad + 1) * 4)); CU(dsync.alloc(8)); CU(dph.alloc(sizeof(PhaseDev)));
+  CU(dy.alloc(((size_t)batch * Npad + 1) * 4)); CU(dph.alloc(sizeof(PhaseDev)));
   CU(cudaMemcpy(dW.p, W, n * 4, cudaMemcpyDefault));
   CU(cudaMemcpy(dx.p, x, (size_t)batch * K * 4, cudaMemcpyDefault));
-  CU(cudaMemset(dsync.p, 0, 8));
   CU(cudaMemset(dy.p, 0, ((size_t)batch * Npad + 1) * 4));
   CU(cudaMemset(drs.p, 0, (size_t)Npad * 2));
   if (fmt == FMT_FP16) {
@@ -759,8 +814,8 @@ int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float 
   memset(&p, 0, sizeof(p));
   // C only sizes the operand space, max(3*C, F) * batch halfs
   p.version = 4; p.L = 0; p.C = 64; p.F = K; p.V = N; p.Vpad = Npad; p.fmt = fmt; p.B = batch; p.n_phases = 1;
-  p.phases = (const PhaseDev *)dph.p; p.kk = (float *)dx.p; p.logits = (float *)dy.p;
-  p.sync = (unsigned *)dsync.p; p.status = (int *)((float *)dy.p + (size_t)batch * Npad);
+  p.phases = (const PhaseDev *)dph.p; p.kk = (exch_t *)dx.p; p.logits = (float *)dy.p;   // PH_MATVEC reads kk as plain fp32
+  p.status = (int *)((float *)dy.p + (size_t)batch * Npad);
   const int mode = decode_mode(batch);
   int optin = 0, grid = 0;
   CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));

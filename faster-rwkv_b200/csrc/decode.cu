@@ -1,11 +1,10 @@
 // Persistent whole-token decode kernel for sm_100a.
 //
-// One cooperative launch runs a whole token (all layers + head) for up to 8 independent streams.
-// grid = one CTA per SM.  Each CTA has one producer warp and NW consumer warps:
+// One cooperative launch (all CTAs co-resident, one per SM) runs a whole token — all layers and the
+// head — for up to 8 independent streams.  Each CTA has one producer warp and NW consumer warps:
 //   * the producer walks the CTA's static list of weight tiles (a function of phase index and CTA id
 //     only) and keeps a ring of shared-memory stages full with 1-D TMA bulk copies; weights do not
-//     depend on activations, so it runs ahead across phase boundaries and HBM stays busy while the
-//     consumers sit in a grid barrier;
+//     depend on activations, so it runs ahead across phase boundaries;
 //   * the consumers stage the phase's input vectors in shared memory as fp16 tensor-core operands
 //     (LayerNorm + token-shift mix fused here), then for every 16-row block multiply the streamed
 //     tile with mma.sync.m16n8k16 (weights = A operand, streams = B operand columns, fp32
@@ -14,8 +13,13 @@
 //     Each activation is fed as two fp16 columns, hi = fp16(x) and lo = fp16(x - hi), whose results
 //     are added: the operand keeps ~22 mantissa bits at no extra MMA for one stream (7 of the 8
 //     columns are idle anyway) and 4 streams share one MMA.
-// Phases are separated by a grid barrier (release/acquire counter in global memory).  Every wait
-// is bounded: after WAIT_LIMIT_NS it records a status and the CTA drains without hanging.
+//
+// Phases are not separated by barriers.  Every value one phase hands to the next across CTAs is a
+// 64-bit word {fp32 value, sequence number of the writing phase}; a reader polls the words it needs
+// until they carry the expected number.  Because each phase needs all outputs of the one before it,
+// a CTA can only overwrite a vector after every reader of its previous contents has moved on; a CTA
+// that owns no row block in a phase skips the phase.  The token-shift states are double-buffered for
+// the same reason.  Every wait is bounded: after WAIT_LIMIT_NS the CTA records a status and drains.
 #include "common.cuh"
 #include "internal.h"
 
@@ -29,13 +33,10 @@ struct Smem {
   uint64_t *full, *empty;
   volatile int *abort_flag;
   float *ln_red;     // [NW][2*MAX_B]
-  float *stats;      // [2*MAX_B] mean, rstd
-  float *stash;      // [MAX_B][STASH_N] LayerNorm outputs of the channels whose shift state this CTA writes
-  float *red;        // [2][3][NW][RED_N]
+  float *red;        // [3][NW][RED_N] per-warp partial sums of the current row block
   __half *xs;        // operand vectors
   uint8_t *ring;
 };
-constexpr int STASH_N = 128;
 
 // NB = operand columns kept per n-tile (2: one stream as hi/lo; 8: four streams as hi/lo), NT = n-tiles.
 template <int NB, int NT> __host__ __device__ constexpr int n_streams() { return NB == 2 ? 1 : 4 * NT; }
@@ -44,15 +45,14 @@ template <int NB, int NT> __host__ __device__ constexpr int red_n() { return ROW
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 template <int NB, int NT>
-__host__ __device__ inline size_t smem_layout(size_t xs_halfs, int n_stages, size_t *off_stash, size_t *off_red,
-                                              size_t *off_xs, size_t *off_ring) {
+__host__ __device__ inline size_t smem_layout(int fmt, size_t xs_halfs, int n_stages, size_t *off_red, size_t *off_xs,
+                                              size_t *off_ring) {
   size_t o = 1024;  // barriers + flags + LN scratch
-  *off_stash = o; o += sizeof(float) * n_streams<NB, NT>() * STASH_N;
-  *off_red = o;   o += sizeof(float) * 2 * 3 * NW * red_n<NB, NT>();
+  *off_red = o;   o += sizeof(float) * 3 * NW * red_n<NB, NT>();
   o = align_up(o, 128);
   *off_xs = o;    o += xs_halfs * 2;
   o = align_up(o, 1024);
-  *off_ring = o;  o += (size_t)n_stages * SLOT_BYTES;
+  *off_ring = o;  o += (size_t)n_stages * slot_bytes(fmt);
   return o;
 }
 
@@ -165,58 +165,85 @@ struct Ctx {
   int tid, warp, lane, cta, G;
   int slot;            // ring position of the next stage
   uint32_t parity;     // parity of the next full-barrier wait
-  unsigned epoch;      // grid barriers passed
-  int own0, ownn;      // channels whose shift state this CTA writes
-  uint8_t *stash_dst;  // pending shift-state write (per-stream base + b*state_stride), or null
+  uint32_t slot_b;     // bytes per ring slot
+  int prof_phase;
+  unsigned long long wait_ns;  // profiling: time thread 0 spent waiting for weight tiles in the current phase
 };
 
 __device__ __forceinline__ int token_id(const DecodeParams &p, int b) {
   return p.ids_dev ? __ldcg(p.ids_dev + b) : p.ids_val[b];
 }
+__device__ __forceinline__ unsigned phase_tag(const DecodeParams &p, int pi) { return p.seq_base + (unsigned)pi + 1u; }
 
-__device__ __forceinline__ void grid_barrier(Ctx &cx) {
-  const DecodeParams &p = *cx.p;
-  bar_sync(BAR_CONS, NCONS);
-  if (cx.tid == 0) {
-    cx.epoch++;
-    __threadfence();
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
-    const unsigned target = cx.epoch * (unsigned)cx.G;
-    unsigned v;
-    unsigned long long t0 = 0;
-    int it = 0;
-    while (true) {
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sync) : "memory");
-      if ((int)(v - target) >= 0) break;
-      if (*cx.sm.abort_flag) break;
-      if ((++it & 1023) == 0) {
-        if (t0 == 0) t0 = globaltimer_ns();
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS || __ldcg(p.status) != 0) {
-          *cx.sm.abort_flag = 1;
-          atomicCAS(p.status, 0, ST_TIMEOUT_GRID);
-          break;
-        }
-      }
-    }
-    __threadfence();
-  }
-  bar_sync(BAR_CONS, NCONS);
+// ---- tagged exchange words ----------------------------------------------------------------------
+__device__ __forceinline__ void ex_store(exch_t *dst, float v, unsigned tag) {
+  const exch_t w = ((exch_t)tag << 32) | (exch_t)__float_as_uint(v);
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+}
+__device__ __forceinline__ exch_t ex_load_raw(const exch_t *src) {
+  exch_t w;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+  return w;
+}
+// one word; false while the writer has not stored it yet
+__device__ __forceinline__ bool ex_try1(const exch_t *src, unsigned tag, float &v) {
+  const exch_t w = ex_load_raw(src);
+  v = __uint_as_float((unsigned)w);
+  return (unsigned)(w >> 32) == tag;
+}
+// four consecutive words (32-byte aligned)
+__device__ __forceinline__ bool ex_try4(const exch_t *src, unsigned tag, float4 &v) {
+  exch_t a, b, c, d;
+  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(c), "=l"(d) : "l"(src + 2) : "memory");
+  v = make_float4(__uint_as_float((unsigned)a), __uint_as_float((unsigned)b), __uint_as_float((unsigned)c),
+                  __uint_as_float((unsigned)d));
+  return (unsigned)(a >> 32) == tag && (unsigned)(b >> 32) == tag && (unsigned)(c >> 32) == tag &&
+         (unsigned)(d >> 32) == tag;
 }
 
-// write the stashed LayerNorm outputs into the token-shift state (after the barrier that follows
-// the phase which read the old state)
-__device__ __forceinline__ void flush_stash(Ctx &cx) {
-  if (!cx.stash_dst) return;
-  const DecodeParams &p = *cx.p;
-  const int n = cx.ownn * p.B;
-  for (int t = cx.tid; t < n; t += NCONS) {
-    const int b = t / cx.ownn, i = t - b * cx.ownn;
-    const float v = cx.sm.stash[b * STASH_N + i];
-    uint8_t *dst = cx.stash_dst + (size_t)b * p.state_stride;
-    if (p.act_fp16) reinterpret_cast<__half *>(dst)[cx.own0 + i] = __float2half_rn(v);
-    else reinterpret_cast<float *>(dst)[cx.own0 + i] = v;
+// Bounded polling: gives up after WAIT_LIMIT_NS (or as soon as another thread of the CTA gave up).
+struct Poll {
+  unsigned long long t0;
+  int it;
+  __device__ __forceinline__ Poll() : t0(0), it(0) {}
+  __device__ __forceinline__ bool keep_waiting(Ctx &cx) {
+    if ((++it & 63) != 0) return true;
+    if (*cx.sm.abort_flag) return false;
+    const unsigned long long now = globaltimer_ns();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > WAIT_LIMIT_NS || __ldcg(cx.p->status) != 0) {
+      *cx.sm.abort_flag = 1;
+      atomicCAS(cx.p->status, 0, ST_TIMEOUT_DATA);
+      return false;
+    }
+    return true;
   }
-  cx.stash_dst = nullptr;
+};
+__device__ __forceinline__ float ex_wait1(Ctx &cx, const exch_t *src, unsigned tag) {
+  float v;
+  Poll poll;
+  while (!ex_try1(src, tag, v) && poll.keep_waiting(cx)) { }
+  return v;
+}
+__device__ __forceinline__ float4 ex_wait4(Ctx &cx, const exch_t *src, unsigned tag) {
+  float4 v;
+  Poll poll;
+  while (!ex_try4(src, tag, v) && poll.keep_waiting(cx)) { }
+  return v;
+}
+
+// Wait until an exchange vector [B][K] written by phase `tag` is (almost certainly) complete, touching as
+// little of it as possible: writers store 16 consecutive words (one row block) with one warp instruction,
+// so polling the first word of every block tells when the block has landed.  The full read that follows
+// still checks every tag.  Keeps 148 CTAs from hammering the whole vector while they wait.
+__device__ __forceinline__ void wait_sentinels(Ctx &cx, const exch_t *src, int K, unsigned tag) {
+  const int per = K / ROWS, n = cx.p->B * per;
+  for (int idx = cx.tid; idx < n; idx += NCONS) {
+    const int b = idx / per, t = idx - b * per;
+    ex_wait1(cx, src + (size_t)b * K + (size_t)t * ROWS, tag);
+  }
+  bar_sync(BAR_CONS, NCONS);
 }
 
 __device__ __forceinline__ float4 load_act4(const uint8_t *base, int i4, int act_fp16) {
@@ -227,6 +254,17 @@ __device__ __forceinline__ float4 load_act4(const uint8_t *base, int i4, int act
     return make_float4(a.x, a.y, b.x, b.y);
   }
   return __ldcg(reinterpret_cast<const float4 *>(base) + i4);
+}
+__device__ __forceinline__ void store_act4(uint8_t *base, int i4, int act_fp16, const float4 &v) {
+  if (act_fp16) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t *>(&lo);
+    u.y = *reinterpret_cast<const uint32_t *>(&hi);
+    reinterpret_cast<uint2 *>(base)[i4] = u;
+  } else {
+    reinterpret_cast<float4 *>(base)[i4] = v;
+  }
 }
 
 // Operand position of stream b inside a vector: n-tile plane and the hi / lo columns.
@@ -253,8 +291,10 @@ __device__ __forceinline__ void store_operand4(__half *vec, size_t plane_halfs, 
   *reinterpret_cast<uint2 *>(pl + xs_index(k, cl, NB)) = u;
 }
 
-// Residual stream column b, float4 index i4: the embedding row at layer 0, else x.
-__device__ __forceinline__ float4 load_x4(const DecodeParams &p, int layer0, int b, int i4) {
+// Residual stream of stream b, elements 4*i4 .. 4*i4+3: the embedding row at layer 0, else the
+// exchange vector x written by phase `tag` (waits for it).
+__device__ __forceinline__ float4 wait_x4(Ctx &cx, bool layer0, int b, int i4, unsigned tag) {
+  const DecodeParams &p = *cx.p;
   if (layer0) {
     if (p.emb_f32)
       return __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * p.C) + i4);
@@ -264,27 +304,163 @@ __device__ __forceinline__ float4 load_x4(const DecodeParams &p, int layer0, int
     const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
     return make_float4(a.x, a.y, c.x, c.y);
   }
-  return __ldcg(reinterpret_cast<const float4 *>(p.x + (size_t)b * p.C) + i4);
+  return ex_wait4(cx, p.x + (size_t)b * p.C + (size_t)i4 * 4, tag);
 }
 
-// LayerNorm statistics of the residual stream for all B columns -> sm.stats (mean[b], rstd[b]).
-// Shifted single pass: sums of (x - x[0]) and (x - x[0])^2 in fp32.
-template <int SB>
-__device__ __forceinline__ void ln_stats(Ctx &cx, int layer0) {
-  constexpr int NB = SB;  // one slot per stream
+constexpr int XR = 2;   // float4 slots per thread that the one-stream LayerNorm keeps in registers
+
+// Element 4*i4.. of the residual stream of stream b without waiting: the embedding row at layer 0
+// (always there), else one attempt at the tagged words.
+__device__ __forceinline__ bool try_x4(const DecodeParams &p, bool layer0, int b, int i4, unsigned tag, float4 &v) {
+  if (layer0) {
+    if (p.emb_f32) {
+      v = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * p.C) + i4);
+    } else {
+      const __half *row = reinterpret_cast<const __half *>(p.emb) + (size_t)token_id(p, b) * p.C;
+      const uint2 u = __ldg(reinterpret_cast<const uint2 *>(row) + i4);
+      const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+      const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+      v = make_float4(a.x, a.y, c.x, c.y);
+    }
+    return true;
+  }
+  return ex_try4(p.x + (size_t)b * p.C + (size_t)i4 * 4, tag, v);
+}
+
+// Normalised value -> operand vectors (token-shift mix) and, on the owning CTA, the new shift state.
+template <int NB, int NT>
+__device__ __forceinline__ void ln_emit(Ctx &cx, const PhaseDev &ph, int nvec, uint8_t *sx_wr, int sx_item0, int i4, int b,
+                                        const float4 &xv, float mean, float rstd, const float4 &gw, const float4 &gb,
+                                        const float4 *mx4, const float4 &sx) {
+  const DecodeParams &p = *cx.p;
+  const size_t plane = (size_t)p.C * NB;   // halfs per (vector, n-tile)
+  const size_t vstride = plane * NT;       // halfs per operand vector
+  float4 xx;
+  xx.x = (xv.x - mean) * rstd * gw.x + gb.x;
+  xx.y = (xv.y - mean) * rstd * gw.y + gb.y;
+  xx.z = (xv.z - mean) * rstd * gw.z + gb.z;
+  xx.w = (xv.w - mean) * rstd * gw.w + gb.w;
+  if (nvec == 0) {
+    store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, xx.x, xx.y, xx.z, xx.w);
+    return;
+  }
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (v < nvec) {
+      const float4 m = mx4[v];
+      store_operand4<NB>(cx.sm.xs + v * vstride, plane, i4 * 4, b, xx.x * m.x + sx.x * (1.f - m.x),
+                         xx.y * m.y + sx.y * (1.f - m.y), xx.z * m.z + sx.z * (1.f - m.z),
+                         xx.w * m.w + sx.w * (1.f - m.w));
+    }
+  }
+  // new token-shift state: written once, by the CTA that owns the row block of these channels
+  if ((sx_item0 + (i4 >> 2) + ph.rot) % cx.G == cx.cta)
+    store_act4(sx_wr + (size_t)b * p.state_stride, i4, p.act_fp16, xx);
+}
+
+// LayerNorm + token-shift mix for ONE stream of a model with n_embd <= 4 * XR * NCONS: the latency-critical
+// prologue of batch-1 decode.  All parameter loads are issued first (they miss L2: the weight stream evicts
+// them every token), then every thread polls its own slots of x plus the pivot element in one go, so a
+// round costs one memory round trip.  Statistics: shifted single pass, sums of (x - x[0]) and (x - x[0])^2.
+// nvec == 0: plain LayerNorm -> operand vector 0 (head).
+template <int NB, int NT>
+__device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, bool layer0, unsigned xtag, const float *ln_w,
+                                                const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
+                                                uint8_t *sx_wr, int sx_item0) {
   const DecodeParams &p = *cx.p;
   const int n4 = p.C >> 2;
-  float s1[NB], s2[NB], piv[NB];
+  // 1. wait cheaply: every thread polls one word of each of its slots (and nothing else) until it is there
+  if (!layer0) {
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
+    for (int r = 0; r < XR; ++r) {
+      const int i4 = cx.tid + r * NCONS;
+      if (i4 < n4) ex_wait1(cx, p.x + (size_t)i4 * 4, xtag);
+    }
+  }
+  // 2. one round trip: x (all tags checked), the pivot element, and the parameters of the same channels
+  float4 gw[XR], gb[XR], mx[4][XR], sx[XR], xv[XR], pv;
+  bool ok = try_x4(p, layer0, 0, 0, xtag, pv);
+#pragma unroll
+  for (int r = 0; r < XR; ++r) {
+    const int i4 = cx.tid + r * NCONS;
+    if (i4 < n4) {
+      ok = try_x4(p, layer0, 0, i4, xtag, xv[r]) && ok;
+      gw[r] = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4);
+      gb[r] = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4);
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        if (v < nvec) mx[v][r] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4);
+      if (nvec > 0) sx[r] = load_act4(sx_rd, i4, p.act_fp16);
+    }
+  }
+  if (!ok) {
+    // a word of a slot lagged behind the one polled above: wait for exactly what is missing
+    pv = wait_x4(cx, layer0, 0, 0, xtag);
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      const int i4 = cx.tid + r * NCONS;
+      if (i4 < n4) xv[r] = wait_x4(cx, layer0, 0, i4, xtag);
+    }
+  }
+  const float piv = pv.x;
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int r = 0; r < XR; ++r) {
+    const int i4 = cx.tid + r * NCONS;
+    if (i4 < n4) {
+      const float d0 = xv[r].x - piv, d1 = xv[r].y - piv, d2 = xv[r].z - piv, d3 = xv[r].w - piv;
+      s1 += (d0 + d1) + (d2 + d3);
+      s2 += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if (cx.lane == 0) { cx.sm.ln_red[cx.warp * 2] = s1; cx.sm.ln_red[cx.warp * 2 + 1] = s2; }
+  bar_sync(BAR_CONS, NCONS);
+  float a = 0.f, c = 0.f;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) { a += cx.sm.ln_red[w * 2]; c += cx.sm.ln_red[w * 2 + 1]; }
+  const float inv = 1.f / (float)p.C;
+  const float m = a * inv;
+  float var = c * inv - m * m;
+  var = var > 0.f ? var : 0.f;
+  const float mean = piv + m, rstd = rsqrtf(var + 1e-5f);
+#pragma unroll
+  for (int r = 0; r < XR; ++r) {
+    const int i4 = cx.tid + r * NCONS;
+    if (i4 < n4) {
+      const float4 mx4[4] = {mx[0][r], mx[1][r], mx[2][r], mx[3][r]};
+      ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4, 0, xv[r], mean, rstd, gw[r], gb[r], mx4, sx[r]);
+    }
+  }
+  bar_sync(BAR_CONS, NCONS);
+}
+
+// LayerNorm + token-shift mix, any number of streams and any width: a statistics pass (which also waits
+// for the data) and a second pass over x.
+template <int NB, int NT>
+__device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, bool layer0, unsigned xtag, const float *ln_w,
+                                             const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
+                                             uint8_t *sx_wr, int sx_item0) {
+  constexpr int SB = n_streams<NB, NT>();
+  const DecodeParams &p = *cx.p;
+  const int n4 = p.C >> 2;
+  const float inv = 1.f / (float)p.C;
+  if (!layer0) wait_sentinels(cx, p.x, p.C, xtag);
+  float s1[SB], s2[SB], piv[SB], mean[SB], rstd[SB];
+#pragma unroll
+  for (int b = 0; b < SB; ++b) {
     s1[b] = s2[b] = 0.f;
-    piv[b] = b < p.B ? load_x4(p, layer0, b, 0).x : 0.f;
+    piv[b] = b < p.B ? wait_x4(cx, layer0, b, 0, xtag).x : 0.f;
   }
   for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < SB; ++b) {
       if (b < p.B) {
-        const float4 v = load_x4(p, layer0, b, i4);
+        const float4 v = wait_x4(cx, layer0, b, i4, xtag);
         const float d0 = v.x - piv[b], d1 = v.y - piv[b], d2 = v.z - piv[b], d3 = v.w - piv[b];
         s1[b] += (d0 + d1) + (d2 + d3);
         s2[b] += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
@@ -292,7 +468,7 @@ __device__ __forceinline__ void ln_stats(Ctx &cx, int layer0) {
     }
   }
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
+  for (int b = 0; b < SB; ++b) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       s1[b] += __shfl_xor_sync(0xffffffffu, s1[b], o);
@@ -301,87 +477,98 @@ __device__ __forceinline__ void ln_stats(Ctx &cx, int layer0) {
   }
   if (cx.lane == 0) {
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < SB; ++b) {
       cx.sm.ln_red[cx.warp * 2 * MAX_B + 2 * b] = s1[b];
       cx.sm.ln_red[cx.warp * 2 * MAX_B + 2 * b + 1] = s2[b];
     }
   }
   bar_sync(BAR_CONS, NCONS);
-  if (cx.tid < NB && cx.tid < p.B) {
-    const int b = cx.tid;
+#pragma unroll
+  for (int b = 0; b < SB; ++b) {
     float a = 0.f, c = 0.f;
+#pragma unroll
     for (int w = 0; w < NW; ++w) {
       a += cx.sm.ln_red[w * 2 * MAX_B + 2 * b];
       c += cx.sm.ln_red[w * 2 * MAX_B + 2 * b + 1];
     }
-    const float inv = 1.f / (float)p.C;
     const float m = a * inv;
     float var = c * inv - m * m;
     var = var > 0.f ? var : 0.f;
-    cx.sm.stats[2 * b] = load_x4(p, layer0, b, 0).x + m;  // same pivot every thread used
-    cx.sm.stats[2 * b + 1] = rsqrtf(var + 1e-5f);
+    mean[b] = piv[b] + m;
+    rstd[b] = rsqrtf(var + 1e-5f);
   }
-  bar_sync(BAR_CONS, NCONS);
-}
-
-// LayerNorm + token-shift mix: writes nvec operand vectors (fp16) into sm.xs, stashes LN output of
-// the owned channels for the deferred shift-state write.  nvec == 0: plain LayerNorm -> xs[0].
-template <int NB, int NT>
-__device__ __forceinline__ void prologue_ln_mix(Ctx &cx, int layer0, const float *ln_w, const float *ln_b,
-                                                const float *const *mix, int nvec, const uint8_t *sx_state) {
-  constexpr int SB = n_streams<NB, NT>();
-  const DecodeParams &p = *cx.p;
-  ln_stats<SB>(cx, layer0);
-  const int n4 = p.C >> 2;
-  const size_t plane = (size_t)p.C * NB;   // halfs per (vector, n-tile)
-  const size_t vstride = plane * NT;       // halfs per operand vector
   for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
+    float4 mx4[4];
     const float4 gw = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4);
     const float4 gb = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4);
-    float4 mx[4];
 #pragma unroll
     for (int v = 0; v < 4; ++v)
-      if (v < nvec) mx[v] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4);
+      if (v < nvec) mx4[v] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4);
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
-      const float mean = cx.sm.stats[2 * b], rstd = cx.sm.stats[2 * b + 1];
-      const float4 xv = load_x4(p, layer0, b, i4);
-      float4 xx;
-      xx.x = (xv.x - mean) * rstd * gw.x + gb.x;
-      xx.y = (xv.y - mean) * rstd * gw.y + gb.y;
-      xx.z = (xv.z - mean) * rstd * gw.z + gb.z;
-      xx.w = (xv.w - mean) * rstd * gw.w + gb.w;
-      if (nvec == 0) {
-        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, xx.x, xx.y, xx.z, xx.w);
-        continue;
-      }
-      const float4 sx = load_act4(sx_state + (size_t)b * p.state_stride, i4, p.act_fp16);
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        if (v < nvec) {
-          const float4 m = mx[v];
-          store_operand4<NB>(cx.sm.xs + v * vstride, plane, i4 * 4, b, xx.x * m.x + sx.x * (1.f - m.x),
-                             xx.y * m.y + sx.y * (1.f - m.y), xx.z * m.z + sx.z * (1.f - m.z),
-                             xx.w * m.w + sx.w * (1.f - m.w));
-        }
-      }
-      const int c = i4 * 4 - cx.own0;
-      if (c > -4 && c < cx.ownn) {
-        float *st = cx.sm.stash + b * STASH_N;
-        if (c >= 0 && c < cx.ownn) st[c] = xx.x;
-        if (c + 1 >= 0 && c + 1 < cx.ownn) st[c + 1] = xx.y;
-        if (c + 2 >= 0 && c + 2 < cx.ownn) st[c + 2] = xx.z;
-        if (c + 3 >= 0 && c + 3 < cx.ownn) st[c + 3] = xx.w;
-      }
+      const float4 xv = wait_x4(cx, layer0, b, i4, xtag);  // already there: the statistics pass waited
+      float4 sx = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (nvec > 0) sx = load_act4(sx_rd + (size_t)b * p.state_stride, i4, p.act_fp16);
+      ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4, b, xv, mean[b], rstd[b], gw, gb, mx4, sx);
     }
   }
   bar_sync(BAR_CONS, NCONS);
 }
 
-// fp32 vector [B][K] in global memory -> operand vector 0
 template <int NB, int NT>
-__device__ __forceinline__ void prologue_vec(Ctx &cx, const float *src, int K) {
+__device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, bool layer0, unsigned xtag, const float *ln_w,
+                                            const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
+                                            uint8_t *sx_wr, int sx_item0) {
+  if (n_streams<NB, NT>() == 1 && (cx.p->C >> 2) <= XR * NCONS)
+    prologue_ln_one<NB, NT>(cx, ph, layer0, xtag, ln_w, ln_b, mix, nvec, sx_rd, sx_wr, sx_item0);
+  else
+    prologue_ln_mix<NB, NT>(cx, ph, layer0, xtag, ln_w, ln_b, mix, nvec, sx_rd, sx_wr, sx_item0);
+}
+
+// exchange vector [B][K] written by phase `tag` -> operand vector 0.  Short vectors are polled directly,
+// every thread issuing the loads of all its slots before it looks at a tag; long ones wait on the block
+// sentinels first so that the waiting CTAs do not sweep 64 KB each per round.
+template <int NB, int NT>
+__device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, unsigned tag) {
+  constexpr int SB = n_streams<NB, NT>();
+  constexpr int VR = 4;   // slots polled together
+  const DecodeParams &p = *cx.p;
+  const int n4 = K >> 2;
+  const size_t plane = (size_t)K * NB;
+  if ((long long)n4 * p.B > (long long)VR * NCONS) wait_sentinels(cx, src, K, tag);
+  const int total = n4 * p.B;   // slot index s -> stream s / n4, float4 s % n4
+  for (int base = cx.tid; base < total; base += VR * NCONS) {
+    float4 v[VR];
+    Poll poll;
+    bool ok;
+    do {
+      ok = true;
+#pragma unroll
+      for (int r = 0; r < VR; ++r) {
+        const int s = base + r * NCONS;
+        if (s < total) {
+          const int b = s / n4, i4 = s - b * n4;
+          ok = ex_try4(src + (size_t)b * K + (size_t)i4 * 4, tag, v[r]) && ok;
+        }
+      }
+    } while (!ok && poll.keep_waiting(cx));
+#pragma unroll
+    for (int r = 0; r < VR; ++r) {
+      const int s = base + r * NCONS;
+      if (s < total) {
+        const int b = s / n4, i4 = s - b * n4;
+        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v[r].x, v[r].y, v[r].z, v[r].w);
+      }
+    }
+  }
+  bar_sync(BAR_CONS, NCONS);
+  (void)SB;
+}
+
+// plain fp32 vector [B][K] (stand-alone matvec) -> operand vector 0
+template <int NB, int NT>
+__device__ __forceinline__ void prologue_plain(Ctx &cx, const float *src, int K) {
   constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
   const int n4 = K >> 2;
@@ -399,18 +586,20 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const float *src, int K) {
 
 // v5 output projection input: GroupNorm over each head's 64 readout values, times the gate
 template <int NB, int NT>
-__device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly) {
+__device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly, unsigned otag, unsigned gtag) {
   constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
   const size_t plane = (size_t)p.C * NB;
   const int n4 = p.C >> 2;  // 16 float4 per head -> 16 consecutive threads share a head
+  wait_sentinels(cx, p.o5, p.C, otag);
   for (int base = 0; base < n4; base += NCONS) {
     const int i4 = base + cx.tid;
     const bool ok = i4 < n4;
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
-      float4 v = ok ? __ldcg(reinterpret_cast<const float4 *>(p.o5 + (size_t)b * p.C) + i4) : make_float4(0, 0, 0, 0);
+      float4 v = make_float4(0, 0, 0, 0);
+      if (ok) v = ex_wait4(cx, p.o5 + (size_t)b * p.C + (size_t)i4 * 4, otag);
       float s = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -426,7 +615,7 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly) {
         float4 y = make_float4(d0 * rstd * gw.x + gb.x, d1 * rstd * gw.y + gb.y, d2 * rstd * gw.z + gb.z,
                                d3 * rstd * gw.w + gb.w);
         if (p.version >= 51) {
-          const float4 g = __ldcg(reinterpret_cast<const float4 *>(p.g5 + (size_t)b * p.C) + i4);
+          const float4 g = ex_wait4(cx, p.g5 + (size_t)b * p.C + (size_t)i4 * 4, gtag);
           y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w;
         }
         store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, y.x, y.y, y.z, y.w);
@@ -436,26 +625,71 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly) {
   bar_sync(BAR_CONS, NCONS);
 }
 
+// ---- epilogue of one (row, stream) output --------------------------------------------------------
+// Values the epilogue needs from global memory; requested when the row block starts so that their
+// latency hides behind the wait for the weight tiles.
+struct EpiIn {
+  float a, b, c, d, e;
+  float rscale[3];
+};
+
+template <int FMT>
+__device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, const LayerDev *ly, int pi, int it, int row,
+                                                  int b, EpiIn &in) {
+  const DecodeParams &p = *cx.p;
+  const int C = p.C;
+  if (FMT == FMT_INT8) {
+#pragma unroll
+    for (int u = 0; u < 3; ++u)
+      if (u < ph.n_sub) in.rscale[u] = __half2float(__ldg(ph.rscale + ((size_t)it * ph.n_sub + u) * ROWS + row));
+  }
+  switch (ph.kind) {
+    case PH_ATT_KVR: {
+      const int c = it * ROWS + row;
+      const uint8_t *st = p.state + (size_t)b * p.state_stride + (size_t)ph.layer * p.layer_stride;
+      const float *aa = reinterpret_cast<const float *>(st + off_mid(C, p.act_fp16));
+      in.a = aa[c]; in.b = aa[C + c]; in.c = aa[2 * C + c];
+      in.d = __ldg(ly->first + c); in.e = __ldg(ly->decay + c);
+      break;
+    }
+    case PH_ATT_O: {
+      // residual input: the embedding row at layer 0, else x as the previous layer's ffn value phase left it
+      const int c = it * ROWS + row;
+      if (ph.layer == 0)
+        in.a = p.emb_f32 ? __ldg(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * C + c)
+                         : __half2float(reinterpret_cast<const __half *>(p.emb)[(size_t)token_id(p, b) * C + c]);
+      else in.a = ex_wait1(cx, p.x + (size_t)b * C + c, phase_tag(p, pi - (p.version == 4 ? 2 : 3)));
+      break;
+    }
+    case PH_FFN_V: {
+      const int c = it * ROWS + row;
+      in.a = ex_wait1(cx, p.x + (size_t)b * C + c, phase_tag(p, pi - 2));   // written by the output projection
+      in.b = ex_wait1(cx, p.rr + (size_t)b * C + c, phase_tag(p, pi - 1));  // written by the ffn receptance rows
+      break;
+    }
+    default: break;
+  }
+}
+
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
-// ---- epilogue of one (row, stream) output --------------------------------------------------------
-__device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &ph, const LayerDev *ly, int it,
-                                         int row, int b, const float val[3]) {
+__device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &ph, unsigned tag, int it, int row, int b,
+                                         const float val[3], const EpiIn &in) {
   const int C = p.C;
   switch (ph.kind) {
     case PH_ATT_KVR: {
       const int c = it * ROWS + row;
       uint8_t *st = p.state + (size_t)b * p.state_stride + (size_t)ph.layer * p.layer_stride;
-      float *aa = reinterpret_cast<float *>(st + (size_t)C * act_bytes(p.act_fp16));
+      float *aa = reinterpret_cast<float *>(st + off_mid(C, p.act_fp16));
       float *bb = aa + C, *pp = bb + C;
       const float k = val[0], v = val[1], r = sigmoid_f(val[2]);
-      const float u = __ldg(ly->first + c), w = __ldg(ly->decay + c);
-      const float a0 = aa[c], b0 = bb[c], p0 = pp[c];
+      const float u = in.d, w = in.e;
+      const float a0 = in.a, b0 = in.b, p0 = in.c;
       float ww = u + k;
       float pm = fmaxf(p0, ww);
       float e1 = expf(p0 - pm), e2 = expf(ww - pm);
       const float wkv = (e1 * a0 + e2 * v) / (e1 * b0 + e2);
-      p.rwkv[(size_t)b * C + c] = r * wkv;
+      ex_store(p.rwkv + (size_t)b * C + c, r * wkv, tag);
       ww = w + p0;
       pm = fmaxf(ww, k);
       e1 = expf(ww - pm);
@@ -467,30 +701,25 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
     }
     case PH_ATT_O: {
       const int c = it * ROWS + row;
-      float xin;
-      if (ph.layer == 0)
-        xin = p.emb_f32 ? __ldg(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * C + c)
-                        : __half2float(reinterpret_cast<const __half *>(p.emb)[(size_t)token_id(p, b) * C + c]);
-      else xin = __ldcg(p.x + (size_t)b * C + c);
-      p.x[(size_t)b * C + c] = xin + val[0];
+      ex_store(p.x + (size_t)b * C + c, in.a + val[0], tag);
       break;
     }
     case PH_FFN_KR: {
       if (it < ph.split[0]) {
         const int f = it * ROWS + row;
         const float t = fmaxf(val[0], 0.f);
-        p.kk[(size_t)b * p.F + f] = t * t;
+        ex_store(p.kk + (size_t)b * p.F + f, t * t, tag);
       } else {
         const int c = (it - ph.split[0]) * ROWS + row;
-        p.rr[(size_t)b * C + c] = sigmoid_f(val[0]);
+        ex_store(p.rr + (size_t)b * C + c, sigmoid_f(val[0]), tag);
       }
       break;
     }
     case PH_FFN_V: {
       const int c = it * ROWS + row;
-      float xn = __ldcg(p.x + (size_t)b * C + c) + __ldcg(p.rr + (size_t)b * C + c) * val[0];
+      float xn = in.a + in.b * val[0];
       if (p.rescale_every > 0 && (ph.layer + 1) % p.rescale_every == 0) xn *= 0.5f;
-      p.x[(size_t)b * C + c] = xn;
+      ex_store(p.x + (size_t)b * C + c, xn, tag);
       break;
     }
     case PH_MATVEC:
@@ -502,10 +731,10 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
     case PH5_KVRG: {
       const int nb = C / ROWS;
       const int cls = it / nb, c = (it - cls * nb) * ROWS + row;
-      float *dst = cls == 0 ? p.k5 : cls == 1 ? p.v5 : cls == 2 ? p.r5 : p.g5;
+      exch_t *dst = cls == 0 ? p.k5 : cls == 1 ? p.v5 : cls == 2 ? p.r5 : p.g5;
       float v = val[0];
       if (cls == 3) v = v * sigmoid_f(v);
-      dst[(size_t)b * C + c] = v;
+      ex_store(dst + (size_t)b * C + c, v, tag);
       break;
     }
     default: break;
@@ -514,7 +743,7 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
 
 // ---- all row blocks of a phase that belong to this CTA ----------------------------------------------
 template <int FMT, int NB, int NT>
-__device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const LayerDev *ly) {
+__device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const LayerDev *ly, int pi, int first) {
   constexpr int SB = n_streams<NB, NT>();
   constexpr int RN = red_n<NB, NT>();
   const DecodeParams &p = *cx.p;
@@ -522,105 +751,113 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
   const int nst = num_stages(FMT, ph.K);
   const size_t plane = (size_t)ph.K * NB;   // halfs per (vector, n-tile)
   const size_t vstride = plane * NT;
-  int buf = 0;
-  const int first = (cx.cta + cx.G - ph.rot) % cx.G;
+  const unsigned tag = phase_tag(p, pi);
+  const int g = cx.lane >> 2, q = cx.lane & 3;
+  const int erow = cx.tid / SB, eb = cx.tid % SB;
+  const bool epi_thread = cx.tid < ROWS * SB && eb < p.B;
+  const bool prof = p.prof != nullptr && cx.tid == 0;
+  long long c_st = 0, c_bar = 0, c_epi = 0, c_n = 0;
   for (int it = first; it < ph.n_items; it += cx.G) {
-    float acc[3][2][NT][4];
-#pragma unroll
-    for (int u = 0; u < 3; ++u)
+    const long long ck0 = prof ? clock64() : 0;
+    EpiIn epi_in;
+    if (epi_thread) epilogue_prefetch<FMT>(cx, ph, ly, pi, it, erow, eb, epi_in);
+    for (int u = 0; u < ph.n_sub; ++u) {
+      // which operand vector feeds this matrix
+      int vec = u;
+      if (ph.kind == PH_FFN_KR) vec = it < ph.split[0] ? 0 : 1;
+      else if (ph.kind == PH5_KVRG) vec = it / (p.C / ROWS);
+      const __half *xv = cx.sm.xs + (size_t)vec * vstride;
+      float acc[2][NT][4];
 #pragma unroll
       for (int e = 0; e < 2; ++e)
 #pragma unroll
         for (int t = 0; t < NT; ++t)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[u][e][t][i] = 0.f;
-#pragma unroll
-    for (int u = 0; u < 3; ++u) {
-      if (u < ph.n_sub) {
-        // which operand vector feeds this matrix
-        int vec = u;
-        if (ph.kind == PH_FFN_KR) vec = it < ph.split[0] ? 0 : 1;
-        else if (ph.kind == PH5_KVRG) vec = it / (p.C / ROWS);
-        const __half *xv = cx.sm.xs + (size_t)vec * vstride;
-        for (int s = 0; s < nst; ++s) {
-          const int kt = min(KT, ph.K - s * KT);
+          for (int i = 0; i < 4; ++i) acc[e][t][i] = 0.f;
+      for (int s = 0; s < nst; ++s) {
+        const int kt = min(KT, ph.K - s * KT);
+        if (prof) {
+          const unsigned long long w0 = globaltimer_ns();
           mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
-          process_stage<FMT, NB, NT>(cx.sm.ring + (size_t)cx.slot * SLOT_BYTES, kt / CHUNK_K, xv, plane / 8,
-                                     s * (KT / CHUNK_K), cx.warp, cx.lane, acc[u]);
-          __syncwarp();
-          if (cx.lane == 0) mbar_arrive(&cx.sm.empty[cx.slot]);
-          if (++cx.slot == p.n_stages) { cx.slot = 0; cx.parity ^= 1u; }
+          cx.wait_ns += globaltimer_ns() - w0;
+        } else {
+          mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
         }
+        process_stage<FMT, NB, NT>(cx.sm.ring + (size_t)cx.slot * cx.slot_b, kt / CHUNK_K, xv, plane / 8,
+                                   s * (KT / CHUNK_K), cx.warp, cx.lane, acc);
+        __syncwarp();
+        if (cx.lane == 0) mbar_arrive(&cx.sm.empty[cx.slot]);
+        if (++cx.slot == p.n_stages) { cx.slot = 0; cx.parity ^= 1u; }
       }
-    }
-    // hi + lo columns, then the cross-warp reduction of the K split.  Accumulator c0,c1 = row g,
-    // columns 2q, 2q+1; c2,c3 = row g+8.
-    float *red = cx.sm.red + (size_t)buf * 3 * NW * RN;
-    const int g = cx.lane >> 2, q = cx.lane & 3;
+      // this warp's share of the K split: hi + lo columns summed, parked in shared memory.
+      // Accumulator c0,c1 = row g, columns 2q, 2q+1; c2,c3 = row g+8.
+      float *r = cx.sm.red + ((size_t)u * NW + cx.warp) * RN;
 #pragma unroll
-    for (int u = 0; u < 3; ++u) {
-      if (u < ph.n_sub) {
-        float *r = red + ((size_t)u * NW + cx.warp) * RN;
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          float c0 = acc[u][0][t][0] + acc[u][1][t][0], c1 = acc[u][0][t][1] + acc[u][1][t][1];
-          float c2 = acc[u][0][t][2] + acc[u][1][t][2], c3 = acc[u][0][t][3] + acc[u][1][t][3];
-          if (NB == 2) {
-            // columns 0 (hi) and 1 (lo) of the q == 0 lanes
-            if (q == 0) { r[g] = c0 + c1; r[g + 8] = c2 + c3; }
-          } else {
-            // columns 0..3 = hi of streams 0..3 (lanes q = 0,1), columns 4..7 = lo (lanes q = 2,3)
-            c0 += __shfl_xor_sync(0xffffffffu, c0, 2);
-            c1 += __shfl_xor_sync(0xffffffffu, c1, 2);
-            c2 += __shfl_xor_sync(0xffffffffu, c2, 2);
-            c3 += __shfl_xor_sync(0xffffffffu, c3, 2);
-            if (q < 2) {
-              const int sb = t * 4 + 2 * q;
-              r[g * SB + sb] = c0; r[g * SB + sb + 1] = c1;
-              r[(g + 8) * SB + sb] = c2; r[(g + 8) * SB + sb + 1] = c3;
-            }
+      for (int t = 0; t < NT; ++t) {
+        float c0 = acc[0][t][0] + acc[1][t][0], c1 = acc[0][t][1] + acc[1][t][1];
+        float c2 = acc[0][t][2] + acc[1][t][2], c3 = acc[0][t][3] + acc[1][t][3];
+        if (NB == 2) {
+          // columns 0 (hi) and 1 (lo) of the q == 0 lanes
+          if (q == 0) { r[g] = c0 + c1; r[g + 8] = c2 + c3; }
+        } else {
+          // columns 0..3 = hi of streams 0..3 (lanes q = 0,1), columns 4..7 = lo (lanes q = 2,3)
+          c0 += __shfl_xor_sync(0xffffffffu, c0, 2);
+          c1 += __shfl_xor_sync(0xffffffffu, c1, 2);
+          c2 += __shfl_xor_sync(0xffffffffu, c2, 2);
+          c3 += __shfl_xor_sync(0xffffffffu, c3, 2);
+          if (q < 2) {
+            const int sb = t * 4 + 2 * q;
+            r[g * SB + sb] = c0; r[g * SB + sb + 1] = c1;
+            r[(g + 8) * SB + sb] = c2; r[(g + 8) * SB + sb + 1] = c3;
           }
         }
       }
     }
+    const long long ck1 = prof ? clock64() : 0;
     bar_sync(BAR_CONS, NCONS);
-    if (cx.tid < ROWS * SB) {
-      const int row = cx.tid / SB, b = cx.tid % SB;
-      if (b < p.B) {
-        float val[3] = {0.f, 0.f, 0.f};
+    const long long ck2 = prof ? clock64() : 0;
+    if (epi_thread) {
+      float val[3] = {0.f, 0.f, 0.f};
 #pragma unroll
-        for (int u = 0; u < 3; ++u) {
-          if (u < ph.n_sub) {
-            float s = 0.f;
+      for (int u = 0; u < 3; ++u) {
+        if (u < ph.n_sub) {
+          float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < NW; ++w) s += red[((size_t)u * NW + w) * RN + cx.tid];
-            if (FMT == FMT_INT8) s *= __half2float(__ldg(ph.rscale + ((size_t)it * ph.n_sub + u) * ROWS + row));
-            val[u] = s;
-          }
+          for (int w = 0; w < NW; ++w) s += cx.sm.red[((size_t)u * NW + w) * RN + cx.tid];
+          if (FMT == FMT_INT8) s *= epi_in.rscale[u];
+          val[u] = s;
         }
-        epilogue(p, ph, ly, it, row, b, val);
       }
+      epilogue(p, ph, tag, it, erow, eb, val, epi_in);
     }
-    buf ^= 1;
+    // the partial sums are read: the next row block may overwrite them
+    bar_sync(BAR_CONS, NCONS);
+    if (prof) { const long long ck3 = clock64(); c_st += ck1 - ck0; c_bar += ck2 - ck1; c_epi += ck3 - ck2; ++c_n; }
+  }
+  if (prof && (ph.kind == PH_ATT_O || ph.kind == PH_FFN_V)) {
+    p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 4] = c_st; p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 5] = c_bar; p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 6] = c_epi;
+    p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 7] = c_n;
   }
 }
 
 // ---- v5 state update + readout: units of (stream, head, 16 value columns) ----------------------------
-__device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const LayerDev &ly) {
+__device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const LayerDev &ly, int pi) {
   const DecodeParams &p = *cx.p;
   const int C = p.C, H = p.H;
   const int units = p.B * H * 4;
+  const unsigned in_tag = phase_tag(p, pi - 1), tag = phase_tag(p, pi);
   float *scratch = reinterpret_cast<float *>(cx.sm.xs);  // [NW][16] partial readouts
   const int first = (cx.cta + cx.G - ph.rot) % cx.G;
   for (int un = first; un < units; un += cx.G) {
     const int b = un / (H * 4), h = (un / 4) % H, j0 = (un & 3) * 16;
     const int i = cx.tid >> 2, jq = (cx.tid & 3) * 4;
     uint8_t *stb = p.state + (size_t)b * p.state_stride + (size_t)ph.layer * p.layer_stride;
-    float *S = reinterpret_cast<float *>(stb + (size_t)C * act_bytes(p.act_fp16)) + (size_t)h * 4096;
+    float *S = reinterpret_cast<float *>(stb + off_mid(C, p.act_fp16)) + (size_t)h * 4096;
     float4 *sp = reinterpret_cast<float4 *>(S + i * 64 + j0 + jq);
     float4 s = *sp;
-    const float ki = __ldcg(p.k5 + (size_t)b * C + h * 64 + i), ri = __ldcg(p.r5 + (size_t)b * C + h * 64 + i);
-    const float4 vj = __ldcg(reinterpret_cast<const float4 *>(p.v5 + (size_t)b * C + h * 64 + j0 + jq));
+    const float ki = ex_wait1(cx, p.k5 + (size_t)b * C + h * 64 + i, in_tag);
+    const float ri = ex_wait1(cx, p.r5 + (size_t)b * C + h * 64 + i, in_tag);
+    const float4 vj = ex_wait4(cx, p.v5 + (size_t)b * C + h * 64 + j0 + jq, in_tag);
     const float u = p.version == 50 ? __ldg(ly.first + h) : __ldg(ly.first + h * 64 + i);
     const float w = p.version == 50 ? __ldg(ly.decay + h) : __ldg(ly.decay + h * 64 + i);
     const float a0 = ki * vj.x, a1 = ki * vj.y, a2 = ki * vj.z, a3 = ki * vj.w;
@@ -644,7 +881,7 @@ __device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const La
       float t = 0.f;
 #pragma unroll
       for (int w8 = 0; w8 < NW; ++w8) t += scratch[w8 * 16 + cx.tid];
-      p.o5[(size_t)b * C + h * 64 + j0 + cx.tid] = t;
+      ex_store(p.o5 + (size_t)b * C + h * 64 + j0 + cx.tid, t, tag);
     }
     bar_sync(BAR_CONS, NCONS);
   }
@@ -654,73 +891,142 @@ __device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const La
 template <int FMT, int NB, int NT>
 __device__ __forceinline__ void consumer(Ctx &cx) {
   const DecodeParams &p = *cx.p;
+  const bool prof = p.prof != nullptr && cx.tid == 0;
+  const int v5 = p.version != 4;
   for (int pi = 0; pi < p.n_phases; ++pi) {
     const PhaseDev ph = p.phases[pi];
+    const int first = (cx.cta + cx.G - ph.rot) % cx.G;
+    if (ph.kind == PH5_WKV) {
+      if (first < p.B * p.H * 4) phase_wkv5(cx, ph, p.layers[ph.layer], pi);
+      continue;
+    }
+    if (first >= ph.n_items) continue;   // no row block here: nothing to read, nothing to write
+    cx.prof_phase = pi;
+    if (prof) p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 0] = globaltimer_ns();
     const bool layered = ph.kind != PH_HEAD && ph.kind != PH_MATVEC;
     const LayerDev *ly = layered ? p.layers + ph.layer : nullptr;
     uint8_t *st0 = p.state + (size_t)(layered ? ph.layer : 0) * p.layer_stride;  // stream 0
-    flush_stash(cx);
-    switch (ph.kind) {
-      case PH_ATT_KVR:
-      case PH5_KVRG: {
-        const int nvec = p.version == 4 || p.version == 50 ? 3 : 4;
-        prologue_ln_mix<NB, NT>(cx, ph.layer == 0, ly->ln1_w, ly->ln1_b, ly->att_mix, nvec, st0);
-        cx.stash_dst = st0;
-        break;
+    // the streams of one launch advance together, so they share the parity of stream 0
+    const int par = (int)(p.par_mask & 1u);
+    if (ph.kind == PH_ATT_KVR || ph.kind == PH5_KVRG || ph.kind == PH_FFN_KR || ph.kind == PH_HEAD) {
+      // one LayerNorm prologue, three parameter sets
+      const float *ln_w = p.lnout_w, *ln_b = p.lnout_b;
+      const float *const *mix = nullptr;
+      const uint8_t *sx_rd = nullptr;
+      uint8_t *sx_wr = nullptr;
+      int nvec = 0, item0 = 0;
+      if (ph.kind == PH_FFN_KR) {
+        ln_w = ly->ln2_w; ln_b = ly->ln2_b; mix = ly->ffn_mix; nvec = 2; item0 = ph.split[0];
+        sx_rd = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par);
+        sx_wr = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par ^ 1);
+      } else if (ph.kind != PH_HEAD) {
+        ln_w = ly->ln1_w; ln_b = ly->ln1_b; mix = ly->att_mix;
+        nvec = p.version == 4 || p.version == 50 ? 3 : 4;
+        sx_rd = st0 + off_sx(p.C, p.act_fp16, par);
+        sx_wr = st0 + off_sx(p.C, p.act_fp16, par ^ 1);
       }
-      case PH_ATT_O:
-        if (p.version == 4) prologue_vec<NB, NT>(cx, p.rwkv, p.C);
-        else prologue_gn_gate<NB, NT>(cx, *ly);
-        break;
-      case PH_FFN_KR: {
-        const size_t off = p.version == 4 ? (size_t)p.C * act_bytes(p.act_fp16) + 3 * (size_t)p.C * 4
-                                          : (size_t)p.C * act_bytes(p.act_fp16) + (size_t)p.H * 4096 * 4;
-        prologue_ln_mix<NB, NT>(cx, 0, ly->ln2_w, ly->ln2_b, ly->ffn_mix, 2, st0 + off);
-        cx.stash_dst = st0 + off;
-        break;
-      }
-      case PH_FFN_V: prologue_vec<NB, NT>(cx, p.kk, p.F); break;
-      case PH_HEAD: prologue_ln_mix<NB, NT>(cx, 0, p.lnout_w, p.lnout_b, nullptr, 0, nullptr); break;
-      case PH_MATVEC: prologue_vec<NB, NT>(cx, p.kk, ph.K); break;
-      default: break;
+      const bool layer0 = ph.layer == 0 && (ph.kind == PH_ATT_KVR || ph.kind == PH5_KVRG);
+      prologue_ln<NB, NT>(cx, ph, layer0, phase_tag(p, pi - 1), ln_w, ln_b, mix, nvec, sx_rd, sx_wr, item0);
+    } else if (ph.kind == PH_ATT_O) {
+      if (p.version == 4) prologue_vec<NB, NT>(cx, p.rwkv, p.C, phase_tag(p, pi - 1));
+      else prologue_gn_gate<NB, NT>(cx, *ly, phase_tag(p, pi - 1), phase_tag(p, pi - 2));
+    } else if (ph.kind == PH_FFN_V) {
+      prologue_vec<NB, NT>(cx, p.kk, p.F, phase_tag(p, pi - 1));
+    } else if (ph.kind == PH_MATVEC) {
+      prologue_plain<NB, NT>(cx, reinterpret_cast<const float *>(p.kk), ph.K);
     }
-    if (ph.kind == PH5_WKV) phase_wkv5(cx, ph, *ly);
-    else run_items<FMT, NB, NT>(cx, ph, ly);
-    if (pi + 1 < p.n_phases) grid_barrier(cx);
+    if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 1] = globaltimer_ns(); cx.wait_ns = 0; }
+    run_items<FMT, NB, NT>(cx, ph, ly, pi, first);
+    if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 2] = globaltimer_ns(); p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 3] = cx.wait_ns; }
   }
 }
 
+// Walks this CTA's weight tiles in the order the consumers use them: phases in order, the CTA's row
+// blocks of the phase, the matrices fused in a row block, the stages of a matrix.
+template <int FMT>
+struct TileIter {
+  const DecodeParams *p;
+  int cta, G;
+  int pi, it, u, s, nst;
+  PhaseDev ph;
+  const uint8_t *src;
+  bool done;
+
+  __device__ __forceinline__ void load_phase() {
+    // advance pi to the next phase in which this CTA owns a row block
+    while (pi < p->n_phases) {
+      ph = p->phases[pi];
+      if (ph.n_items > 0) {
+        it = (cta + G - ph.rot) % G;
+        if (it < ph.n_items) {
+          nst = num_stages(FMT, ph.K);
+          u = 0; s = 0;
+          src = ph.w + (size_t)it * rowblock_bytes(FMT, ph.K) * ph.n_sub;
+          return;
+        }
+      }
+      ++pi;
+    }
+    done = true;
+  }
+  __device__ __forceinline__ void init(const DecodeParams *pp, int cta_, int G_) {
+    p = pp; cta = cta_; G = G_; pi = 0; done = false;
+    load_phase();
+  }
+  __device__ __forceinline__ uint32_t bytes() const {
+    const int KT = kt_max(FMT);
+    return stage_bytes(FMT, min(KT, ph.K - s * KT));
+  }
+  __device__ __forceinline__ void next() {
+    src += bytes();
+    if (++s < nst) return;
+    s = 0;
+    if (++u < ph.n_sub) return;
+    u = 0;
+    it += G;
+    if (it < ph.n_items) {
+      src = ph.w + (size_t)it * rowblock_bytes(FMT, ph.K) * ph.n_sub;
+      return;
+    }
+    ++pi;
+    load_phase();
+  }
+};
+
+__device__ __forceinline__ void prefetch_l2(const void *src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// One thread per CTA.  Keeps the shared-memory ring full; optionally asks L2 for tiles further ahead.
 template <int FMT>
 __device__ __forceinline__ void producer(Ctx &cx) {
   const DecodeParams &p = *cx.p;
-  const int KT = kt_max(FMT);
+  TileIter<FMT> ld, pf;
+  ld.init(&p, cx.cta, cx.G);
+  pf.init(&p, cx.cta, cx.G);
+  long long ld_bytes = 0, pf_bytes = 0;
+  const long long window = (long long)p.l2_prefetch_bytes;
   int slot = 0;
   uint32_t parity = 1;  // a fresh barrier reads as "previous phase complete"
   bool live = true;
-  for (int pi = 0; pi < p.n_phases && live; ++pi) {
-    const PhaseDev ph = p.phases[pi];
-    if (ph.n_items == 0) continue;
-    const int nst = num_stages(FMT, ph.K);
-    const size_t sub_bytes = rowblock_bytes(FMT, ph.K);
-    const size_t item_bytes = sub_bytes * ph.n_sub;
-    const int first = (cx.cta + cx.G - ph.rot) % cx.G;
-    for (int it = first; it < ph.n_items && live; it += cx.G) {
-      const uint8_t *src = ph.w + (size_t)it * item_bytes;
-      for (int u = 0; u < ph.n_sub && live; ++u) {
-        for (int s = 0; s < nst; ++s) {
-          const int kt = min(KT, ph.K - s * KT);
-          const uint32_t bytes = stage_bytes(FMT, kt);
-          if (!mbar_wait(&cx.sm.empty[slot], parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
-            live = false;
-            break;
-          }
-          mbar_expect_tx(&cx.sm.full[slot], bytes);
-          bulk_g2s(cx.sm.ring + (size_t)slot * SLOT_BYTES, src, bytes, &cx.sm.full[slot]);
-          src += bytes;
-          if (++slot == p.n_stages) { slot = 0; parity ^= 1u; }
-        }
-      }
+  const uint64_t pol = l2_evict_first_policy();
+  while (!ld.done) {
+    while (window > 0 && !pf.done && pf_bytes - ld_bytes < window) {
+      const uint32_t b = pf.bytes();
+      if (pf_bytes >= ld_bytes + (long long)p.n_stages * cx.slot_b) prefetch_l2(pf.src, b);  // beyond the ring
+      pf_bytes += b;
+      pf.next();
     }
+    const uint32_t bytes = ld.bytes();
+    if (!mbar_wait(&cx.sm.empty[slot], parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
+      live = false;
+      break;
+    }
+    mbar_expect_tx(&cx.sm.full[slot], bytes);
+    bulk_g2s_hint(cx.sm.ring + (size_t)slot * cx.slot_b, ld.src, bytes, &cx.sm.full[slot], pol);
+    ld_bytes += bytes;
+    ld.next();
+    if (++slot == p.n_stages) { slot = 0; parity ^= 1u; }
   }
   if (!live) {
     // give copies that are still in flight time to land before the CTA's shared memory goes away
@@ -736,21 +1042,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   cx.p = &p;
   cx.tid = threadIdx.x; cx.warp = threadIdx.x >> 5; cx.lane = threadIdx.x & 31;
   cx.cta = blockIdx.x; cx.G = gridDim.x;
-  cx.slot = 0; cx.parity = 0; cx.epoch = 0; cx.stash_dst = nullptr;
-  size_t o_stash, o_red, o_xs, o_ring;
-  smem_layout<NB, NT>(xs_halfs_needed(p.C, p.F, p.version, NB, NT), p.n_stages, &o_stash, &o_red, &o_xs, &o_ring);
+  cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0;
+  cx.slot_b = slot_bytes(FMT);
+  size_t o_red, o_xs, o_ring;
+  smem_layout<NB, NT>(FMT, xs_halfs_needed(p.C, p.F, p.version, NB, NT), p.n_stages, &o_red, &o_xs, &o_ring);
   cx.sm.full = reinterpret_cast<uint64_t *>(smem);
   cx.sm.empty = cx.sm.full + MAX_STAGES;
   cx.sm.abort_flag = reinterpret_cast<volatile int *>(smem + 256);
   cx.sm.ln_red = reinterpret_cast<float *>(smem + 320);
-  cx.sm.stats = reinterpret_cast<float *>(smem + 896);
-  cx.sm.stash = reinterpret_cast<float *>(smem + o_stash);
   cx.sm.red = reinterpret_cast<float *>(smem + o_red);
   cx.sm.xs = reinterpret_cast<__half *>(smem + o_xs);
   cx.sm.ring = smem + o_ring;
-  const int per = (p.C + cx.G - 1) / cx.G;
-  cx.own0 = min(cx.cta * per, p.C);
-  cx.ownn = min(per, p.C - cx.own0);
 
   if (cx.tid == 0) {
     for (int s = 0; s < p.n_stages; ++s) {
@@ -762,21 +1064,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   }
   __syncthreads();
 
-  if (cx.warp == NW) {
-    if (cx.lane == 0) producer<FMT>(cx);
+  // Register hand-over between the warp groups (the launch gives every thread 168): the producer group
+  // keeps 40 and the two consumer groups grow to 232, enough to hold a row block's accumulators, the
+  // prefetched epilogue inputs and a LayerNorm prologue's parameters without touching local memory.
+  if (cx.warp >= NW) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (cx.warp == NW && cx.lane == 0) producer<FMT>(cx);
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     consumer<FMT, NB, NT>(cx);
-    // last arrival resets the barrier words for the next launch
-    bar_sync(BAR_CONS, NCONS);
-    if (cx.tid == 0) {
-      __threadfence();
-      const unsigned done = atomicAdd(p.sync + 1, 1u);
-      if (done == (unsigned)cx.G - 1) {
-        p.sync[0] = 0;
-        p.sync[1] = 0;
-        __threadfence();
-      }
-    }
   }
 }
 
@@ -837,12 +1133,11 @@ cudaError_t max_grid_t(size_t smem, int device, int *grid) {
 
 // mode: 0 = one stream, 1 = up to 4 streams, 2 = up to 8 streams
 size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages) {
-  (void)fmt;
-  size_t a, b, c, d;
+  size_t a, b, c;
   switch (mode) {
-    case 0: return smem_layout<2, 1>(xs_halfs_needed(C, F, version, 2, 1), n_stages, &a, &b, &c, &d);
-    case 1: return smem_layout<8, 1>(xs_halfs_needed(C, F, version, 8, 1), n_stages, &a, &b, &c, &d);
-    default: return smem_layout<8, 2>(xs_halfs_needed(C, F, version, 8, 2), n_stages, &a, &b, &c, &d);
+    case 0: return smem_layout<2, 1>(fmt, xs_halfs_needed(C, F, version, 2, 1), n_stages, &a, &b, &c);
+    case 1: return smem_layout<8, 1>(fmt, xs_halfs_needed(C, F, version, 8, 1), n_stages, &a, &b, &c);
+    default: return smem_layout<8, 2>(fmt, xs_halfs_needed(C, F, version, 8, 2), n_stages, &a, &b, &c);
   }
 }
 

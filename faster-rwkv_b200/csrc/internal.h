@@ -11,7 +11,7 @@ namespace frb {
 
 constexpr int NW = 8;                       // consumer warps per CTA
 constexpr int NCONS = NW * 32;              // consumer threads
-constexpr int NTHREADS = NCONS + 32;        // + one producer warp
+constexpr int NTHREADS = NCONS + 128;       // + one producer warp group (one thread of it issues the copies)
 constexpr int MAX_STAGES = 12;
 constexpr int MAX_B = 8;
 
@@ -49,12 +49,21 @@ struct LayerDev {
   const float *lnx_w, *lnx_b;  // v5
 };
 
+// One element of an exchange vector (a vector one phase writes and the next phases read across CTAs):
+// the fp32 value in the low word and, in the high word, the sequence number of the phase that wrote it.
+// A reader knows which phase must have produced the value and polls until the tag matches, so the data
+// is its own synchronisation: no grid-wide barrier, no fence, one 64-bit store per value.
+typedef unsigned long long exch_t;
+
 struct DecodeParams {
   int version, L, C, F, V, Vpad, H;
   int fmt, act_fp16, rescale_every;
   int B;
   int n_phases;
   int n_stages;
+  int l2_prefetch_bytes;       // per CTA: how far ahead of the ring the producer asks L2 for tiles (0 = off)
+  unsigned seq_base;           // tag of phase pi of this launch = seq_base + pi + 1
+  unsigned par_mask;           // bit b: which copy of the token-shift states stream b reads (it writes the other)
   int ids_val[MAX_B];
   const int32_t *ids_dev;      // when non-null the ids are read from here
   const void *emb;             // [V][C], fp32 when emb_f32 else fp16 (the file's dtype)
@@ -62,22 +71,29 @@ struct DecodeParams {
   const LayerDev *layers;
   const float *lnout_w, *lnout_b;
   const PhaseDev *phases;
-  float *x, *rwkv, *kk, *rr, *logits;   // [B][C], [B][C], [B][F], [B][C], [B][Vpad]
-  float *k5, *v5, *r5, *g5, *o5;        // v5 exchange vectors [B][C]
+  exch_t *x, *rwkv, *kk, *rr;           // [B][C], [B][C], [B][F], [B][C]
+  exch_t *k5, *v5, *r5, *g5, *o5;       // v5 exchange vectors [B][C]
+  float *logits;                        // [B][Vpad]
   uint8_t *state;                       // stream slot b at state + b * state_stride
   size_t state_stride, layer_stride;    // bytes
-  unsigned *sync;                       // [0] grid barrier counter, [1] exit counter
   int *status;                          // 0 = ok, else first failure code
+  unsigned long long *prof;             // optional [n_phases][8] profile of CTA 0
 };
 
 // status codes written by the kernel
-constexpr int ST_TIMEOUT_FULL = 101, ST_TIMEOUT_EMPTY = 102, ST_TIMEOUT_GRID = 103;
+constexpr int ST_TIMEOUT_FULL = 101, ST_TIMEOUT_EMPTY = 102, ST_TIMEOUT_DATA = 103;
 
-// state byte offsets inside one layer of one stream slot
+// State bytes inside one layer of one stream slot.  The token-shift states exist twice (a token reads
+// copy `par` and writes copy `1 - par`), so no CTA can overwrite a value another CTA still has to read.
+//   RWKV-4: sx[2][C] act, aa[C], bb[C], pp[C] f32, ffn_sx[2][C] act
+//   RWKV-5: sx[2][C] act, s[H][64][64] f32, ffn_sx[2][C] act
 FRB_HD size_t act_bytes(int act_fp16) { return act_fp16 ? 2 : 4; }
-FRB_HD size_t v4_layer_bytes(int C, int act_fp16) { return 2 * C * act_bytes(act_fp16) + 3 * (size_t)C * 4; }
-FRB_HD size_t v5_layer_bytes(int C, int H, int act_fp16) {
-  return 2 * C * act_bytes(act_fp16) + (size_t)H * 64 * 64 * 4;
+FRB_HD size_t mid_bytes(int C, int H, int v5) { return v5 ? (size_t)H * 4096 * 4 : 3 * (size_t)C * 4; }
+FRB_HD size_t layer_bytes(int C, int H, int v5, int act_fp16) { return 4 * C * act_bytes(act_fp16) + mid_bytes(C, H, v5); }
+FRB_HD size_t off_sx(int C, int act_fp16, int par) { return (size_t)par * C * act_bytes(act_fp16); }
+FRB_HD size_t off_mid(int C, int act_fp16) { return 2 * (size_t)C * act_bytes(act_fp16); }
+FRB_HD size_t off_ffn_sx(int C, int H, int v5, int act_fp16, int par) {
+  return off_mid(C, act_fp16) + mid_bytes(C, H, v5) + (size_t)par * C * act_bytes(act_fp16);
 }
 
 // ---- launchers implemented in the .cu files ------------------------------------------------------

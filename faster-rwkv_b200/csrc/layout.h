@@ -32,7 +32,7 @@ constexpr int FMT_FP16 = 0, FMT_INT8 = 1, FMT_INT4 = 2;
 constexpr int ROWS = 16;      // outputs per row block
 constexpr int CHUNK_K = 64;   // inputs per chunk
 
-FRB_HD int kt_max(int fmt) { return fmt == FMT_FP16 ? 512 : fmt == FMT_INT8 ? 1024 : 2048; }
+FRB_HD int kt_max(int fmt) { return fmt == FMT_FP16 ? 1024 : 2048; }   // inputs per stage
 FRB_HD int chunk_weight_bytes(int fmt) { return fmt == FMT_FP16 ? 2048 : fmt == FMT_INT8 ? 1024 : 512; }
 FRB_HD int chunk_bytes(int fmt) { return chunk_weight_bytes(fmt) + (fmt == FMT_INT4 ? 64 : 0); }
 // bytes of a stage covering kt inputs (kt a multiple of 64)
@@ -40,7 +40,8 @@ FRB_HD uint32_t stage_bytes(int fmt, int kt) { return (uint32_t)(kt / CHUNK_K) *
 FRB_HD int num_stages(int fmt, int K) { return (K + kt_max(fmt) - 1) / kt_max(fmt); }
 // bytes of one row block over all K inputs
 FRB_HD uint32_t rowblock_bytes(int fmt, int K) { return (uint32_t)(K / CHUNK_K) * (uint32_t)chunk_bytes(fmt); }
-constexpr uint32_t SLOT_BYTES = 18432;  // largest stage: int4, 2048 inputs
+// bytes of one ring slot = the largest stage of the format (fp16 / int8: 32 KiB, int4: 18 KiB)
+FRB_HD uint32_t slot_bytes(int fmt) { return (uint32_t)(kt_max(fmt) / CHUNK_K) * (uint32_t)chunk_bytes(fmt); }
 
 // Element position of input k, batch column n inside the fp16 operand vector a CTA keeps in shared
 // memory (NB = padded batch, 1 or 8): [chunk][j/2][n][q][(j&1)*4 + s] with k = 64*chunk + 16*j + 4*q + s.
