@@ -1,0 +1,49 @@
+"""Build the reference's own CPU path from its sources where they lie (never copied into this tree).
+
+Outputs go to oracle/_ref/ only (git-ignored, shipped to the GPU box as built files):
+  fr_ref_run   rwkv::Model driver: reference model.cpp, tensor.cpp, utils.cpp, kernels/cpu/*,
+               kernels/default/*, kernels/shape/*, kernels/export-ncnn/kernels.cpp  +  oracle/ref/cpu_prims.cpp
+               (the fp32 CPU primitives the reference lacks)  +  oracle/ref/ref_driver.cpp
+msgpack-c (a FetchContent dependency of the reference) is replaced by oracle/compat/msgpack.hpp.
+The reference's CMake build is not run.  TEST INFRASTRUCTURE ONLY.
+"""
+import glob
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("FR_REFERENCE_DIR", "/root/reference")
+OUT = os.path.join(HERE, "_ref")
+
+
+def build(force: bool = False) -> str:
+    if not os.path.isdir(REF):
+        raise RuntimeError(f"reference tree not found at {REF}")
+    os.makedirs(OUT, exist_ok=True)
+    exe = os.path.join(OUT, "fr_ref_run")
+    srcs = [os.path.join(REF, f) for f in ("model.cpp", "tensor.cpp", "utils.cpp")]
+    for d in ("kernels/cpu", "kernels/default", "kernels/shape"):
+        srcs += sorted(glob.glob(os.path.join(REF, d, "*.cpp")))
+    srcs.append(os.path.join(REF, "kernels/export-ncnn/kernels.cpp"))
+    srcs += [os.path.join(HERE, "ref", "cpu_prims.cpp"), os.path.join(HERE, "ref", "ref_driver.cpp")]
+    newest = max(os.path.getmtime(s) for s in srcs + [os.path.join(HERE, "compat", "msgpack.hpp")])
+    if not force and os.path.exists(exe) and os.path.getmtime(exe) >= newest:
+        return exe
+    objs, procs = [], []
+    for s in srcs:
+        o = os.path.join(OUT, os.path.relpath(s, "/").replace("/", "_").replace(".cpp", ".o"))
+        objs.append(o)
+        if force or not os.path.exists(o) or os.path.getmtime(o) < newest:
+            cmd = ["g++", "-std=c++17", "-O2", "-march=x86-64-v3", "-w", "-include", "immintrin.h", "-I", os.path.join(HERE, "compat"), "-I", REF,
+                   "-c", s, "-o", o]
+            procs.append((s, subprocess.Popen(cmd)))
+    for s, p in procs:
+        if p.wait() != 0:
+            raise RuntimeError(f"g++ failed on {s}")
+    subprocess.check_call(["g++", "-o", exe, *objs])
+    return exe
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

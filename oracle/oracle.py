@@ -28,7 +28,7 @@ def build(force: bool = False) -> str:
 
 class _Cfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in
-                ("version", "n_layer", "n_embd", "n_ffn", "n_head", "vocab", "rescale_every", "state_fp16")]
+                ("version", "n_layer", "n_embd", "n_ffn", "n_head", "vocab", "rescale_every", "state_fp16", "gate_from_xx")]
 
 
 def lib() -> ctypes.CDLL:
@@ -126,15 +126,17 @@ class OracleModel:
     (kernels/default/model_forward.cpp:173-175) for files whose weights were pre-divided.
     state_fp16=True stores the token-shift states rounded to fp16, as the "cuda fp16" strategy does
     (its state tensors have the activation dtype, model.cpp:149-151).
+    gate_from_xx=True reproduces kernels/default/att.cpp:101 (RWKV-5.1/5.2 gate fed by xx); the default
+    follows the CUDA path (kernels/cuda/att.cu:289, gate fed by the mixed gx).
     weight_format "int8" / "int4" replaces every projection matrix and the head by its
     quantise->dequantise image, which is what the quantised strategies multiply by.
     """
 
     def __init__(self, shape, tensors: Dict[str, np.ndarray], param_order: List[str], rescale_every: int = 0,
-                 weight_format: str = "fp16", state_fp16: bool = False):
+                 weight_format: str = "fp16", state_fp16: bool = False, gate_from_xx: bool = False):
         self.shape = shape
         self.cfg = _Cfg(_version_code(shape.version), shape.n_layer, shape.n_embd, shape.n_ffn, shape.n_head,
-                        shape.vocab, rescale_every, int(state_fp16))
+                        shape.vocab, rescale_every, int(state_fp16), int(gate_from_xx))
         self._keep = []
         for name in param_order:
             a = np.ascontiguousarray(tensors[name], dtype=np.float32)

@@ -28,6 +28,8 @@ typedef struct {
   int rescale_every;  /* 6 when the activations are fp16 (model_forward.cpp:173), else 0 */
   int state_fp16;     /* 1: token-shift states are stored as fp16, as under "cuda fp16" where the state
                          tensors have the activation dtype (model.cpp:149-151, kernels/cuda/att.cu:337-359) */
+  int gate_from_xx;   /* 1: v5.1/5.2 gate = silu(xx @ Wg) as kernels/default/att.cpp:101 writes it; 0 (default):
+                         silu(gx @ Wg) as the CUDA path computes it (kernels/cuda/att.cu:289) */
 } orc_cfg;
 
 int orc_num_threads(void) {
@@ -135,7 +137,7 @@ static void att_v4(int C, int sf16, float *x, float *sx, float *aa, float *bb, f
  * by gx as the CUDA path does (kernels/cuda/att.cu:289).  State s is [H][S key][S value];
  * decay / first are indexed per head (v5.0, att.cu:242) or per (head, key) (v5.1/5.2,
  * att.cu:306).  GroupNorm with H groups, eps 1e-5 (kernels/cuda/group_norm.cu:322-357). */
-static void att_v5(int version, int C, int H, int sf16, float *x, float *sx, float *s, const float *const *p,
+static void att_v5(int version, int C, int H, int sf16, int gate_xx, float *x, float *sx, float *s, const float *const *p,
                    float *tmp) {
   const int S = C / H, gate = version >= 51;
   int q = 0;
@@ -156,7 +158,7 @@ static void att_v5(int version, int C, int H, int sf16, float *x, float *sx, flo
   matvec(vx, vw, C, C, v);
   if (gate) {
     mix(xx, sx, mg, C, gx);
-    matvec(gx, gw, C, C, g);
+    matvec(gate_xx ? xx : gx, gw, C, C, g);
     for (int i = 0; i < C; ++i) g[i] = g[i] * sigmoidf_(g[i]); /* SiLU, att.cu:145-152 */
   }
   for (int h = 0; h < H; ++h) {
@@ -238,7 +240,7 @@ int orc_forward(const orc_cfg *c, const float *const *params, const float *emb, 
     } else {
       size_t S = C / H, per = 2 * (size_t)C + (size_t)H * S * S;
       float *st = state + (size_t)l * per;
-      att_v5(c->version, C, H, c->state_fp16, x, st, st + C, p, tmp);
+      att_v5(c->version, C, H, c->state_fp16, c->gate_from_xx, x, st, st + C, p, tmp);
       ffn(C, F, c->state_fp16, x, st + C + (size_t)H * S * S, p + natt, tmp);
     }
     if (c->rescale_every > 0 && (l + 1) % c->rescale_every == 0)
