@@ -58,6 +58,8 @@ SHAPES: Dict[str, Shape] = {
     "tiny52": Shape("5.2", 2, 128, 448, 96, n_head=2),
     "tiny51": Shape("5.1", 2, 128, 448, 96, n_head=2),
     "tiny50": Shape("5", 2, 128, 448, 96, n_head=2),
+    "mid4": Shape("4", 7, 256, 1024, 512),
+    "mid52": Shape("5.2", 3, 256, 1024, 512, n_head=4),
 }
 
 

@@ -60,22 +60,25 @@ def test_dropin_error_is_an_exception_not_a_crash(synth, tmp_path):
 
 
 @pytest.mark.skipif(not (os.path.exists(DROPIN) and os.path.exists(REF_CUDA)), reason="reference CUDA baseline not built")
-@pytest.mark.parametrize("name", ["tiny4b", "tiny52"])
+@pytest.mark.parametrize("name", ["mid4", "mid52"])
 def test_against_reference_cuda_fp16(orc, synth, tmp_path, name):
-    """Same `.fr`, same ids: this backend vs the reference's kernels/cuda ("cuda fp16").  The reference rounds
-    every activation to fp16, so both are also compared with the fp32 oracle: this backend must be the closer one."""
+    """Same `.fr`, same ids: this backend vs the reference's own kernels/cuda + cuBLAS ("cuda fp16") rebuilt for
+    sm_100a.  The reference rounds every activation to fp16 (kernels/cuda/att.cu:90-143, layer_norm.cu:64-72), so
+    it sits 1e-3 .. 3e-3 (rel-L2) away from the fp32 forward on these models; this backend must be the closer of
+    the two, and the distance between the two is bounded by the reference's own rounding error.
+    (Shapes: the reference's CUDA kernels return garbage for the odd-sized tiny shapes used elsewhere in this
+    suite, vocab 96 / 211 and n_embd 192, so the comparison uses 256-wide models.)"""
     shape, tensors, fr = _model_file(synth, str(tmp_path), name, "fp16")
     ids = synth.token_ids(shape, 8, seed=3)
-    if str(shape.version) == "4":
-        theirs = _run(REF_CUDA, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
-    else:
-        theirs = _run(REF_CUDA, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
+    theirs = _run(REF_CUDA, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
     ours = _run(DROPIN, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)
     ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6)
     exact = np.stack([ref.run(int(t)) for t in ids])
-    d_ours = np.linalg.norm(ours - exact) / np.linalg.norm(exact)
-    d_theirs = np.linalg.norm(theirs - exact) / np.linalg.norm(exact)
-    d_pair = np.abs(ours - theirs).max()
-    print(f"{name}: rel-L2 to fp32 oracle ours {d_ours:.2e} reference-cuda {d_theirs:.2e}; max-abs ours-vs-reference {d_pair:.2e}")
-    assert d_ours <= d_theirs + 1e-4
-    assert d_pair < 5e-2   # the reference's own fp16 rounding noise on these tiny random models
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    d_ours, d_theirs, d_pair = rel(ours, exact), rel(theirs, exact), rel(ours, theirs)
+    print(f"{name}: rel-L2 to the fp32 forward: ours {d_ours:.2e}, reference cuda fp16 {d_theirs:.2e}; "
+          f"ours vs reference: rel-L2 {d_pair:.2e}, max-abs {np.abs(ours - theirs).max():.2e}")
+    assert d_ours < 1e-3                       # the north star's tolerance against the fp32 forward
+    assert d_ours < d_theirs
+    assert d_pair < d_theirs + d_ours + 1e-4   # triangle: nothing but the reference's rounding separates the two
+    assert np.abs(ours - theirs).max() < 3e-2
