@@ -188,6 +188,37 @@ def cpu_baseline(shape, host_master, n_tokens: int, seed: int = 0):
             "sample": f"{n_tokens} tokens, batch 1, fp32 weights, same model shape ({dt:.1f} s)"}
 
 
+# ------------------------------------------------------------------ reference GPU path, same driver binary
+
+def reference_gpu_leg(pkg, n_tokens: int = 256):
+    """The reference's own kernels/cuda + cuBLAS ("cuda fp16", rebuilt for sm_100a: oracle/_ref/fr_ref_cuda_run) and
+    this backend behind the same unchanged rwkv::Model (faster-rwkv_b200/backend/build/fr_b200_run), both timed
+    through Model::Run(int) + host argmax on the 0.1B-shaped model the reference's bench_model.cpp uses."""
+    import tempfile
+    ref_exe = os.path.join(ROOT, "oracle", "_ref", "fr_ref_cuda_run")
+    our_exe = os.path.join(ROOT, "faster-rwkv_b200", "backend", "build", "fr_b200_run")
+    if not (os.path.exists(ref_exe) and os.path.exists(our_exe)):
+        return {"unavailable": "reference-linked binaries not built (need the reference tree at build time)"}
+    synth = pkg.synth
+    shape = synth.SHAPES["c0"]
+    out = {"workload": "c0: RWKV-4 0.1B-shaped, cuda fp16, batch 1, Model::Run(int) + host argmax, wall clock",
+           "tokens": n_tokens}
+    with tempfile.TemporaryDirectory() as tmp:
+        fr = os.path.join(tmp, "c0-fp16.fr")
+        synth.write_fr(fr, shape, synth.to_file_dtypes(shape, synth.generate(shape, seed=0), "fp16"))
+        for key, exe in (("reference_cuda", ref_exe), ("b200_backend", our_exe)):
+            try:
+                r = subprocess.run([exe, fr, "cuda fp16", os.path.join(tmp, "o.bin"), "--bench", str(n_tokens), "1"],
+                                   capture_output=True, text=True, timeout=600)
+                ms = [float(l.split()[1]) for l in r.stdout.splitlines() if l.startswith("ms_per_token")]
+                out[key] = {"ms_per_token": ms[0], "tok_s": 1e3 / ms[0]} if ms else {"error": (r.stderr or r.stdout)[-200:]}
+            except Exception as ex:
+                out[key] = {"error": str(ex)[:200]}
+    if "tok_s" in out.get("reference_cuda", {}) and "tok_s" in out.get("b200_backend", {}):
+        out["speedup"] = out["b200_backend"]["tok_s"] / out["reference_cuda"]["tok_s"]
+    return out
+
+
 # ------------------------------------------------------------------ main
 
 def main():
@@ -202,6 +233,7 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=24)
     ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-ref-gpu", action="store_true")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -330,6 +362,9 @@ def main():
     cb = None
     if host_master is not None:
         cb = cpu_baseline(shape, host_master, args.cpu_tokens)
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_ref_gpu and args.workload == "c1":
+        ref_gpu = reference_gpu_leg(pkg)
 
     if rank == 0:
         line = {"metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K,
@@ -339,6 +374,8 @@ def main():
                 "data": "synthetic", "config": config, "e2e": e2e, "gpu_launches": int(launches),
                 "clocks": clocks, "roofline": roofline, "cpu_baseline": cb, "variants": variants,
                 "kernel_geometry": {k: info[k] for k in ("n_ctas", "n_threads", "smem_bytes", "n_stages", "n_phases")}}
+        if ref_gpu:
+            line["reference_gpu"] = ref_gpu
         if check:
             line["cross_gpu_check"] = check
         print(json.dumps(line))

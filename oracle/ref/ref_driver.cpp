@@ -2,6 +2,9 @@
 // TEST INFRASTRUCTURE ONLY.  usage: fr_ref_run <model.fr> <strategy> <out.bin> [--seq] id id id ...
 // Without --seq every id goes through Model::Run(int) (model.cpp:205); with --seq all ids go through
 // Model::Run(vector) once (model.cpp:188-203) and only the last logits are written.
+// --bench N: after the ids, N greedy tokens through Model::Run(int) (host argmax, as bench_model.cpp:5-10 times
+// Run + the copy to the host) are timed with the wall clock; prints "ms_per_token <x>".
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -20,9 +23,11 @@ int main(int argc, char **argv) {
     rwkv::Model model(argv[1], argv[2]);
     std::ofstream out(argv[3], std::ios::binary);
     bool seq = false;
+    int bench = 0;
     std::vector<int> ids;
     for (int i = 4; i < argc; ++i) {
       if (!std::strcmp(argv[i], "--seq")) seq = true;
+      else if (!std::strcmp(argv[i], "--bench") && i + 1 < argc) bench = std::atoi(argv[++i]);
       else ids.push_back(std::atoi(argv[i]));
     }
     auto dump = [&](const rwkv::Tensor &t) {
@@ -30,6 +35,21 @@ int main(int argc, char **argv) {
     };
     if (seq) dump(model.Run(ids));
     else for (int id : ids) dump(model.Run(id));
+    if (bench > 0) {
+      auto greedy = [&](int id) {
+        rwkv::Tensor t = model.Run(id);
+        const float *p = t.data_ptr<float>();
+        int best = 0;
+        for (long i = 1; i < t.numel(); ++i) if (p[i] > p[best]) best = (int)i;
+        return best;
+      };
+      int id = ids.empty() ? 0 : ids.back();
+      for (int i = 0; i < 8; ++i) id = greedy(id);   // warm-up
+      auto t0 = std::chrono::steady_clock::now();
+      for (int i = 0; i < bench; ++i) id = greedy(id);
+      auto t1 = std::chrono::steady_clock::now();
+      std::printf("ms_per_token %.6f\n", std::chrono::duration<double, std::milli>(t1 - t0).count() / bench);
+    }
     if (std::getenv("FR_REF_STATE")) model.SaveStateFile(std::getenv("FR_REF_STATE"));
   } catch (const std::exception &e) {
     std::fprintf(stderr, "error: %s\n", e.what());
