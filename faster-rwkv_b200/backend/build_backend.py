@@ -6,7 +6,7 @@
 The reference sources are compiled where they lie (FR_REFERENCE_DIR, default /root/reference) with
 -DFR_ENABLE_CUDA; kernels/cuda/* is left out (this backend replaces it).  registry_backend.o is linked last so
 that its registrations for Device::kCUDA win over def::init_model / def::ModelForward (kernels/registry.h:17-19).
-msgpack-c is not available offline; oracle/compat/msgpack.hpp stands in for it in this container.
+msgpack-c is not available offline; backend/compat/msgpack.hpp stands in for it in this container.
 """
 import glob
 import os
@@ -29,10 +29,10 @@ def build(force: bool = False) -> str:
     for d in ("kernels/cpu", "kernels/default", "kernels/shape"):
         srcs += sorted(glob.glob(os.path.join(REF, d, "*.cpp")))
     srcs.append(os.path.join(REF, "kernels/export-ncnn/kernels.cpp"))
-    srcs.append(os.path.join(ROOT, "oracle", "ref", "ref_driver.cpp"))
+    srcs.append(os.path.join(HERE, "fr_run.cpp"))
     srcs.append(os.path.join(HERE, "registry_backend.cpp"))      # last: its registrations must win
     lib = os.path.join(os.path.dirname(HERE), "csrc", "libfr_b200.so")
-    deps = srcs + [os.path.join(ROOT, "include", "fr_b200.h"), os.path.join(ROOT, "oracle", "compat", "msgpack.hpp")]
+    deps = srcs + [os.path.join(ROOT, "include", "fr_b200.h"), os.path.join(HERE, "compat", "msgpack.hpp")]
     newest = max(os.path.getmtime(s) for s in deps)
     if not force and os.path.exists(exe) and os.path.getmtime(exe) >= max(newest, os.path.getmtime(lib)):
         return exe
@@ -42,7 +42,7 @@ def build(force: bool = False) -> str:
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < newest:
             cmd = ["g++", "-std=c++17", "-O2", "-march=x86-64-v3", "-w", "-include", "immintrin.h", "-DFR_ENABLE_CUDA",
-                   "-I", os.path.join(ROOT, "oracle", "compat"), "-I", REF, "-I", os.path.join(CUDA, "include"),
+                   "-I", os.path.join(HERE, "compat"), "-I", REF, "-I", os.path.join(CUDA, "include"),
                    "-c", s, "-o", o]
             procs.append((s, subprocess.Popen(cmd)))
     for s, p in procs:

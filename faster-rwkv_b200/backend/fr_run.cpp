@@ -1,5 +1,5 @@
 // Runs the reference's rwkv::Model on a `.fr` file and dumps the logits of every step as raw float32.
-// TEST INFRASTRUCTURE ONLY.  usage: fr_ref_run <model.fr> <strategy> <out.bin> [--seq] id id id ...
+// usage: fr_run <model.fr> <strategy> <out.bin> [--seq] id id id ...
 // Without --seq every id goes through Model::Run(int) (model.cpp:205); with --seq all ids go through
 // Model::Run(vector) once (model.cpp:188-203) and only the last logits are written.
 // --bench N: after the ids, N greedy tokens through Model::Run(int) (host argmax, as bench_model.cpp:5-10 times

@@ -168,6 +168,21 @@ def to_file_dtypes(shape: Shape, master: Dict[str, np.ndarray], dtype: str) -> D
     return out
 
 
+def fp16_exact_pair(shape: Shape, master: Dict[str, np.ndarray]):
+    """(fp16 file tensors, fp32 file tensors) that describe the SAME model exactly: the fp32 set is the fp16
+    set widened, with the 2**(layer//6) pre-division of att.output / ffn.value undone (exact: a power of two).
+    An fp32 strategy without the x/2 rescale on the second set and the fp16 strategy on the first then
+    multiply by identical weight values."""
+    f16 = to_file_dtypes(shape, master, "fp16")
+    f32 = {}
+    for k, v in f16.items():
+        w = v.astype(np.float32)
+        if k.endswith(("att.output.weight", "ffn.value.weight")):
+            w = w * np.float32(2 ** (int(k.split(".")[1]) // 6))
+        f32[k] = w
+    return f16, f32
+
+
 def write_fr(path: str, shape: Shape, tensors: Dict[str, np.ndarray]) -> None:
     """Write the msgpack container of tools/convert_weight.py:9-55."""
     def pack(x: np.ndarray) -> dict:

@@ -3,8 +3,8 @@
 Outputs go to oracle/_ref/ only (git-ignored, shipped to the GPU box as built files):
   fr_ref_run   rwkv::Model driver: reference model.cpp, tensor.cpp, utils.cpp, kernels/cpu/*,
                kernels/default/*, kernels/shape/*, kernels/export-ncnn/kernels.cpp  +  oracle/ref/cpu_prims.cpp
-               (the fp32 CPU primitives the reference lacks)  +  oracle/ref/ref_driver.cpp
-msgpack-c (a FetchContent dependency of the reference) is replaced by oracle/compat/msgpack.hpp.
+               (the fp32 CPU primitives the reference lacks)  +  faster-rwkv_b200/backend/fr_run.cpp
+msgpack-c (a FetchContent dependency of the reference) is replaced by faster-rwkv_b200/backend/compat/msgpack.hpp.
 The reference's CMake build is not run.  TEST INFRASTRUCTURE ONLY.
 """
 import glob
@@ -13,6 +13,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+BACKEND = os.path.join(os.path.dirname(HERE), "faster-rwkv_b200", "backend")   # msgpack stand-in + the shared driver
 REF = os.environ.get("FR_REFERENCE_DIR", "/root/reference")
 OUT = os.path.join(HERE, "_ref")
 
@@ -26,8 +27,8 @@ def build(force: bool = False) -> str:
     for d in ("kernels/cpu", "kernels/default", "kernels/shape"):
         srcs += sorted(glob.glob(os.path.join(REF, d, "*.cpp")))
     srcs.append(os.path.join(REF, "kernels/export-ncnn/kernels.cpp"))
-    srcs += [os.path.join(HERE, "ref", "cpu_prims.cpp"), os.path.join(HERE, "ref", "ref_driver.cpp")]
-    newest = max(os.path.getmtime(s) for s in srcs + [os.path.join(HERE, "compat", "msgpack.hpp")])
+    srcs += [os.path.join(HERE, "ref", "cpu_prims.cpp"), os.path.join(BACKEND, "fr_run.cpp")]
+    newest = max(os.path.getmtime(s) for s in srcs + [os.path.join(BACKEND, "compat", "msgpack.hpp")])
     if not force and os.path.exists(exe) and os.path.getmtime(exe) >= newest:
         return exe
     objs, procs = [], []
@@ -35,7 +36,7 @@ def build(force: bool = False) -> str:
         o = os.path.join(OUT, os.path.relpath(s, "/").replace("/", "_").replace(".cpp", ".o"))
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < newest:
-            cmd = ["g++", "-std=c++17", "-O2", "-march=x86-64-v3", "-w", "-include", "immintrin.h", "-I", os.path.join(HERE, "compat"), "-I", REF,
+            cmd = ["g++", "-std=c++17", "-O2", "-march=x86-64-v3", "-w", "-include", "immintrin.h", "-I", os.path.join(BACKEND, "compat"), "-I", REF,
                    "-c", s, "-o", o]
             procs.append((s, subprocess.Popen(cmd)))
     for s, p in procs:
@@ -58,8 +59,8 @@ def build_cuda(force: bool = False) -> str:
     srcs += sorted(glob.glob(os.path.join(REF, "kernels/cuda", "*.cpp")))
     srcs += sorted(glob.glob(os.path.join(REF, "kernels/cuda", "*.cu")))
     srcs += sorted(glob.glob(os.path.join(REF, "kernels/cuda", "activations", "*.cu")))
-    srcs.append(os.path.join(HERE, "ref", "ref_driver.cpp"))
-    newest = max(os.path.getmtime(s) for s in srcs + [os.path.join(HERE, "compat", "msgpack.hpp")])
+    srcs.append(os.path.join(BACKEND, "fr_run.cpp"))
+    newest = max(os.path.getmtime(s) for s in srcs + [os.path.join(BACKEND, "compat", "msgpack.hpp")])
     if not force and os.path.exists(exe) and os.path.getmtime(exe) >= newest:
         return exe
     objs, procs = [], []
@@ -69,10 +70,10 @@ def build_cuda(force: bool = False) -> str:
         if force or not os.path.exists(o) or os.path.getmtime(o) < newest:
             if s.endswith(".cu"):
                 cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O2", "-w", "-DFR_ENABLE_CUDA",
-                       "-I", os.path.join(HERE, "compat"), "-I", REF, "-c", s, "-o", o]
+                       "-I", os.path.join(BACKEND, "compat"), "-I", REF, "-c", s, "-o", o]
             else:
                 cmd = ["g++", "-std=c++17", "-O2", "-march=x86-64-v3", "-w", "-include", "immintrin.h", "-DFR_ENABLE_CUDA",
-                       "-I", os.path.join(HERE, "compat"), "-I", REF, "-I", os.path.join(cuda, "include"), "-c", s, "-o", o]
+                       "-I", os.path.join(BACKEND, "compat"), "-I", REF, "-I", os.path.join(cuda, "include"), "-c", s, "-o", o]
             procs.append((s, subprocess.Popen(cmd)))
     for s, p in procs:
         if p.wait() != 0:

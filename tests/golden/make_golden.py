@@ -33,7 +33,8 @@ def main():
     with tempfile.TemporaryDirectory() as tmp:
         for name, seed, n in CASES:
             shape = synth.SHAPES[name]
-            tensors = synth.to_file_dtypes(shape, synth.generate(shape, seed=seed, ln_random=True), "fp32")
+            # weights on the fp16 grid, so that the same model can also be given to the "cuda fp16" strategy exactly
+            _, tensors = synth.fp16_exact_pair(shape, synth.generate(shape, seed=seed, ln_random=True))
             fr = os.path.join(tmp, name + ".fr")
             synth.write_fr(fr, shape, tensors)
             ids = synth.token_ids(shape, n, seed=seed)

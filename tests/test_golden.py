@@ -21,7 +21,7 @@ def _load(name):
 def test_oracle_reproduces_reference_golden(orc, synth, name):
     seed, ids, want = _load(name)
     shape = synth.SHAPES[name]
-    tensors = synth.to_file_dtypes(shape, synth.generate(shape, seed=seed, ln_random=True), "fp32")
+    _, tensors = synth.fp16_exact_pair(shape, synth.generate(shape, seed=seed, ln_random=True))
     # the golden files come from kernels/default/att.cpp, which feeds the v5.1/5.2 gate with xx (att.cpp:101)
     m = orc.OracleModel(shape, tensors, synth.param_names(shape), gate_from_xx=True)
     got = np.stack([m.run(int(t)) for t in ids])
@@ -36,7 +36,7 @@ def test_cuda_gate_convention_differs_only_for_gated_versions(orc, synth):
     for name, differs in (("tiny4", False), ("tiny50", False), ("tiny52", True)):
         seed, ids, _ = _load(name)
         shape = synth.SHAPES[name]
-        t = synth.to_file_dtypes(shape, synth.generate(shape, seed=seed, ln_random=True), "fp32")
+        _, t = synth.fp16_exact_pair(shape, synth.generate(shape, seed=seed, ln_random=True))
         a = orc.OracleModel(shape, t, synth.param_names(shape), gate_from_xx=True)
         b = orc.OracleModel(shape, t, synth.param_names(shape), gate_from_xx=False)
         # the shift state is zero at the first token, where gx == xx * mix_g: compare the second token
