@@ -49,6 +49,11 @@ def algorithmic_bytes(shape, fmt: str) -> int:
     return P // 2 + 2 * (P // 32)
 
 
+# DRAM bytes per decode_kernel launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture summarised
+# in profiles/decode_kernel_c1_fp16_launch_list.md; other workloads have no capture yet.
+MEASURED_TRAFFIC = {("c1", "fp16", 1): 2_893_527_000}
+
+
 def measured_peak_gbs():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -335,7 +340,7 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     achieved = algo * K / (ms_max * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_kind, "kernel": "decode_kernel (persistent, one launch per token)",
+                "traffic": MEASURED_TRAFFIC.get((args.workload, args.weights, B)), "peak_source": peak_kind, "kernel": "decode_kernel (persistent, one launch per token)",
                 "algorithmic_bytes_per_launch": algo}
 
     variants = {}
