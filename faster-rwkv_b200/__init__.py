@@ -73,6 +73,8 @@ SIGNATURES = {
     "fr_b200_dequantize_int4": (_i, [_vp, _vp, _i, _i, _vp, _i]),
     "fr_b200_unpack_matrix": (_i, [_vp, ctypes.c_char_p, _vp, _i, _i]),
     "fr_b200_matvec": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i]),
+    "fr_b200_matvec_noalloc": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp]),
+    "fr_b200_noalloc_last_error": (ctypes.c_char_p, []),
     "fr_b200_get_info": (_i, [_vp, ctypes.POINTER(Info)]),
     "fr_b200_decode_profile": (_i, [_vp, _vp, _i, _vp, _i]),
     "fr_b200_strerror": (ctypes.c_char_p, [_i]),

@@ -140,6 +140,24 @@ int fr_b200_unpack_matrix(fr_b200_model *m, const char *name, float *W, int K, i
 int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float *x, int batch, float *y,
                    int device);
 
+/* The same matvec for callers that are not allowed to allocate (no counterpart in the reference; it allocates
+ * through its caching allocator on every op, kernels/cuda/allocator.cpp:47-479).  Meant for hosts that fix their
+ * GPU memory budget up front — a serving process whose execute callback must not call cudaMalloc, which stalls the
+ * whole device and may fail once a framework pool owns the memory, or a latency-bound loop.  All scratch (the
+ * converted matrix, the packed tiles, scales, padded output, descriptor) sits in a fixed 4.7 MiB array inside the
+ * library image, present on every GPU that loads the library until the process ends.
+ *   - W [K,N], x [batch,K], y [batch,N]: fp32 DEVICE pointers on `device`; nothing is allocated, no
+ *     cudaMalloc / cudaFree / pool routine is called.
+ *   - limits: K a multiple of 64, K <= 8192, N <= 16384, ceil16(N) * K <= 1,048,576, batch <= 8; larger inputs
+ *     return FR_B200_E_UNSUPPORTED with the reason in fr_b200_noalloc_last_error().
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make it before any
+ *     stream capture begins.
+ *   - every call reuses the one array: calls whose GPU work can overlap race; serialise them.
+ * Synchronises `stream` before returning. */
+int fr_b200_matvec_noalloc(const float *W, int K, int N, int weight_format, const float *x, int batch, float *y,
+                           int device, void *stream);
+const char *fr_b200_noalloc_last_error(void);
+
 /* ---- introspection ---- */
 typedef struct fr_b200_info {
   int n_ctas, n_threads, smem_bytes, n_stages, stage_bytes, n_phases;
