@@ -64,7 +64,8 @@ struct fr_b200_model {
   LayerDev *d_layers = nullptr;
   PhaseDev *d_phases = nullptr;
   uint8_t *h_out = nullptr;      // pinned mirror of d_out
-  int32_t *d_hist = nullptr;     size_t hist_n = 0;   // sampled ids of decode_greedy
+  unsigned long long *d_hist = nullptr; size_t hist_n = 0;   // packed arg-max words of decode_greedy, [tokens][batch]
+  unsigned long long *d_amax = nullptr;   // packed arg-max words of a single decode, [max_batch]
   // scratch for uploads
   void *d_scratch[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t scratch_bytes[4] = {0, 0, 0, 0};
@@ -333,6 +334,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * 8);
   if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * 8);
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
+  if (!rc) rc = alloc((void **)&m->d_amax, (size_t)B * 8);
   if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
   if (!rc) rc = alloc((void **)&m->d_phases, sizeof(PhaseDev) * m->phases.size());
   if (!rc && cudaMallocHost((void **)&m->h_out, m->out_bytes()) != cudaSuccess) rc = fail(FR_B200_E_NOMEM, "cudaMallocHost failed");
@@ -354,7 +356,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   cudaSetDevice(m->device);
   free_scratch(m);
   void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_rwkv, m->d_kk, m->d_rr,
-                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases};
+                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax};
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);
@@ -483,8 +485,8 @@ int fr_b200_finalize(fr_b200_model *m) {
   return fr_b200_state_reset(m, -1);
 }
 
-static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t *ids_dev, int batch, cudaStream_t st,
-                       bool want_argmax, unsigned long long *prof = nullptr) {
+static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned long long *ids_packed, int batch,
+                       cudaStream_t st, unsigned long long *amax, unsigned long long *prof = nullptr) {
   DecodeParams p;
   memset(&p, 0, sizeof(p));
   p.version = m->cfg.version == FR_B200_V4 ? 4 : m->cfg.version;
@@ -500,7 +502,8 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t 
       if (ids_host[b] < 0 || ids_host[b] >= m->V) return fail(FR_B200_E_ARG, "token id out of range");
       p.ids_val[b] = ids_host[b];
     }
-  p.ids_dev = ids_dev;
+  p.ids_packed = ids_packed;
+  p.amax = amax;
   p.emb = m->d_emb; p.emb_f32 = m->emb_dtype == FR_B200_T_F32; p.layers = m->d_layers; p.phases = m->d_phases;
   p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
   p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
@@ -521,10 +524,6 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const int32_t 
   m->launches++;
   m->seq += (unsigned)m->phases.size();
   for (int b = 0; b < batch; ++b) m->par[b] ^= 1u;
-  if (want_argmax) {
-    CU(launch_argmax(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), st));
-    m->launches++;
-  }
   return 0;
 }
 
@@ -534,8 +533,13 @@ int fr_b200_decode(fr_b200_model *m, const int32_t *ids, int batch, float *logit
   if (batch < 1 || batch > m->cfg.max_batch) return fail(FR_B200_E_ARG, "batch must be 1..max_batch");
   CU(cudaSetDevice(m->device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int rc = decode_impl(m, ids, nullptr, batch, st, argmax != nullptr);
+  if (argmax) CU(cudaMemsetAsync(m->d_amax, 0, (size_t)batch * 8, st));
+  int rc = decode_impl(m, ids, nullptr, batch, st, argmax ? m->d_amax : nullptr);
   if (rc) return rc;
+  if (argmax) {
+    CU(launch_unpack_ids(m->d_amax, batch, m->out_argmax(), st));
+    m->launches++;
+  }
   const bool lh = logits && is_host_ptr(logits), ah = argmax && is_host_ptr(argmax);
   if (logits && !lh)
     CU(cudaMemcpy2DAsync(logits, (size_t)m->V * 4, m->d_out, (size_t)m->Vpad * 4, (size_t)m->V * 4, batch, cudaMemcpyDeviceToDevice, st));
@@ -569,23 +573,27 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
     CU(cudaStreamSynchronize(st));
     if (m->d_hist) cudaFree(m->d_hist);
     m->d_hist = nullptr; m->hist_n = 0;
-    CU(cudaMalloc((void **)&m->d_hist, need * 4));
+    CU(cudaMalloc((void **)&m->d_hist, need * 12));
     m->hist_n = need;
   }
+  // one packed arg-max word per (token, stream), all cleared up front; token t+1 reads its ids from row t
+  CU(cudaMemsetAsync(m->d_hist, 0, need * 8, st));
   for (int t = 0; t < n_tokens; ++t) {
-    int rc = decode_impl(m, t == 0 ? first_ids : nullptr, t == 0 ? nullptr : m->d_hist + (size_t)(t - 1) * batch, batch, st, false);
+    int rc = decode_impl(m, t == 0 ? first_ids : nullptr, t == 0 ? nullptr : m->d_hist + (size_t)(t - 1) * batch, batch, st,
+                         m->d_hist + (size_t)t * batch);
     if (rc) return rc;
-    CU(launch_argmax(m->d_out, batch, m->V, m->Vpad, m->d_hist + (size_t)t * batch, st));
-    m->launches++;
   }
+  int32_t *ids32 = reinterpret_cast<int32_t *>(m->d_hist + need);   // unpacked ids behind the packed words
+  CU(launch_unpack_ids(m->d_hist, (int)need, ids32, st));
+  m->launches++;
   if (is_host_ptr(out_ids)) {
-    CU(cudaMemcpyAsync(out_ids, m->d_hist, need * 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaMemcpyAsync(out_ids, ids32, need * 4, cudaMemcpyDeviceToHost, st));
     int status = 0;
     CU(cudaMemcpyAsync(&status, m->out_status(), 4, cudaMemcpyDeviceToHost, st));
     CU(cudaStreamSynchronize(st));
     return check_status(m, status);
   }
-  CU(cudaMemcpyAsync(out_ids, m->d_hist, need * 4, cudaMemcpyDeviceToDevice, st));
+  CU(cudaMemcpyAsync(out_ids, ids32, need * 4, cudaMemcpyDeviceToDevice, st));
   return FR_B200_OK;
 }
 
@@ -599,7 +607,7 @@ int fr_b200_decode_profile(fr_b200_model *m, const int32_t *ids, int batch, uint
   DevBuf buf;
   CU(buf.alloc((size_t)need * 8));
   CU(cudaMemset(buf.p, 0, (size_t)need * 8));
-  int rc = decode_impl(m, ids, nullptr, batch, 0, false, (unsigned long long *)buf.p);
+  int rc = decode_impl(m, ids, nullptr, batch, 0, nullptr, (unsigned long long *)buf.p);
   if (rc) return rc;
   CU(cudaDeviceSynchronize());
   CU(cudaMemcpy(stamps, buf.p, (size_t)need * 8, cudaMemcpyDeviceToHost));

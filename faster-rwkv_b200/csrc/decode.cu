@@ -34,6 +34,7 @@ struct Smem {
   volatile int *abort_flag;
   float *ln_red;     // [NW][2*MAX_B]
   float *red;        // [3][NW][RED_N] per-warp partial sums of the current row block
+  float *par;        // one-stream mode: LayerNorm parameters of the next LN phase, staged with cp.async (or null)
   __half *xs;        // operand vectors
   uint8_t *ring;
 };
@@ -44,22 +45,30 @@ template <int NB, int NT> __host__ __device__ constexpr int red_n() { return ROW
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-template <int NB, int NT>
-__host__ __device__ inline size_t smem_layout(int fmt, size_t xs_halfs, int n_stages, size_t *off_red, size_t *off_xs,
-                                              size_t *off_ring) {
-  size_t o = 1024;  // barriers + flags + LN scratch
-  *off_red = o;   o += sizeof(float) * 3 * NW * red_n<NB, NT>();
-  o = align_up(o, 128);
-  *off_xs = o;    o += xs_halfs * 2;
-  o = align_up(o, 1024);
-  *off_ring = o;  o += (size_t)n_stages * slot_bytes(fmt);
-  return o;
-}
+constexpr int XR = 2;        // float4 slots per thread that the one-stream LayerNorm keeps in registers
+constexpr int PAR_VECS = 7;  // staged per LN phase: gamma, beta, up to 4 mix vectors, the shift state
 
 __host__ __device__ inline size_t xs_halfs_needed(int C, int F, int version, int NB, int NT) {
   size_t a = (size_t)(version == 4 ? 3 : 4) * C;
   size_t b = F;
   return (a > b ? a : b) * NB * NT;
+}
+// one stream and a model narrow enough for the register-resident LayerNorm: parameters are staged in shared memory
+template <int NB, int NT> __host__ __device__ inline size_t par_bytes(int C) {
+  return (NB == 2 && (C >> 2) <= XR * NCONS) ? (size_t)PAR_VECS * C * 4 : 0;
+}
+
+template <int NB, int NT>
+__host__ __device__ inline size_t smem_layout(int fmt, int C, int F, int version, int n_stages, size_t *off_red,
+                                              size_t *off_par, size_t *off_xs, size_t *off_ring) {
+  size_t o = 1024;  // barriers + flags + LN scratch
+  *off_red = o;   o += sizeof(float) * 3 * NW * red_n<NB, NT>();
+  o = align_up(o, 128);
+  *off_par = o;   o += par_bytes<NB, NT>(C);
+  *off_xs = o;    o += xs_halfs_needed(C, F, version, NB, NT) * 2;
+  o = align_up(o, 1024);
+  *off_ring = o;  o += (size_t)n_stages * slot_bytes(fmt);
+  return o;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -167,11 +176,12 @@ struct Ctx {
   uint32_t parity;     // parity of the next full-barrier wait
   uint32_t slot_b;     // bytes per ring slot
   int prof_phase;
+  int par_phase;       // phase whose LayerNorm parameters sit in sm.par (-1: none)
   unsigned long long wait_ns;  // profiling: time thread 0 spent waiting for weight tiles in the current phase
 };
 
 __device__ __forceinline__ int token_id(const DecodeParams &p, int b) {
-  return p.ids_dev ? __ldcg(p.ids_dev + b) : p.ids_val[b];
+  return p.ids_packed ? (int)(0xffffffffu - (unsigned)__ldcg(p.ids_packed + b)) : p.ids_val[b];
 }
 __device__ __forceinline__ unsigned phase_tag(const DecodeParams &p, int pi) { return p.seq_base + (unsigned)pi + 1u; }
 
@@ -239,10 +249,16 @@ __device__ __forceinline__ float4 ex_wait4(Ctx &cx, const exch_t *src, unsigned 
 // still checks every tag.  Keeps 148 CTAs from hammering the whole vector while they wait.
 __device__ __forceinline__ void wait_sentinels(Ctx &cx, const exch_t *src, int K, unsigned tag) {
   const int per = K / ROWS, n = cx.p->B * per;
-  for (int idx = cx.tid; idx < n; idx += NCONS) {
-    const int b = idx / per, t = idx - b * per;
-    ex_wait1(cx, src + (size_t)b * K + (size_t)t * ROWS, tag);
-  }
+  Poll poll;
+  bool ok;
+  do {
+    ok = true;
+    for (int idx = cx.tid; idx < n; idx += NCONS) {
+      const int b = idx / per, t = idx - b * per;
+      float v;
+      ok = ex_try1(src + (size_t)b * K + (size_t)t * ROWS, tag, v) && ok;
+    }
+  } while (!ok && poll.keep_waiting(cx));
   bar_sync(BAR_CONS, NCONS);
 }
 
@@ -307,7 +323,6 @@ __device__ __forceinline__ float4 wait_x4(Ctx &cx, bool layer0, int b, int i4, u
   return ex_wait4(cx, p.x + (size_t)b * p.C + (size_t)i4 * 4, tag);
 }
 
-constexpr int XR = 2;   // float4 slots per thread that the one-stream LayerNorm keeps in registers
 
 // Element 4*i4.. of the residual stream of stream b without waiting: the embedding row at layer 0
 // (always there), else one attempt at the tagged words.
@@ -358,50 +373,88 @@ __device__ __forceinline__ void ln_emit(Ctx &cx, const PhaseDev &ph, int nvec, u
     store_act4(sx_wr + (size_t)b * p.state_stride, i4, p.act_fp16, xx);
 }
 
-// LayerNorm + token-shift mix for ONE stream of a model with n_embd <= 4 * XR * NCONS: the latency-critical
-// prologue of batch-1 decode.  All parameter loads are issued first (they miss L2: the weight stream evicts
-// them every token), then every thread polls its own slots of x plus the pivot element in one go, so a
-// round costs one memory round trip.  Statistics: shifted single pass, sums of (x - x[0]) and (x - x[0])^2.
-// nvec == 0: plain LayerNorm -> operand vector 0 (head).
-template <int NB, int NT>
-__device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, bool layer0, unsigned xtag, const float *ln_w,
-                                                const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
-                                                uint8_t *sx_wr, int sx_item0) {
+// What a LayerNorm phase reads besides the residual stream.
+struct LnArgs {
+  const float *ln_w, *ln_b;
+  const float *const *mix;
+  const uint8_t *sx_rd;
+  uint8_t *sx_wr;
+  int nvec, item0;
+  bool layer0;
+};
+__device__ __forceinline__ bool is_ln_phase(int kind) {
+  return kind == PH_ATT_KVR || kind == PH5_KVRG || kind == PH_FFN_KR || kind == PH_HEAD;
+}
+__device__ __forceinline__ LnArgs ln_args(const DecodeParams &p, const PhaseDev &ph) {
+  LnArgs a;
+  const int v5 = p.version != 4, par = (int)(p.par_mask & 1u);   // streams of one launch share the parity
+  a.ln_w = p.lnout_w; a.ln_b = p.lnout_b; a.mix = nullptr; a.sx_rd = nullptr; a.sx_wr = nullptr;
+  a.nvec = 0; a.item0 = 0; a.layer0 = false;
+  if (ph.kind == PH_HEAD) return a;
+  const LayerDev *ly = p.layers + ph.layer;
+  uint8_t *st0 = p.state + (size_t)ph.layer * p.layer_stride;   // stream 0
+  if (ph.kind == PH_FFN_KR) {
+    a.ln_w = ly->ln2_w; a.ln_b = ly->ln2_b; a.mix = ly->ffn_mix; a.nvec = 2; a.item0 = ph.split[0];
+    a.sx_rd = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par);
+    a.sx_wr = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par ^ 1);
+  } else {
+    a.ln_w = ly->ln1_w; a.ln_b = ly->ln1_b; a.mix = ly->att_mix;
+    a.nvec = p.version == 4 || p.version == 50 ? 3 : 4;
+    a.sx_rd = st0 + off_sx(p.C, p.act_fp16, par);
+    a.sx_wr = st0 + off_sx(p.C, p.act_fp16, par ^ 1);
+    a.layer0 = ph.layer == 0;
+  }
+  return a;
+}
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// Start copying an LN phase's parameters (and shift state) into sm.par.  Asynchronous: costs no registers and no
+// waiting; each thread copies exactly the slots it will read back itself, so cp.async.wait_all is all it needs.
+__device__ __forceinline__ void ln_stage_params(Ctx &cx, const LnArgs &a) {
   const DecodeParams &p = *cx.p;
   const int n4 = p.C >> 2;
-  // 1. wait cheaply: every thread polls one word of each of its slots (and nothing else) until it is there
-  if (!layer0) {
-#pragma unroll
-    for (int r = 0; r < XR; ++r) {
-      const int i4 = cx.tid + r * NCONS;
-      if (i4 < n4) ex_wait1(cx, p.x + (size_t)i4 * 4, xtag);
-    }
-  }
-  // 2. one round trip: x (all tags checked), the pivot element, and the parameters of the same channels
-  float4 gw[XR], gb[XR], mx[4][XR], sx[XR], xv[XR], pv;
-  bool ok = try_x4(p, layer0, 0, 0, xtag, pv);
+  float *par = cx.sm.par;
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
     const int i4 = cx.tid + r * NCONS;
     if (i4 < n4) {
-      ok = try_x4(p, layer0, 0, i4, xtag, xv[r]) && ok;
-      gw[r] = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4);
-      gb[r] = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4);
-#pragma unroll
-      for (int v = 0; v < 4; ++v)
-        if (v < nvec) mx[v][r] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4);
-      if (nvec > 0) sx[r] = load_act4(sx_rd, i4, p.act_fp16);
+      cp_async16(par + 0 * p.C + i4 * 4, a.ln_w + i4 * 4);
+      cp_async16(par + 1 * p.C + i4 * 4, a.ln_b + i4 * 4);
+      for (int v = 0; v < a.nvec; ++v) cp_async16(par + (2 + v) * p.C + i4 * 4, a.mix[v] + i4 * 4);
+      if (a.nvec > 0) {
+        if (p.act_fp16) cp_async8(reinterpret_cast<__half *>(par + 6 * p.C) + i4 * 4, reinterpret_cast<const __half *>(a.sx_rd) + i4 * 4);
+        else cp_async16(par + 6 * p.C + i4 * 4, reinterpret_cast<const float *>(a.sx_rd) + i4 * 4);
+      }
     }
   }
-  if (!ok) {
-    // a word of a slot lagged behind the one polled above: wait for exactly what is missing
-    pv = wait_x4(cx, layer0, 0, 0, xtag);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// LayerNorm + token-shift mix for ONE stream of a model with n_embd <= 4 * XR * NCONS: the latency-critical
+// prologue of batch-1 decode.  The parameters were staged into shared memory ahead of time (ln_stage_params), so
+// the only global round trip left is the one that fetches x: every thread polls its own slots plus the pivot
+// element together until all tags match.  Statistics: shifted single pass, sums of (x - x[0]) and (x - x[0])^2.
+// nvec == 0: plain LayerNorm -> operand vector 0 (head).
+template <int NB, int NT>
+__device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, const LnArgs &a, unsigned xtag) {
+  const DecodeParams &p = *cx.p;
+  const int n4 = p.C >> 2;
+  float4 xv[XR], pv;
+  Poll poll;
+  bool ok;
+  do {
+    ok = try_x4(p, a.layer0, 0, 0, xtag, pv);
 #pragma unroll
     for (int r = 0; r < XR; ++r) {
       const int i4 = cx.tid + r * NCONS;
-      if (i4 < n4) xv[r] = wait_x4(cx, layer0, 0, i4, xtag);
+      if (i4 < n4) ok = try_x4(p, a.layer0, 0, i4, xtag, xv[r]) && ok;
     }
-  }
+  } while (!ok && poll.keep_waiting(cx));
   const float piv = pv.x;
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -419,21 +472,38 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, boo
     s2 += __shfl_xor_sync(0xffffffffu, s2, o);
   }
   if (cx.lane == 0) { cx.sm.ln_red[cx.warp * 2] = s1; cx.sm.ln_red[cx.warp * 2 + 1] = s2; }
+  asm volatile("cp.async.wait_all;" ::: "memory");   // this thread's staged parameters have landed
   bar_sync(BAR_CONS, NCONS);
-  float a = 0.f, c = 0.f;
+  float sa = 0.f, sc = 0.f;
 #pragma unroll
-  for (int w = 0; w < NW; ++w) { a += cx.sm.ln_red[w * 2]; c += cx.sm.ln_red[w * 2 + 1]; }
+  for (int w = 0; w < NW; ++w) { sa += cx.sm.ln_red[w * 2]; sc += cx.sm.ln_red[w * 2 + 1]; }
   const float inv = 1.f / (float)p.C;
-  const float m = a * inv;
-  float var = c * inv - m * m;
+  const float m = sa * inv;
+  float var = sc * inv - m * m;
   var = var > 0.f ? var : 0.f;
   const float mean = piv + m, rstd = rsqrtf(var + 1e-5f);
+  const float *par = cx.sm.par;
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
     const int i4 = cx.tid + r * NCONS;
     if (i4 < n4) {
-      const float4 mx4[4] = {mx[0][r], mx[1][r], mx[2][r], mx[3][r]};
-      ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4, 0, xv[r], mean, rstd, gw[r], gb[r], mx4, sx[r]);
+      const float4 gw = *reinterpret_cast<const float4 *>(par + 0 * p.C + i4 * 4);
+      const float4 gb = *reinterpret_cast<const float4 *>(par + 1 * p.C + i4 * 4);
+      float4 mx4[4], sx = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        if (v < a.nvec) mx4[v] = *reinterpret_cast<const float4 *>(par + (2 + v) * p.C + i4 * 4);
+      if (a.nvec > 0) {
+        if (p.act_fp16) {
+          const uint2 u = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(par + 6 * p.C) + i4 * 4);
+          const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+          const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+          sx = make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+          sx = *reinterpret_cast<const float4 *>(par + 6 * p.C + i4 * 4);
+        }
+      }
+      ln_emit<NB, NT>(cx, ph, a.nvec, a.sx_wr, a.item0, i4, 0, xv[r], mean, rstd, gw, gb, mx4, sx);
     }
   }
   bar_sync(BAR_CONS, NCONS);
@@ -517,13 +587,14 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, boo
 }
 
 template <int NB, int NT>
-__device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, bool layer0, unsigned xtag, const float *ln_w,
-                                            const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
-                                            uint8_t *sx_wr, int sx_item0) {
-  if (n_streams<NB, NT>() == 1 && (cx.p->C >> 2) <= XR * NCONS)
-    prologue_ln_one<NB, NT>(cx, ph, layer0, xtag, ln_w, ln_b, mix, nvec, sx_rd, sx_wr, sx_item0);
-  else
-    prologue_ln_mix<NB, NT>(cx, ph, layer0, xtag, ln_w, ln_b, mix, nvec, sx_rd, sx_wr, sx_item0);
+__device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, int pi, unsigned xtag) {
+  const LnArgs a = ln_args(*cx.p, ph);
+  if (cx.sm.par) {
+    if (cx.par_phase != pi) { ln_stage_params(cx, a); cx.par_phase = pi; }   // not staged ahead: do it now
+    prologue_ln_one<NB, NT>(cx, ph, a, xtag);
+  } else {
+    prologue_ln_mix<NB, NT>(cx, ph, a.layer0, xtag, a.ln_w, a.ln_b, a.mix, a.nvec, a.sx_rd, a.sx_wr, a.item0);
+  }
 }
 
 // exchange vector [B][K] written by phase `tag` -> operand vector 0.  Short vectors are polled directly,
@@ -532,7 +603,7 @@ __device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, bool la
 template <int NB, int NT>
 __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, unsigned tag) {
   constexpr int SB = n_streams<NB, NT>();
-  constexpr int VR = 4;   // slots polled together
+  constexpr int VR = 8;   // slots polled together
   const DecodeParams &p = *cx.p;
   const int n4 = K >> 2;
   const size_t plane = (size_t)K * NB;
@@ -757,6 +828,7 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
   const bool epi_thread = cx.tid < ROWS * SB && eb < p.B;
   const bool prof = p.prof != nullptr && cx.tid == 0;
   long long c_st = 0, c_bar = 0, c_epi = 0, c_n = 0;
+  unsigned long long best = 0;   // head phase: packed arg-max over this thread's logits
   for (int it = first; it < ph.n_items; it += cx.G) {
     const long long ck0 = prof ? clock64() : 0;
     EpiIn epi_in;
@@ -829,11 +901,18 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
         }
       }
       epilogue(p, ph, tag, it, erow, eb, val, epi_in);
+      if (ph.kind == PH_HEAD && p.amax && it * ROWS + erow < p.V) {
+        unsigned u = __float_as_uint(val[0]);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        const unsigned long long w = ((unsigned long long)u << 32) | (0xffffffffu - (unsigned)(it * ROWS + erow));
+        best = w > best ? w : best;
+      }
     }
     // the partial sums are read: the next row block may overwrite them
     bar_sync(BAR_CONS, NCONS);
     if (prof) { const long long ck3 = clock64(); c_st += ck1 - ck0; c_bar += ck2 - ck1; c_epi += ck3 - ck2; ++c_n; }
   }
+  if (ph.kind == PH_HEAD && p.amax && epi_thread && best) atomicMax(p.amax + eb, best);
   if (prof && (ph.kind == PH_ATT_O || ph.kind == PH_FFN_V)) {
     p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 4] = c_st; p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 5] = c_bar; p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 6] = c_epi;
     p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 7] = c_n;
@@ -892,7 +971,6 @@ template <int FMT, int NB, int NT>
 __device__ __forceinline__ void consumer(Ctx &cx) {
   const DecodeParams &p = *cx.p;
   const bool prof = p.prof != nullptr && cx.tid == 0;
-  const int v5 = p.version != 4;
   for (int pi = 0; pi < p.n_phases; ++pi) {
     const PhaseDev ph = p.phases[pi];
     const int first = (cx.cta + cx.G - ph.rot) % cx.G;
@@ -901,32 +979,20 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
       continue;
     }
     if (first >= ph.n_items) continue;   // no row block here: nothing to read, nothing to write
+    // stage the LayerNorm parameters of the next phase while this one runs (sm.par is free: this phase is not LN)
+    if (cx.sm.par && !is_ln_phase(ph.kind) && pi + 1 < p.n_phases) {
+      const PhaseDev nx = p.phases[pi + 1];
+      if (is_ln_phase(nx.kind) && (cx.cta + cx.G - nx.rot) % cx.G < nx.n_items) {
+        ln_stage_params(cx, ln_args(p, nx));
+        cx.par_phase = pi + 1;
+      }
+    }
     cx.prof_phase = pi;
     if (prof) p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 0] = globaltimer_ns();
     const bool layered = ph.kind != PH_HEAD && ph.kind != PH_MATVEC;
     const LayerDev *ly = layered ? p.layers + ph.layer : nullptr;
-    uint8_t *st0 = p.state + (size_t)(layered ? ph.layer : 0) * p.layer_stride;  // stream 0
-    // the streams of one launch advance together, so they share the parity of stream 0
-    const int par = (int)(p.par_mask & 1u);
-    if (ph.kind == PH_ATT_KVR || ph.kind == PH5_KVRG || ph.kind == PH_FFN_KR || ph.kind == PH_HEAD) {
-      // one LayerNorm prologue, three parameter sets
-      const float *ln_w = p.lnout_w, *ln_b = p.lnout_b;
-      const float *const *mix = nullptr;
-      const uint8_t *sx_rd = nullptr;
-      uint8_t *sx_wr = nullptr;
-      int nvec = 0, item0 = 0;
-      if (ph.kind == PH_FFN_KR) {
-        ln_w = ly->ln2_w; ln_b = ly->ln2_b; mix = ly->ffn_mix; nvec = 2; item0 = ph.split[0];
-        sx_rd = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par);
-        sx_wr = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par ^ 1);
-      } else if (ph.kind != PH_HEAD) {
-        ln_w = ly->ln1_w; ln_b = ly->ln1_b; mix = ly->att_mix;
-        nvec = p.version == 4 || p.version == 50 ? 3 : 4;
-        sx_rd = st0 + off_sx(p.C, p.act_fp16, par);
-        sx_wr = st0 + off_sx(p.C, p.act_fp16, par ^ 1);
-      }
-      const bool layer0 = ph.layer == 0 && (ph.kind == PH_ATT_KVR || ph.kind == PH5_KVRG);
-      prologue_ln<NB, NT>(cx, ph, layer0, phase_tag(p, pi - 1), ln_w, ln_b, mix, nvec, sx_rd, sx_wr, item0);
+    if (is_ln_phase(ph.kind)) {
+      prologue_ln<NB, NT>(cx, ph, pi, phase_tag(p, pi - 1));
     } else if (ph.kind == PH_ATT_O) {
       if (p.version == 4) prologue_vec<NB, NT>(cx, p.rwkv, p.C, phase_tag(p, pi - 1));
       else prologue_gn_gate<NB, NT>(cx, *ly, phase_tag(p, pi - 1), phase_tag(p, pi - 2));
@@ -1044,8 +1110,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   cx.cta = blockIdx.x; cx.G = gridDim.x;
   cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0;
   cx.slot_b = slot_bytes(FMT);
-  size_t o_red, o_xs, o_ring;
-  smem_layout<NB, NT>(FMT, xs_halfs_needed(p.C, p.F, p.version, NB, NT), p.n_stages, &o_red, &o_xs, &o_ring);
+  size_t o_red, o_par, o_xs, o_ring;
+  smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, &o_red, &o_par, &o_xs, &o_ring);
+  cx.sm.par = par_bytes<NB, NT>(p.C) ? reinterpret_cast<float *>(smem + o_par) : nullptr;
+  cx.par_phase = -1;
   cx.sm.full = reinterpret_cast<uint64_t *>(smem);
   cx.sm.empty = cx.sm.full + MAX_STAGES;
   cx.sm.abort_flag = reinterpret_cast<volatile int *>(smem + 256);
@@ -1076,36 +1144,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   }
 }
 
-__global__ void argmax_kernel(const float *logits, int V, int Vpad, int32_t *out) {
-  const float *row = logits + (size_t)blockIdx.x * Vpad;
-  float best = -INFINITY;
-  int bi = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best) { best = v; bi = i; }
-  }
-  __shared__ float sv[32];
-  __shared__ int si[32];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-  }
-  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    const int nw = blockDim.x >> 5;
-    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
-    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (threadIdx.x == 0) out[blockIdx.x] = bi;
-  }
+__global__ void unpack_ids_kernel(const unsigned long long *packed, int n, int32_t *out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = (int32_t)(0xffffffffu - (unsigned)packed[i]);
 }
 
 template <int FMT, int NB, int NT>
@@ -1133,11 +1174,11 @@ cudaError_t max_grid_t(size_t smem, int device, int *grid) {
 
 // mode: 0 = one stream, 1 = up to 4 streams, 2 = up to 8 streams
 size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages) {
-  size_t a, b, c;
+  size_t a, b, c, d;
   switch (mode) {
-    case 0: return smem_layout<2, 1>(fmt, xs_halfs_needed(C, F, version, 2, 1), n_stages, &a, &b, &c);
-    case 1: return smem_layout<8, 1>(fmt, xs_halfs_needed(C, F, version, 8, 1), n_stages, &a, &b, &c);
-    default: return smem_layout<8, 2>(fmt, xs_halfs_needed(C, F, version, 8, 2), n_stages, &a, &b, &c);
+    case 0: return smem_layout<2, 1>(fmt, C, F, version, n_stages, &a, &b, &c, &d);
+    case 1: return smem_layout<8, 1>(fmt, C, F, version, n_stages, &a, &b, &c, &d);
+    default: return smem_layout<8, 2>(fmt, C, F, version, n_stages, &a, &b, &c, &d);
   }
 }
 
@@ -1164,8 +1205,8 @@ cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *gri
   FRB_DISPATCH(max_grid_t, smem, device, grid)
 }
 
-cudaError_t launch_argmax(const float *logits, int B, int V, int Vpad, int32_t *out, cudaStream_t st) {
-  argmax_kernel<<<B, 1024, 0, st>>>(logits, V, Vpad, out);
+cudaError_t launch_unpack_ids(const unsigned long long *packed, int n, int32_t *out, cudaStream_t st) {
+  unpack_ids_kernel<<<(n + 255) / 256, 256, 0, st>>>(packed, n, out);
   return cudaGetLastError();
 }
 

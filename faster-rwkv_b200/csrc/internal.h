@@ -65,7 +65,8 @@ struct DecodeParams {
   unsigned seq_base;           // tag of phase pi of this launch = seq_base + pi + 1
   unsigned par_mask;           // bit b: which copy of the token-shift states stream b reads (it writes the other)
   int ids_val[MAX_B];
-  const int32_t *ids_dev;      // when non-null the ids are read from here
+  const unsigned long long *ids_packed;  // when non-null: ids are the packed arg-max words of the previous token
+  unsigned long long *amax;    // optional [B]: packed arg-max of this token's logits (zeroed by the host)
   const void *emb;             // [V][C], fp32 when emb_f32 else fp16 (the file's dtype)
   int emb_f32;
   const LayerDev *layers;
@@ -102,7 +103,9 @@ inline int decode_mode(int batch) { return batch == 1 ? 0 : batch <= 4 ? 1 : 2; 
 size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages);
 cudaError_t launch_decode(const DecodeParams &p, int mode, int grid, size_t smem, cudaStream_t st);
 cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *grid);
-cudaError_t launch_argmax(const float *logits, int B, int V, int Vpad, int32_t *out, cudaStream_t st);
+// packed arg-max word = {order-preserving image of the fp32 logit, 0xFFFFFFFF - index}: a 64-bit max picks the
+// largest logit and, among equals, the smallest index
+cudaError_t launch_unpack_ids(const unsigned long long *packed, int n, int32_t *out, cudaStream_t st);
 
 // quantise / pack (pack.cu); all pointers device
 cudaError_t launch_f16_to_f32(const __half *src, float *dst, size_t n, cudaStream_t st);
