@@ -58,6 +58,7 @@ struct fr_b200_model {
   uint8_t *d_state = nullptr;    size_t state_stride = 0, layer_stride = 0;
   exch_t *d_x = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;   // tagged exchange vectors
   exch_t *d_v5buf = nullptr;     // k5, v5, r5, g5, o5
+  int exch_batch = 0;            // streams the last launch wrote into the exchange vectors (0: clear them first)
   unsigned seq = 0;              // phases launched so far (tags continue across launches)
   unsigned par[MAX_B] = {0, 0, 0, 0, 0, 0, 0, 0};   // which copy of the token-shift states each slot reads next
   float *d_out = nullptr;        // [B][Vpad] logits, then [B] argmax ints, then status int
@@ -249,6 +250,7 @@ int check_status(fr_b200_model *m, int st) {
   if (st == 0) return 0;
   // a bounded wait gave up: clear the status word for the next launch
   cudaMemset(m->out_status(), 0, 4);
+  m->exch_batch = 0;   // exchange vectors may be half written
   return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(st) + ")");
 }
 
@@ -328,11 +330,11 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_rscale, m->rscale_n * 2);
   if (!rc) rc = alloc((void **)&m->d_vecs, m->vecs_n * 4);
   if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
-  if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * 8);
-  if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * 8);
-  if (!rc) rc = alloc((void **)&m->d_kk, (size_t)B * m->F * 8);
-  if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * 8);
-  if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * 8);
+  if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * sizeof(exch_t));
+  if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * sizeof(exch_t));
+  if (!rc) rc = alloc((void **)&m->d_kk, (size_t)B * m->F * sizeof(exch_t));
+  if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * sizeof(exch_t));
+  if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
   if (!rc) rc = alloc((void **)&m->d_amax, (size_t)B * 8);
   if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
@@ -343,9 +345,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   cudaMemset(m->d_rscale, 0, m->rscale_n * 2);
   cudaMemset(m->d_out, 0, m->out_bytes());
   // tag 0 is never expected by a reader
-  cudaMemset(m->d_x, 0, (size_t)B * m->C * 8); cudaMemset(m->d_rwkv, 0, (size_t)B * m->C * 8);
-  cudaMemset(m->d_kk, 0, (size_t)B * m->F * 8); cudaMemset(m->d_rr, 0, (size_t)B * m->C * 8);
-  cudaMemset(m->d_v5buf, 0, (size_t)5 * B * m->C * 8);
+  m->exch_batch = 0;   // the first launch clears the exchange vectors
   m->emb_rows_set.assign(m->V, 0);
   *out = m;
   return FR_B200_OK;
@@ -508,7 +508,18 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned
   p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
   p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
   p.x = m->d_x; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
-  p.seq_base = m->seq;
+  // Exchange words carry 8-bit tags: unambiguous only against the write just before them in the same slot.  Slots of
+  // streams the previous launch did not write, or words a failed launch left half written, could alias: start clean.
+  if (m->exch_batch != batch) {
+    const size_t B = m->cfg.max_batch;
+    CU(cudaMemsetAsync(m->d_x, 0, B * m->C * sizeof(exch_t), st));
+    CU(cudaMemsetAsync(m->d_rwkv, 0, B * m->C * sizeof(exch_t), st));
+    CU(cudaMemsetAsync(m->d_kk, 0, B * m->F * sizeof(exch_t), st));
+    CU(cudaMemsetAsync(m->d_rr, 0, B * m->C * sizeof(exch_t), st));
+    CU(cudaMemsetAsync(m->d_v5buf, 0, 5 * B * m->C * sizeof(exch_t), st));
+    m->exch_batch = batch;
+  }
+  p.seq_base = 255u + m->seq;
   p.par_mask = 0;
   for (int b = 0; b < batch; ++b) {
     if (m->par[b] != m->par[0]) return fail(FR_B200_E_STATE, "streams decoded together must have seen the same number of tokens since their last reset");
@@ -522,7 +533,7 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned
   p.l2_prefetch_bytes = m->l2_prefetch;
   CU(launch_decode(p, mode, m->grid, smem, st));
   m->launches++;
-  m->seq += (unsigned)m->phases.size();
+  m->seq = (m->seq + (unsigned)m->phases.size()) % 255u;
   for (int b = 0; b < batch; ++b) m->par[b] ^= 1u;
   return 0;
 }

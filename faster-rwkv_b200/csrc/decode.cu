@@ -183,33 +183,40 @@ struct Ctx {
 __device__ __forceinline__ int token_id(const DecodeParams &p, int b) {
   return p.ids_packed ? (int)(0xffffffffu - (unsigned)__ldcg(p.ids_packed + b)) : p.ids_val[b];
 }
-__device__ __forceinline__ unsigned phase_tag(const DecodeParams &p, int pi) { return p.seq_base + (unsigned)pi + 1u; }
+// 8-bit tag of phase pi of this launch, never 0 (a zeroed buffer matches no phase).  Two consecutive writes of
+// one exchange slot are a handful of phases apart, so their tags differ.
+__device__ __forceinline__ unsigned phase_tag(const DecodeParams &p, int pi) {
+  return 1u + (p.seq_base + (unsigned)pi) % 255u;
+}
 
 // ---- tagged exchange words ----------------------------------------------------------------------
+// One 32-bit word per value: the fp32 value rounded to 16 significant bits, its low 8 mantissa bits replaced
+// by the writer's phase tag.  A reader that sees its tag has the value; no second round trip, no fence.
 __device__ __forceinline__ void ex_store(exch_t *dst, float v, unsigned tag) {
-  const exch_t w = ((exch_t)tag << 32) | (exch_t)__float_as_uint(v);
-  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+  unsigned u = __float_as_uint(v);
+  u = ((u & 0x7f800000u) == 0x7f800000u ? u : u + 0x80u) & 0xffffff00u;   // round to nearest; inf / nan keep their class
+  asm volatile("st.relaxed.gpu.global.b32 [%0], %1;" ::"l"(dst), "r"(u | tag) : "memory");
 }
 __device__ __forceinline__ exch_t ex_load_raw(const exch_t *src) {
   exch_t w;
-  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+  asm volatile("ld.relaxed.gpu.global.b32 %0, [%1];" : "=r"(w) : "l"(src) : "memory");
   return w;
 }
+__device__ __forceinline__ float ex_value(exch_t w) { return __uint_as_float(w & 0xffffff00u); }
+__device__ __forceinline__ bool ex_ready(exch_t w, unsigned tag) { return (w & 0xffu) == tag; }
 // one word; false while the writer has not stored it yet
 __device__ __forceinline__ bool ex_try1(const exch_t *src, unsigned tag, float &v) {
   const exch_t w = ex_load_raw(src);
-  v = __uint_as_float((unsigned)w);
-  return (unsigned)(w >> 32) == tag;
+  v = ex_value(w);
+  return ex_ready(w, tag);
 }
-// four consecutive words (32-byte aligned)
+// four consecutive words (16-byte aligned)
 __device__ __forceinline__ bool ex_try4(const exch_t *src, unsigned tag, float4 &v) {
   exch_t a, b, c, d;
-  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
-  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(c), "=l"(d) : "l"(src + 2) : "memory");
-  v = make_float4(__uint_as_float((unsigned)a), __uint_as_float((unsigned)b), __uint_as_float((unsigned)c),
-                  __uint_as_float((unsigned)d));
-  return (unsigned)(a >> 32) == tag && (unsigned)(b >> 32) == tag && (unsigned)(c >> 32) == tag &&
-         (unsigned)(d >> 32) == tag;
+  asm volatile("ld.relaxed.gpu.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(src) : "memory");
+  v = make_float4(ex_value(a), ex_value(b), ex_value(c), ex_value(d));
+  // all four tags equal `tag`: compare the tag bytes in one go
+  return ((a & 0xffu) | ((b & 0xffu) << 8) | ((c & 0xffu) << 16) | (d << 24)) == tag * 0x01010101u;
 }
 
 // Bounded polling: gives up after WAIT_LIMIT_NS (or as soon as another thread of the CTA gave up).
@@ -446,15 +453,16 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   const int n4 = p.C >> 2;
   float4 xv[XR], pv;
   Poll poll;
-  bool ok;
-  do {
-    ok = try_x4(p, a.layer0, 0, 0, xtag, pv);
+  unsigned pending = 1u << XR;   // bit XR: the pivot; bits 0..XR-1: this thread's slots still missing
 #pragma unroll
-    for (int r = 0; r < XR; ++r) {
-      const int i4 = cx.tid + r * NCONS;
-      if (i4 < n4) ok = try_x4(p, a.layer0, 0, i4, xtag, xv[r]) && ok;
-    }
-  } while (!ok && poll.keep_waiting(cx));
+  for (int r = 0; r < XR; ++r)
+    if (cx.tid + r * NCONS < n4) pending |= 1u << r;
+  do {
+    if ((pending >> XR) && try_x4(p, a.layer0, 0, 0, xtag, pv)) pending &= ~(1u << XR);
+#pragma unroll
+    for (int r = 0; r < XR; ++r)
+      if ((pending & (1u << r)) && try_x4(p, a.layer0, 0, cx.tid + r * NCONS, xtag, xv[r])) pending &= ~(1u << r);
+  } while (pending && poll.keep_waiting(cx));
   const float piv = pv.x;
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -612,18 +620,20 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
   for (int base = cx.tid; base < total; base += VR * NCONS) {
     float4 v[VR];
     Poll poll;
-    bool ok;
+    unsigned pending = 0;   // slots whose words have not all arrived: only those are asked for again
+#pragma unroll
+    for (int r = 0; r < VR; ++r)
+      if (base + r * NCONS < total) pending |= 1u << r;
     do {
-      ok = true;
 #pragma unroll
       for (int r = 0; r < VR; ++r) {
-        const int s = base + r * NCONS;
-        if (s < total) {
+        if (pending & (1u << r)) {
+          const int s = base + r * NCONS;
           const int b = s / n4, i4 = s - b * n4;
-          ok = ex_try4(src + (size_t)b * K + (size_t)i4 * 4, tag, v[r]) && ok;
+          if (ex_try4(src + (size_t)b * K + (size_t)i4 * 4, tag, v[r])) pending &= ~(1u << r);
         }
       }
-    } while (!ok && poll.keep_waiting(cx));
+    } while (pending && poll.keep_waiting(cx));
 #pragma unroll
     for (int r = 0; r < VR; ++r) {
       const int s = base + r * NCONS;
@@ -701,6 +711,7 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly, un
 // latency hides behind the wait for the weight tiles.
 struct EpiIn {
   float a, b, c, d, e;
+  exch_t wa, wb;     // exchange words requested early; their tags are checked when the epilogue uses them
   float rscale[3];
 };
 
@@ -729,13 +740,13 @@ __device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, c
       if (ph.layer == 0)
         in.a = p.emb_f32 ? __ldg(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * C + c)
                          : __half2float(reinterpret_cast<const __half *>(p.emb)[(size_t)token_id(p, b) * C + c]);
-      else in.a = ex_wait1(cx, p.x + (size_t)b * C + c, phase_tag(p, pi - (p.version == 4 ? 2 : 3)));
+      else in.wa = ex_load_raw(p.x + (size_t)b * C + c);
       break;
     }
     case PH_FFN_V: {
       const int c = it * ROWS + row;
-      in.a = ex_wait1(cx, p.x + (size_t)b * C + c, phase_tag(p, pi - 2));   // written by the output projection
-      in.b = ex_wait1(cx, p.rr + (size_t)b * C + c, phase_tag(p, pi - 1));  // written by the ffn receptance rows
+      in.wa = ex_load_raw(p.x + (size_t)b * C + c);    // written by the output projection
+      in.wb = ex_load_raw(p.rr + (size_t)b * C + c);   // written by the ffn receptance rows of the phase before
       break;
     }
     default: break;
@@ -744,8 +755,14 @@ __device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, c
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
-__device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &ph, unsigned tag, int it, int row, int b,
+// value of an exchange word that was requested early: taken if its tag is there, else waited for
+__device__ __forceinline__ float ex_finish(Ctx &cx, exch_t w, const exch_t *src, unsigned tag) {
+  return ex_ready(w, tag) ? ex_value(w) : ex_wait1(cx, src, tag);
+}
+
+__device__ __forceinline__ void epilogue(Ctx &cx, const PhaseDev &ph, int pi, unsigned tag, int it, int row, int b,
                                          const float val[3], const EpiIn &in) {
+  const DecodeParams &p = *cx.p;
   const int C = p.C;
   switch (ph.kind) {
     case PH_ATT_KVR: {
@@ -772,7 +789,9 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
     }
     case PH_ATT_O: {
       const int c = it * ROWS + row;
-      ex_store(p.x + (size_t)b * C + c, in.a + val[0], tag);
+      const float xin = ph.layer == 0 ? in.a
+                                      : ex_finish(cx, in.wa, p.x + (size_t)b * C + c, phase_tag(p, pi - (p.version == 4 ? 2 : 3)));
+      ex_store(p.x + (size_t)b * C + c, xin + val[0], tag);
       break;
     }
     case PH_FFN_KR: {
@@ -788,7 +807,9 @@ __device__ __forceinline__ void epilogue(const DecodeParams &p, const PhaseDev &
     }
     case PH_FFN_V: {
       const int c = it * ROWS + row;
-      float xn = in.a + in.b * val[0];
+      const float xin = ex_finish(cx, in.wa, p.x + (size_t)b * C + c, phase_tag(p, pi - 2));
+      const float rin = ex_finish(cx, in.wb, p.rr + (size_t)b * C + c, phase_tag(p, pi - 1));
+      float xn = xin + rin * val[0];
       if (p.rescale_every > 0 && (ph.layer + 1) % p.rescale_every == 0) xn *= 0.5f;
       ex_store(p.x + (size_t)b * C + c, xn, tag);
       break;
@@ -900,7 +921,7 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
           val[u] = s;
         }
       }
-      epilogue(p, ph, tag, it, erow, eb, val, epi_in);
+      epilogue(cx, ph, pi, tag, it, erow, eb, val, epi_in);
       if (ph.kind == PH_HEAD && p.amax && it * ROWS + erow < p.V) {
         unsigned u = __float_as_uint(val[0]);
         u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);

@@ -53,7 +53,7 @@ struct LayerDev {
 // the fp32 value in the low word and, in the high word, the sequence number of the phase that wrote it.
 // A reader knows which phase must have produced the value and polls until the tag matches, so the data
 // is its own synchronisation: no grid-wide barrier, no fence, one 64-bit store per value.
-typedef unsigned long long exch_t;
+typedef uint32_t exch_t;   // fp32 value, low 8 mantissa bits = tag of the phase that wrote it
 
 struct DecodeParams {
   int version, L, C, F, V, Vpad, H;
@@ -62,7 +62,7 @@ struct DecodeParams {
   int n_phases;
   int n_stages;
   int l2_prefetch_bytes;       // per CTA: how far ahead of the ring the producer asks L2 for tiles (0 = off)
-  unsigned seq_base;           // tag of phase pi of this launch = seq_base + pi + 1
+  unsigned seq_base;           // tag of phase pi of this launch = 1 + (seq_base + pi) % 255; host keeps it >= 255
   unsigned par_mask;           // bit b: which copy of the token-shift states stream b reads (it writes the other)
   int ids_val[MAX_B];
   const unsigned long long *ids_packed;  // when non-null: ids are the packed arg-max words of the previous token
