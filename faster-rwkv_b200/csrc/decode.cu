@@ -34,7 +34,8 @@ struct Smem {
   volatile int *abort_flag;
   float *ln_red;     // [NW][2*MAX_B]
   float *red;        // [3][NW][RED_N] per-warp partial sums of the current row block
-  float *par;        // one-stream mode: LayerNorm parameters of the next LN phase, staged with cp.async (or null)
+  float *par;        // one-stream mode: LayerNorm parameters of the next LN phase, staged with bulk copies (or null)
+  uint64_t *par_bar; // completion barrier of those copies
   __half *xs;        // operand vectors
   uint8_t *ring;
 };
@@ -177,6 +178,7 @@ struct Ctx {
   uint32_t slot_b;     // bytes per ring slot
   int prof_phase;
   int par_phase;       // phase whose LayerNorm parameters sit in sm.par (-1: none)
+  uint32_t par_parity; // parity of the next wait on sm.par_bar
   unsigned long long wait_ns;  // profiling: time thread 0 spent waiting for weight tiles in the current phase
 };
 
@@ -414,32 +416,19 @@ __device__ __forceinline__ LnArgs ln_args(const DecodeParams &p, const PhaseDev 
   return a;
 }
 
-__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(void *dst, const void *src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-// Start copying an LN phase's parameters (and shift state) into sm.par.  Asynchronous: costs no registers and no
-// waiting; each thread copies exactly the slots it will read back itself, so cp.async.wait_all is all it needs.
+// Start copying an LN phase's parameters (and shift state) into sm.par: one thread issues a bulk copy per vector,
+// all completing on sm.par_bar.  Nothing waits here; the LayerNorm prologue waits on the barrier when it needs them.
 __device__ __forceinline__ void ln_stage_params(Ctx &cx, const LnArgs &a) {
   const DecodeParams &p = *cx.p;
-  const int n4 = p.C >> 2;
+  if (cx.tid != 0) return;
   float *par = cx.sm.par;
-#pragma unroll
-  for (int r = 0; r < XR; ++r) {
-    const int i4 = cx.tid + r * NCONS;
-    if (i4 < n4) {
-      cp_async16(par + 0 * p.C + i4 * 4, a.ln_w + i4 * 4);
-      cp_async16(par + 1 * p.C + i4 * 4, a.ln_b + i4 * 4);
-      for (int v = 0; v < a.nvec; ++v) cp_async16(par + (2 + v) * p.C + i4 * 4, a.mix[v] + i4 * 4);
-      if (a.nvec > 0) {
-        if (p.act_fp16) cp_async8(reinterpret_cast<__half *>(par + 6 * p.C) + i4 * 4, reinterpret_cast<const __half *>(a.sx_rd) + i4 * 4);
-        else cp_async16(par + 6 * p.C + i4 * 4, reinterpret_cast<const float *>(a.sx_rd) + i4 * 4);
-      }
-    }
-  }
-  asm volatile("cp.async.commit_group;" ::: "memory");
+  const uint32_t vb = (uint32_t)p.C * 4u;
+  const uint32_t sxb = a.nvec > 0 ? (uint32_t)p.C * (p.act_fp16 ? 2u : 4u) : 0u;
+  mbar_expect_tx(cx.sm.par_bar, vb * (2u + (uint32_t)a.nvec) + sxb);
+  bulk_g2s(par, a.ln_w, vb, cx.sm.par_bar);
+  bulk_g2s(par + p.C, a.ln_b, vb, cx.sm.par_bar);
+  for (int v = 0; v < a.nvec; ++v) bulk_g2s(par + (2 + v) * p.C, a.mix[v], vb, cx.sm.par_bar);
+  if (a.nvec > 0) bulk_g2s(par + 6 * p.C, a.sx_rd, sxb, cx.sm.par_bar);
 }
 
 // LayerNorm + token-shift mix for ONE stream of a model with n_embd <= 4 * XR * NCONS: the latency-critical
@@ -480,7 +469,8 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
     s2 += __shfl_xor_sync(0xffffffffu, s2, o);
   }
   if (cx.lane == 0) { cx.sm.ln_red[cx.warp * 2] = s1; cx.sm.ln_red[cx.warp * 2 + 1] = s2; }
-  asm volatile("cp.async.wait_all;" ::: "memory");   // this thread's staged parameters have landed
+  mbar_wait(cx.sm.par_bar, cx.par_parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);   // staged parameters have landed
+  cx.par_parity ^= 1u;
   bar_sync(BAR_CONS, NCONS);
   float sa = 0.f, sc = 0.f;
 #pragma unroll
@@ -624,6 +614,7 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
 #pragma unroll
     for (int r = 0; r < VR; ++r)
       if (base + r * NCONS < total) pending |= 1u << r;
+    int passes = 0; unsigned long long tf = 0;  // PROFX
     do {
 #pragma unroll
       for (int r = 0; r < VR; ++r) {
@@ -633,7 +624,10 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
           if (ex_try4(src + (size_t)b * K + (size_t)i4 * 4, tag, v[r])) pending &= ~(1u << r);
         }
       }
+      if (p.prof) { if (passes == 0) tf = globaltimer_ns(); ++passes; }  // PROFX
     } while (pending && poll.keep_waiting(cx));
+    if (p.prof) { atomicMax(reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640), globaltimer_ns()); atomicMax(reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640) + 1, (unsigned long long)passes); }  // PROFX
+    if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; pr[4] = tf; }  // PROFX
 #pragma unroll
     for (int r = 0; r < VR; ++r) {
       const int s = base + r * NCONS;
@@ -644,6 +638,7 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
     }
   }
   bar_sync(BAR_CONS, NCONS);
+  if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; unsigned long long *q = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640); pr[5] = q[1]; pr[6] = q[0]; q[0] = 0; q[1] = 0; }  // PROFX
   (void)SB;
 }
 
@@ -935,8 +930,7 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
   }
   if (ph.kind == PH_HEAD && p.amax && epi_thread && best) atomicMax(p.amax + eb, best);
   if (prof && (ph.kind == PH_ATT_O || ph.kind == PH_FFN_V)) {
-    p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 4] = c_st; p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 5] = c_bar; p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 6] = c_epi;
-    p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 7] = c_n;
+    p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 7] = c_st;  // PROFX
   }
 }
 
@@ -1000,14 +994,6 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
       continue;
     }
     if (first >= ph.n_items) continue;   // no row block here: nothing to read, nothing to write
-    // stage the LayerNorm parameters of the next phase while this one runs (sm.par is free: this phase is not LN)
-    if (cx.sm.par && !is_ln_phase(ph.kind) && pi + 1 < p.n_phases) {
-      const PhaseDev nx = p.phases[pi + 1];
-      if (is_ln_phase(nx.kind) && (cx.cta + cx.G - nx.rot) % cx.G < nx.n_items) {
-        ln_stage_params(cx, ln_args(p, nx));
-        cx.par_phase = pi + 1;
-      }
-    }
     cx.prof_phase = pi;
     if (prof) p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 0] = globaltimer_ns();
     const bool layered = ph.kind != PH_HEAD && ph.kind != PH_MATVEC;
@@ -1021,6 +1007,15 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
       prologue_vec<NB, NT>(cx, p.kk, p.F, phase_tag(p, pi - 1));
     } else if (ph.kind == PH_MATVEC) {
       prologue_plain<NB, NT>(cx, reinterpret_cast<const float *>(p.kk), ph.K);
+    }
+    // stage the LayerNorm parameters of the next phase while this one multiplies (sm.par is free: this phase is not LN).
+    // Issued after the prologue so that these bulk reads do not sit in front of its latency-critical polls.
+    if (cx.sm.par && !is_ln_phase(ph.kind) && pi + 1 < p.n_phases) {
+      const PhaseDev nx = p.phases[pi + 1];
+      if (is_ln_phase(nx.kind) && (cx.cta + cx.G - nx.rot) % cx.G < nx.n_items) {
+        ln_stage_params(cx, ln_args(p, nx));
+        cx.par_phase = pi + 1;
+      }
     }
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 1] = globaltimer_ns(); cx.wait_ns = 0; }
     run_items<FMT, NB, NT>(cx, ph, ly, pi, first);
@@ -1134,7 +1129,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   size_t o_red, o_par, o_xs, o_ring;
   smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, &o_red, &o_par, &o_xs, &o_ring);
   cx.sm.par = par_bytes<NB, NT>(p.C) ? reinterpret_cast<float *>(smem + o_par) : nullptr;
-  cx.par_phase = -1;
+  cx.par_phase = -1; cx.par_parity = 0;
+  cx.sm.par_bar = reinterpret_cast<uint64_t *>(smem + 200);
   cx.sm.full = reinterpret_cast<uint64_t *>(smem);
   cx.sm.empty = cx.sm.full + MAX_STAGES;
   cx.sm.abort_flag = reinterpret_cast<volatile int *>(smem + 256);
@@ -1149,6 +1145,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
       mbar_init(&cx.sm.empty[s], NW);
     }
     *cx.sm.abort_flag = 0;
+    mbar_init(cx.sm.par_bar, 1);
+    reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640)[0] = 0; reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640)[1] = 0;  // PROFX
     mbar_fence_init();
   }
   __syncthreads();
