@@ -56,7 +56,7 @@ struct fr_b200_model {
   float *d_vecs = nullptr;       size_t vecs_n = 0;
   uint8_t *d_emb = nullptr;      int emb_dtype = -1;   // rows kept in the dtype they arrive in
   uint8_t *d_state = nullptr;    size_t state_stride = 0, layer_stride = 0;
-  exch_t *d_x = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;   // tagged exchange vectors
+  exch_t *d_x = nullptr, *d_xa = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;   // tagged exchange vectors
   exch_t *d_v5buf = nullptr;     // k5, v5, r5, g5, o5
   int exch_batch = 0;            // streams the last launch wrote into the exchange vectors (0: clear them first)
   unsigned seq = 0;              // phases launched so far (tags continue across launches)
@@ -331,6 +331,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_vecs, m->vecs_n * 4);
   if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
   if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * sizeof(exch_t));
+  if (!rc) rc = alloc((void **)&m->d_xa, (size_t)B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_kk, (size_t)B * m->F * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_rr, (size_t)B * m->C * sizeof(exch_t));
@@ -355,7 +356,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   if (!m) return;
   cudaSetDevice(m->device);
   free_scratch(m);
-  void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_rwkv, m->d_kk, m->d_rr,
+  void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
                   m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax};
   for (void *p : ptrs)
     if (p) cudaFree(p);
@@ -507,12 +508,13 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned
   p.emb = m->d_emb; p.emb_f32 = m->emb_dtype == FR_B200_T_F32; p.layers = m->d_layers; p.phases = m->d_phases;
   p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
   p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
-  p.x = m->d_x; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
+  p.x = m->d_x; p.xa = m->d_xa; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
   // Exchange words carry 8-bit tags: unambiguous only against the write just before them in the same slot.  Slots of
   // streams the previous launch did not write, or words a failed launch left half written, could alias: start clean.
   if (m->exch_batch != batch) {
     const size_t B = m->cfg.max_batch;
     CU(cudaMemsetAsync(m->d_x, 0, B * m->C * sizeof(exch_t), st));
+    CU(cudaMemsetAsync(m->d_xa, 0, B * m->C * sizeof(exch_t), st));
     CU(cudaMemsetAsync(m->d_rwkv, 0, B * m->C * sizeof(exch_t), st));
     CU(cudaMemsetAsync(m->d_kk, 0, B * m->F * sizeof(exch_t), st));
     CU(cudaMemsetAsync(m->d_rr, 0, B * m->C * sizeof(exch_t), st));

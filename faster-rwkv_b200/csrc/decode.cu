@@ -36,6 +36,7 @@ struct Smem {
   float *red;        // [3][NW][RED_N] per-warp partial sums of the current row block
   float *par;        // one-stream mode: LayerNorm parameters of the next LN phase, staged with bulk copies (or null)
   uint64_t *par_bar; // completion barrier of those copies
+  uint64_t *par_free; // consumers -> producer: sm.par may be overwritten
   __half *xs;        // operand vectors
   uint8_t *ring;
 };
@@ -177,7 +178,6 @@ struct Ctx {
   uint32_t parity;     // parity of the next full-barrier wait
   uint32_t slot_b;     // bytes per ring slot
   int prof_phase;
-  int par_phase;       // phase whose LayerNorm parameters sit in sm.par (-1: none)
   uint32_t par_parity; // parity of the next wait on sm.par_bar
   unsigned long long wait_ns;  // profiling: time thread 0 spent waiting for weight tiles in the current phase
 };
@@ -233,7 +233,7 @@ struct Poll {
     if (t0 == 0) t0 = now;
     if (now - t0 > WAIT_LIMIT_NS || __ldcg(cx.p->status) != 0) {
       *cx.sm.abort_flag = 1;
-      atomicCAS(cx.p->status, 0, ST_TIMEOUT_DATA);
+      atomicCAS(cx.p->status, 0, ST_TIMEOUT_DATA + 1000 * cx.prof_phase);   // which phase gave up
       return false;
     }
     return true;
@@ -300,25 +300,36 @@ __device__ __forceinline__ void operand_cols(int b, int &tile, int &col_hi, int 
 }
 
 // Write 4 consecutive inputs k..k+3 of stream b into operand vector `vec` as hi + lo fp16 columns.
+// Every lane of the warp must make the call (`valid` says whether this lane has data), with k = 4 * i4 and
+// i4 = lane (mod 8).  One stream: the lane pair (l, l ^ 4) holds the even and the odd 16-input group of a
+// 32-input block; they swap halves so that one lane stores the 16 hi bytes and the other the 16 lo bytes, and a
+// quarter warp writes 128 contiguous bytes (no bank conflicts).
 template <int NB>
 __device__ __forceinline__ void store_operand4(__half *vec, size_t plane_halfs, int k, int b, float a, float bb, float c,
-                                               float dd) {
-  int tile, ch, cl;
-  operand_cols<NB>(b, tile, ch, cl);
-  __half *pl = vec + (size_t)tile * plane_halfs;
+                                               float dd, bool valid) {
   const __half2 h0 = __floats2half2_rn(a, bb), h1 = __floats2half2_rn(c, dd);
   const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
   const __half2 l0 = __floats2half2_rn(a - f0.x, bb - f0.y), l1 = __floats2half2_rn(c - f1.x, dd - f1.y);
-  uint2 u;
-  u.x = *reinterpret_cast<const uint32_t *>(&h0); u.y = *reinterpret_cast<const uint32_t *>(&h1);
-  *reinterpret_cast<uint2 *>(pl + xs_index(k, ch, NB)) = u;
-  u.x = *reinterpret_cast<const uint32_t *>(&l0); u.y = *reinterpret_cast<const uint32_t *>(&l1);
-  *reinterpret_cast<uint2 *>(pl + xs_index(k, cl, NB)) = u;
+  const uint32_t uh0 = *reinterpret_cast<const uint32_t *>(&h0), uh1 = *reinterpret_cast<const uint32_t *>(&h1);
+  const uint32_t ul0 = *reinterpret_cast<const uint32_t *>(&l0), ul1 = *reinterpret_cast<const uint32_t *>(&l1);
+  if (NB == 2) {
+    const bool odd = (k >> 4) & 1;
+    const uint32_t rx = __shfl_xor_sync(0xffffffffu, odd ? uh0 : ul0, 4);
+    const uint32_t ry = __shfl_xor_sync(0xffffffffu, odd ? uh1 : ul1, 4);
+    const uint4 u = odd ? make_uint4(rx, ry, ul0, ul1) : make_uint4(uh0, uh1, rx, ry);
+    if (valid) *reinterpret_cast<uint4 *>(vec + xs_index(k & ~16, odd ? 1 : 0, NB)) = u;
+  } else if (valid) {
+    int tile, ch, cl;
+    operand_cols<NB>(b, tile, ch, cl);
+    __half *pl = vec + (size_t)tile * plane_halfs;
+    *reinterpret_cast<uint2 *>(pl + xs_index(k, ch, NB)) = make_uint2(uh0, uh1);
+    *reinterpret_cast<uint2 *>(pl + xs_index(k, cl, NB)) = make_uint2(ul0, ul1);
+  }
 }
 
 // Residual stream of stream b, elements 4*i4 .. 4*i4+3: the embedding row at layer 0, else the
 // exchange vector x written by phase `tag` (waits for it).
-__device__ __forceinline__ float4 wait_x4(Ctx &cx, bool layer0, int b, int i4, unsigned tag) {
+__device__ __forceinline__ float4 wait_x4(Ctx &cx, const exch_t *xsrc, bool layer0, int b, int i4, unsigned tag) {
   const DecodeParams &p = *cx.p;
   if (layer0) {
     if (p.emb_f32)
@@ -329,13 +340,13 @@ __device__ __forceinline__ float4 wait_x4(Ctx &cx, bool layer0, int b, int i4, u
     const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
     return make_float4(a.x, a.y, c.x, c.y);
   }
-  return ex_wait4(cx, p.x + (size_t)b * p.C + (size_t)i4 * 4, tag);
+  return ex_wait4(cx, xsrc + (size_t)b * p.C + (size_t)i4 * 4, tag);
 }
 
 
 // Element 4*i4.. of the residual stream of stream b without waiting: the embedding row at layer 0
 // (always there), else one attempt at the tagged words.
-__device__ __forceinline__ bool try_x4(const DecodeParams &p, bool layer0, int b, int i4, unsigned tag, float4 &v) {
+__device__ __forceinline__ bool try_x4(const DecodeParams &p, const exch_t *xsrc, bool layer0, int b, int i4, unsigned tag, float4 &v) {
   if (layer0) {
     if (p.emb_f32) {
       v = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * p.C) + i4);
@@ -348,14 +359,14 @@ __device__ __forceinline__ bool try_x4(const DecodeParams &p, bool layer0, int b
     }
     return true;
   }
-  return ex_try4(p.x + (size_t)b * p.C + (size_t)i4 * 4, tag, v);
+  return ex_try4(xsrc + (size_t)b * p.C + (size_t)i4 * 4, tag, v);
 }
 
 // Normalised value -> operand vectors (token-shift mix) and, on the owning CTA, the new shift state.
 template <int NB, int NT>
 __device__ __forceinline__ void ln_emit(Ctx &cx, const PhaseDev &ph, int nvec, uint8_t *sx_wr, int sx_item0, int i4, int b,
                                         const float4 &xv, float mean, float rstd, const float4 &gw, const float4 &gb,
-                                        const float4 *mx4, const float4 &sx) {
+                                        const float4 *mx4, const float4 &sx, bool valid) {
   const DecodeParams &p = *cx.p;
   const size_t plane = (size_t)p.C * NB;   // halfs per (vector, n-tile)
   const size_t vstride = plane * NT;       // halfs per operand vector
@@ -365,7 +376,7 @@ __device__ __forceinline__ void ln_emit(Ctx &cx, const PhaseDev &ph, int nvec, u
   xx.z = (xv.z - mean) * rstd * gw.z + gb.z;
   xx.w = (xv.w - mean) * rstd * gw.w + gb.w;
   if (nvec == 0) {
-    store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, xx.x, xx.y, xx.z, xx.w);
+    store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, xx.x, xx.y, xx.z, xx.w, valid);
     return;
   }
 #pragma unroll
@@ -374,16 +385,17 @@ __device__ __forceinline__ void ln_emit(Ctx &cx, const PhaseDev &ph, int nvec, u
       const float4 m = mx4[v];
       store_operand4<NB>(cx.sm.xs + v * vstride, plane, i4 * 4, b, xx.x * m.x + sx.x * (1.f - m.x),
                          xx.y * m.y + sx.y * (1.f - m.y), xx.z * m.z + sx.z * (1.f - m.z),
-                         xx.w * m.w + sx.w * (1.f - m.w));
+                         xx.w * m.w + sx.w * (1.f - m.w), valid);
     }
   }
   // new token-shift state: written once, by the CTA that owns the row block of these channels
-  if ((sx_item0 + (i4 >> 2) + ph.rot) % cx.G == cx.cta)
+  if (valid && (sx_item0 + (i4 >> 2) + ph.rot) % cx.G == cx.cta)
     store_act4(sx_wr + (size_t)b * p.state_stride, i4, p.act_fp16, xx);
 }
 
 // What a LayerNorm phase reads besides the residual stream.
 struct LnArgs {
+  const exch_t *xsrc;   // residual stream this LayerNorm reads
   const float *ln_w, *ln_b;
   const float *const *mix;
   const uint8_t *sx_rd;
@@ -398,12 +410,12 @@ __device__ __forceinline__ LnArgs ln_args(const DecodeParams &p, const PhaseDev 
   LnArgs a;
   const int v5 = p.version != 4, par = (int)(p.par_mask & 1u);   // streams of one launch share the parity
   a.ln_w = p.lnout_w; a.ln_b = p.lnout_b; a.mix = nullptr; a.sx_rd = nullptr; a.sx_wr = nullptr;
-  a.nvec = 0; a.item0 = 0; a.layer0 = false;
+  a.nvec = 0; a.item0 = 0; a.layer0 = false; a.xsrc = p.x;
   if (ph.kind == PH_HEAD) return a;
   const LayerDev *ly = p.layers + ph.layer;
   uint8_t *st0 = p.state + (size_t)ph.layer * p.layer_stride;   // stream 0
   if (ph.kind == PH_FFN_KR) {
-    a.ln_w = ly->ln2_w; a.ln_b = ly->ln2_b; a.mix = ly->ffn_mix; a.nvec = 2; a.item0 = ph.split[0];
+    a.ln_w = ly->ln2_w; a.ln_b = ly->ln2_b; a.mix = ly->ffn_mix; a.nvec = 2; a.item0 = ph.split[0]; a.xsrc = p.xa;
     a.sx_rd = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par);
     a.sx_wr = st0 + off_ffn_sx(p.C, p.H, v5, p.act_fp16, par ^ 1);
   } else {
@@ -416,11 +428,11 @@ __device__ __forceinline__ LnArgs ln_args(const DecodeParams &p, const PhaseDev 
   return a;
 }
 
-// Start copying an LN phase's parameters (and shift state) into sm.par: one thread issues a bulk copy per vector,
-// all completing on sm.par_bar.  Nothing waits here; the LayerNorm prologue waits on the barrier when it needs them.
+// Copy an LN phase's parameters (and shift state) into sm.par: one bulk copy per vector, all completing on
+// sm.par_bar.  Issued by the producer thread when it reaches the phase's first weight tile, which is a ring depth
+// ahead of the consumers; the LayerNorm prologue waits on the barrier.
 __device__ __forceinline__ void ln_stage_params(Ctx &cx, const LnArgs &a) {
   const DecodeParams &p = *cx.p;
-  if (cx.tid != 0) return;
   float *par = cx.sm.par;
   const uint32_t vb = (uint32_t)p.C * 4u;
   const uint32_t sxb = a.nvec > 0 ? (uint32_t)p.C * (p.act_fp16 ? 2u : 4u) : 0u;
@@ -447,10 +459,10 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   for (int r = 0; r < XR; ++r)
     if (cx.tid + r * NCONS < n4) pending |= 1u << r;
   do {
-    if ((pending >> XR) && try_x4(p, a.layer0, 0, 0, xtag, pv)) pending &= ~(1u << XR);
+    if ((pending >> XR) && try_x4(p, a.xsrc, a.layer0, 0, 0, xtag, pv)) pending &= ~(1u << XR);
 #pragma unroll
     for (int r = 0; r < XR; ++r)
-      if ((pending & (1u << r)) && try_x4(p, a.layer0, 0, cx.tid + r * NCONS, xtag, xv[r])) pending &= ~(1u << r);
+      if ((pending & (1u << r)) && try_x4(p, a.xsrc, a.layer0, 0, cx.tid + r * NCONS, xtag, xv[r])) pending &= ~(1u << r);
   } while (pending && poll.keep_waiting(cx));
   const float piv = pv.x;
   float s1 = 0.f, s2 = 0.f;
@@ -483,8 +495,9 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   const float *par = cx.sm.par;
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
-    const int i4 = cx.tid + r * NCONS;
-    if (i4 < n4) {
+    const bool valid = cx.tid + r * NCONS < n4;
+    const int i4 = valid ? cx.tid + r * NCONS : cx.lane & 7;   // lanes without data still make the (warp-wide) call
+    if (r * NCONS + (cx.tid & ~31) < n4) {                      // warp-uniform
       const float4 gw = *reinterpret_cast<const float4 *>(par + 0 * p.C + i4 * 4);
       const float4 gb = *reinterpret_cast<const float4 *>(par + 1 * p.C + i4 * 4);
       float4 mx4[4], sx = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -501,34 +514,36 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
           sx = *reinterpret_cast<const float4 *>(par + 6 * p.C + i4 * 4);
         }
       }
-      ln_emit<NB, NT>(cx, ph, a.nvec, a.sx_wr, a.item0, i4, 0, xv[r], mean, rstd, gw, gb, mx4, sx);
+      ln_emit<NB, NT>(cx, ph, a.nvec, a.sx_wr, a.item0, i4, 0, xv[r], mean, rstd, gw, gb, mx4, sx, valid);
     }
   }
+  __syncwarp();
+  if (cx.lane == 0) mbar_arrive(cx.sm.par_free);   // this warp is done with sm.par: the producer may refill it
   bar_sync(BAR_CONS, NCONS);
 }
 
 // LayerNorm + token-shift mix, any number of streams and any width: a statistics pass (which also waits
 // for the data) and a second pass over x.
 template <int NB, int NT>
-__device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, bool layer0, unsigned xtag, const float *ln_w,
+__device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, const exch_t *xsrc, bool layer0, unsigned xtag, const float *ln_w,
                                              const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
                                              uint8_t *sx_wr, int sx_item0) {
   constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
   const int n4 = p.C >> 2;
   const float inv = 1.f / (float)p.C;
-  if (!layer0) wait_sentinels(cx, p.x, p.C, xtag);
+  if (!layer0) wait_sentinels(cx, xsrc, p.C, xtag);
   float s1[SB], s2[SB], piv[SB], mean[SB], rstd[SB];
 #pragma unroll
   for (int b = 0; b < SB; ++b) {
     s1[b] = s2[b] = 0.f;
-    piv[b] = b < p.B ? wait_x4(cx, layer0, b, 0, xtag).x : 0.f;
+    piv[b] = b < p.B ? wait_x4(cx, xsrc, layer0, b, 0, xtag).x : 0.f;
   }
   for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
       if (b < p.B) {
-        const float4 v = wait_x4(cx, layer0, b, i4, xtag);
+        const float4 v = wait_x4(cx, xsrc, layer0, b, i4, xtag);
         const float d0 = v.x - piv[b], d1 = v.y - piv[b], d2 = v.z - piv[b], d3 = v.w - piv[b];
         s1[b] += (d0 + d1) + (d2 + d3);
         s2[b] += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
@@ -565,7 +580,10 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, boo
     mean[b] = piv[b] + m;
     rstd[b] = rsqrtf(var + 1e-5f);
   }
-  for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
+  for (int base = 0; base < n4; base += NCONS) {
+    if (base + (cx.tid & ~31) >= n4) break;   // warp-uniform
+    const bool valid = base + cx.tid < n4;
+    const int i4 = valid ? base + cx.tid : cx.lane & 7;
     float4 mx4[4];
     const float4 gw = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4);
     const float4 gb = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4);
@@ -575,10 +593,10 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, boo
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
-      const float4 xv = wait_x4(cx, layer0, b, i4, xtag);  // already there: the statistics pass waited
+      const float4 xv = wait_x4(cx, xsrc, layer0, b, i4, xtag);  // already there: the statistics pass waited
       float4 sx = make_float4(0.f, 0.f, 0.f, 0.f);
       if (nvec > 0) sx = load_act4(sx_rd + (size_t)b * p.state_stride, i4, p.act_fp16);
-      ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4, b, xv, mean[b], rstd[b], gw, gb, mx4, sx);
+      ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4, b, xv, mean[b], rstd[b], gw, gb, mx4, sx, valid);
     }
   }
   bar_sync(BAR_CONS, NCONS);
@@ -588,10 +606,9 @@ template <int NB, int NT>
 __device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, int pi, unsigned xtag) {
   const LnArgs a = ln_args(*cx.p, ph);
   if (cx.sm.par) {
-    if (cx.par_phase != pi) { ln_stage_params(cx, a); cx.par_phase = pi; }   // not staged ahead: do it now
     prologue_ln_one<NB, NT>(cx, ph, a, xtag);
   } else {
-    prologue_ln_mix<NB, NT>(cx, ph, a.layer0, xtag, a.ln_w, a.ln_b, a.mix, a.nvec, a.sx_rd, a.sx_wr, a.item0);
+    prologue_ln_mix<NB, NT>(cx, ph, a.xsrc, a.layer0, xtag, a.ln_w, a.ln_b, a.mix, a.nvec, a.sx_rd, a.sx_wr, a.item0);
   }
 }
 
@@ -607,7 +624,7 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
   const size_t plane = (size_t)K * NB;
   if ((long long)n4 * p.B > (long long)VR * NCONS) wait_sentinels(cx, src, K, tag);
   const int total = n4 * p.B;   // slot index s -> stream s / n4, float4 s % n4
-  for (int base = cx.tid; base < total; base += VR * NCONS) {
+  for (int base = cx.tid; (base & ~31) < total; base += VR * NCONS) {   // warp-uniform: the stores below shuffle
     float4 v[VR];
     Poll poll;
     unsigned pending = 0;   // slots whose words have not all arrived: only those are asked for again
@@ -626,19 +643,22 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
       }
       if (p.prof) { if (passes == 0) tf = globaltimer_ns(); ++passes; }  // PROFX
     } while (pending && poll.keep_waiting(cx));
-    if (p.prof) { atomicMax(reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640), globaltimer_ns()); atomicMax(reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640) + 1, (unsigned long long)passes); }  // PROFX
-    if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; pr[4] = tf; }  // PROFX
+    const long long ca = clock64();  // PROFX
 #pragma unroll
     for (int r = 0; r < VR; ++r) {
       const int s = base + r * NCONS;
-      if (s < total) {
-        const int b = s / n4, i4 = s - b * n4;
-        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v[r].x, v[r].y, v[r].z, v[r].w);
+      if ((s & ~31) < total) {   // warp-uniform
+        const bool valid = s < total;
+        const int sc = valid ? s : cx.lane & 7;
+        const int b = sc / n4, i4 = sc - b * n4;
+        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v[r].x, v[r].y, v[r].z, v[r].w, valid);
       }
     }
+    const long long cb = clock64();  // PROFX
+    if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; pr[4] = cb - ca; pr[5] = clock64(); }  // PROFX
   }
   bar_sync(BAR_CONS, NCONS);
-  if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; unsigned long long *q = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640); pr[5] = q[1]; pr[6] = q[0]; q[0] = 0; q[1] = 0; }  // PROFX
+  if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; const long long cc = clock64(); pr[5] = cc - pr[5]; pr[6] = cc; }  // PROFX
   (void)SB;
 }
 
@@ -649,12 +669,15 @@ __device__ __forceinline__ void prologue_plain(Ctx &cx, const float *src, int K)
   const DecodeParams &p = *cx.p;
   const int n4 = K >> 2;
   const size_t plane = (size_t)K * NB;
-  for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
+  for (int base = 0; base < n4; base += NCONS) {
+    if (base + (cx.tid & ~31) >= n4) break;   // warp-uniform
+    const bool valid = base + cx.tid < n4;
+    const int i4 = valid ? base + cx.tid : cx.lane & 7;
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
       const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)b * K) + i4);
-      store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v.x, v.y, v.z, v.w);
+      store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v.x, v.y, v.z, v.w, valid);
     }
   }
   bar_sync(BAR_CONS, NCONS);
@@ -685,17 +708,18 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly, un
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
       const float rstd = rsqrtf(q * (1.f / 64.f) + 1e-5f);
+      float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
       if (ok) {
         const float4 gw = __ldg(reinterpret_cast<const float4 *>(ly.lnx_w) + i4);
         const float4 gb = __ldg(reinterpret_cast<const float4 *>(ly.lnx_b) + i4);
-        float4 y = make_float4(d0 * rstd * gw.x + gb.x, d1 * rstd * gw.y + gb.y, d2 * rstd * gw.z + gb.z,
-                               d3 * rstd * gw.w + gb.w);
+        y = make_float4(d0 * rstd * gw.x + gb.x, d1 * rstd * gw.y + gb.y, d2 * rstd * gw.z + gb.z,
+                        d3 * rstd * gw.w + gb.w);
         if (p.version >= 51) {
           const float4 g = ex_wait4(cx, p.g5 + (size_t)b * p.C + (size_t)i4 * 4, gtag);
           y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w;
         }
-        store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, y.x, y.y, y.z, y.w);
       }
+      store_operand4<NB>(cx.sm.xs, plane, (ok ? i4 : cx.lane & 7) * 4, b, y.x, y.y, y.z, y.w, ok);
     }
   }
   bar_sync(BAR_CONS, NCONS);
@@ -740,7 +764,7 @@ __device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, c
     }
     case PH_FFN_V: {
       const int c = it * ROWS + row;
-      in.wa = ex_load_raw(p.x + (size_t)b * C + c);    // written by the output projection
+      in.wa = ex_load_raw(p.xa + (size_t)b * C + c);   // written by the output projection
       in.wb = ex_load_raw(p.rr + (size_t)b * C + c);   // written by the ffn receptance rows of the phase before
       break;
     }
@@ -786,7 +810,7 @@ __device__ __forceinline__ void epilogue(Ctx &cx, const PhaseDev &ph, int pi, un
       const int c = it * ROWS + row;
       const float xin = ph.layer == 0 ? in.a
                                       : ex_finish(cx, in.wa, p.x + (size_t)b * C + c, phase_tag(p, pi - (p.version == 4 ? 2 : 3)));
-      ex_store(p.x + (size_t)b * C + c, xin + val[0], tag);
+      ex_store(p.xa + (size_t)b * C + c, xin + val[0], tag);
       break;
     }
     case PH_FFN_KR: {
@@ -802,7 +826,7 @@ __device__ __forceinline__ void epilogue(Ctx &cx, const PhaseDev &ph, int pi, un
     }
     case PH_FFN_V: {
       const int c = it * ROWS + row;
-      const float xin = ex_finish(cx, in.wa, p.x + (size_t)b * C + c, phase_tag(p, pi - 2));
+      const float xin = ex_finish(cx, in.wa, p.xa + (size_t)b * C + c, phase_tag(p, pi - 2));
       const float rin = ex_finish(cx, in.wb, p.rr + (size_t)b * C + c, phase_tag(p, pi - 1));
       float xn = xin + rin * val[0];
       if (p.rescale_every > 0 && (ph.layer + 1) % p.rescale_every == 0) xn *= 0.5f;
@@ -1008,15 +1032,7 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
     } else if (ph.kind == PH_MATVEC) {
       prologue_plain<NB, NT>(cx, reinterpret_cast<const float *>(p.kk), ph.K);
     }
-    // stage the LayerNorm parameters of the next phase while this one multiplies (sm.par is free: this phase is not LN).
-    // Issued after the prologue so that these bulk reads do not sit in front of its latency-critical polls.
-    if (cx.sm.par && !is_ln_phase(ph.kind) && pi + 1 < p.n_phases) {
-      const PhaseDev nx = p.phases[pi + 1];
-      if (is_ln_phase(nx.kind) && (cx.cta + cx.G - nx.rot) % cx.G < nx.n_items) {
-        ln_stage_params(cx, ln_args(p, nx));
-        cx.par_phase = pi + 1;
-      }
-    }
+    if (prof && (ph.kind == PH_ATT_O || ph.kind == PH_FFN_V)) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + pi) * 8; pr[6] = clock64() - pr[6]; }  // PROFX
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 1] = globaltimer_ns(); cx.wait_ns = 0; }
     run_items<FMT, NB, NT>(cx, ph, ly, pi, first);
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 2] = globaltimer_ns(); p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 3] = cx.wait_ns; }
@@ -1090,6 +1106,8 @@ __device__ __forceinline__ void producer(Ctx &cx) {
   const long long window = (long long)p.l2_prefetch_bytes;
   int slot = 0;
   uint32_t parity = 1;  // a fresh barrier reads as "previous phase complete"
+  uint32_t par_parity = 1;
+  int par_pi = -1;      // phase whose LayerNorm parameters were staged last
   bool live = true;
   const uint64_t pol = l2_evict_first_policy();
   while (!ld.done) {
@@ -1098,6 +1116,13 @@ __device__ __forceinline__ void producer(Ctx &cx) {
       if (pf_bytes >= ld_bytes + (long long)p.n_stages * cx.slot_b) prefetch_l2(pf.src, b);  // beyond the ring
       pf_bytes += b;
       pf.next();
+    }
+    if (cx.sm.par && ld.pi != par_pi && is_ln_phase(ld.ph.kind)) {
+      // first tile of a LayerNorm phase: its parameters go in first, once the consumers have left the previous set
+      if (!mbar_wait(cx.sm.par_free, par_parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_EMPTY)) { live = false; break; }
+      par_parity ^= 1u;
+      ln_stage_params(cx, ln_args(p, ld.ph));
+      par_pi = ld.pi;
     }
     const uint32_t bytes = ld.bytes();
     if (!mbar_wait(&cx.sm.empty[slot], parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
@@ -1129,8 +1154,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   size_t o_red, o_par, o_xs, o_ring;
   smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, &o_red, &o_par, &o_xs, &o_ring);
   cx.sm.par = par_bytes<NB, NT>(p.C) ? reinterpret_cast<float *>(smem + o_par) : nullptr;
-  cx.par_phase = -1; cx.par_parity = 0;
+  cx.par_parity = 0;
   cx.sm.par_bar = reinterpret_cast<uint64_t *>(smem + 200);
+  cx.sm.par_free = reinterpret_cast<uint64_t *>(smem + 208);
   cx.sm.full = reinterpret_cast<uint64_t *>(smem);
   cx.sm.empty = cx.sm.full + MAX_STAGES;
   cx.sm.abort_flag = reinterpret_cast<volatile int *>(smem + 256);
@@ -1146,6 +1172,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
     }
     *cx.sm.abort_flag = 0;
     mbar_init(cx.sm.par_bar, 1);
+    mbar_init(cx.sm.par_free, NW);
     reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640)[0] = 0; reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640)[1] = 0;  // PROFX
     mbar_fence_init();
   }

@@ -72,7 +72,10 @@ struct DecodeParams {
   const LayerDev *layers;
   const float *lnout_w, *lnout_b;
   const PhaseDev *phases;
-  exch_t *x, *rwkv, *kk, *rr;           // [B][C], [B][C], [B][F], [B][C]
+  // Residual stream, two copies: x as the ffn value phase (or nothing yet, at layer 0) left it, xa as the attention
+  // output phase left it.  A phase never overwrites the copy that CTAs of the phase before it may still be reading.
+  exch_t *x, *xa;
+  exch_t *rwkv, *kk, *rr;               // [B][C], [B][F], [B][C]
   exch_t *k5, *v5, *r5, *g5, *o5;       // v5 exchange vectors [B][C]
   float *logits;                        // [B][Vpad]
   uint8_t *state;                       // stream slot b at state + b * state_stride
