@@ -480,6 +480,8 @@ int fr_b200_finalize(fr_b200_model *m) {
     ph[i].w = m->d_weights + reinterpret_cast<size_t>(ph[i].w);
     ph[i].rscale = m->fmt == FMT_INT8 ? m->d_rscale + reinterpret_cast<size_t>(ph[i].rscale) : nullptr;
     ph[i].rot = (int)((i * 37) % (size_t)m->grid);
+    if (ph[i].kind == PH_ATT_KVR || ph[i].kind == PH5_WKV) { ph[i].aux0 = layers[ph[i].layer].first; ph[i].aux1 = layers[ph[i].layer].decay; }
+    if (ph[i].kind == PH_ATT_O && m->v5) { ph[i].aux0 = layers[ph[i].layer].lnx_w; ph[i].aux1 = layers[ph[i].layer].lnx_b; }
   }
   CU(cudaMemcpy(m->d_phases, ph.data(), sizeof(PhaseDev) * ph.size(), cudaMemcpyHostToDevice));
   m->finalized = true;

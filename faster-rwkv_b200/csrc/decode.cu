@@ -27,6 +27,9 @@ namespace frb {
 
 namespace {
 
+#ifndef PROF_ITEMS
+#define PROF_ITEMS 0   // PROFX
+#endif
 constexpr int BAR_CONS = 1;  // named barrier id of the consumer warps
 
 struct Smem {
@@ -64,7 +67,7 @@ template <int NB, int NT>
 __host__ __device__ inline size_t smem_layout(int fmt, int C, int F, int version, int n_stages, size_t *off_red,
                                               size_t *off_par, size_t *off_xs, size_t *off_ring) {
   size_t o = 1024;  // barriers + flags + LN scratch
-  *off_red = o;   o += sizeof(float) * 3 * NW * red_n<NB, NT>();
+  *off_red = o;   o += sizeof(float) * 3 * NW * red_n<NB, NT>() * (NB == 2 ? 2 : 1);
   o = align_up(o, 128);
   *off_par = o;   o += par_bytes<NB, NT>(C);
   *off_xs = o;    o += xs_halfs_needed(C, F, version, NB, NT) * 2;
@@ -77,22 +80,22 @@ __host__ __device__ inline size_t smem_layout(int fmt, int C, int F, int version
 // stage x operand -> accumulators.  acc[e][t]: two interleaved accumulator sets e (breaks the MMA
 // dependency chain), n-tile t.
 template <int FMT, int NB, int NT>
-__device__ __forceinline__ void process_stage(const uint8_t *st, int nch, const __half *xv, size_t plane_u4, int chunk0,
+__device__ __forceinline__ void process_stage(uint32_t st, int nch, uint32_t xv, uint32_t plane_bytes, int chunk0,
                                               int warp, int lane, float acc[2][NT][4]) {
   const int g = lane >> 2, q = lane & 3;
   const int n = NB == 2 ? (g & 1) : g;   // operand column this lane feeds
-  const uint4 *xb = reinterpret_cast<const uint4 *>(xv);
+  // st, xv: shared-space addresses of the stage and of the operand vector
   for (int c = warp; c < nch; c += NW) {
-    const size_t xo = ((size_t)(chunk0 + c) * 2 * NB + n) * 4 + q;
+    const uint32_t xo = xv + ((uint32_t)((chunk0 + c) * 2 * NB + n) * 4u + (uint32_t)q) * 16u;
     uint4 b01[NT], b23[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      b01[t] = xb[xo + t * plane_u4];            // MMAs 0,1 of the chunk
-      b23[t] = xb[xo + t * plane_u4 + NB * 4];   // MMAs 2,3
+      b01[t] = lds128(xo + t * plane_bytes);                // MMAs 0,1 of the chunk
+      b23[t] = lds128(xo + t * plane_bytes + NB * 4 * 16);  // MMAs 2,3
     }
     if (FMT == FMT_FP16) {
-      const uint4 *A = reinterpret_cast<const uint4 *>(st + (size_t)c * 2048) + lane;
-      const uint4 a0 = A[0], a1 = A[32], a2 = A[64], a3 = A[96];
+      const uint32_t A = st + (uint32_t)c * 2048u + (uint32_t)lane * 16u;
+      const uint4 a0 = lds128(A), a1 = lds128(A + 512), a2 = lds128(A + 1024), a3 = lds128(A + 1536);
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         mma16816(acc[0][t], a0.x, a0.y, a0.z, a0.w, b01[t].x, b01[t].y);
@@ -101,8 +104,8 @@ __device__ __forceinline__ void process_stage(const uint8_t *st, int nch, const 
         mma16816(acc[1][t], a3.x, a3.y, a3.z, a3.w, b23[t].z, b23[t].w);
       }
     } else if (FMT == FMT_INT8) {
-      const uint4 *A = reinterpret_cast<const uint4 *>(st + (size_t)c * 1024) + lane;
-      const uint4 w01 = A[0], w23 = A[32];
+      const uint32_t A = st + (uint32_t)c * 1024u + (uint32_t)lane * 16u;
+      const uint4 w01 = lds128(A), w23 = lds128(A + 512);
       const uint32_t M = 0x64646464u, OFF = 0x64806480u;  // 1024 + byte, minus 1152 -> byte - 128
 #define FRB_I8(w, sel) hsub2_u32(prmt(w, M, sel), OFF)
       {
@@ -129,8 +132,8 @@ __device__ __forceinline__ void process_stage(const uint8_t *st, int nch, const 
       }
 #undef FRB_I8
     } else {
-      const uint4 w = (reinterpret_cast<const uint4 *>(st + (size_t)c * 512))[lane];
-      const uint2 scw = *reinterpret_cast<const uint2 *>(st + (size_t)nch * 512 + (size_t)c * 64 + g * 8);
+      const uint4 w = lds128(st + (uint32_t)c * 512u + (uint32_t)lane * 16u);
+      const uint2 scw = lds64(st + (uint32_t)nch * 512u + (uint32_t)c * 64u + (uint32_t)g * 8u);
       const float2 s0 = __half22float2(*reinterpret_cast<const __half2 *>(&scw.x));  // group 0: rows g, g+8
       const float2 s1 = __half22float2(*reinterpret_cast<const __half2 *>(&scw.y));  // group 1
       const uint32_t LO = 0x000f000fu, HI = 0x00f000f0u, M0 = 0x64006400u, M1 = 0x54005400u;
@@ -178,6 +181,8 @@ struct Ctx {
   uint32_t parity;     // parity of the next full-barrier wait
   uint32_t slot_b;     // bytes per ring slot
   int prof_phase;
+  uint32_t red_buf;    // one stream: partial-sum buffer of the next row block (0 / 1)
+  long long pc[5];   // PROFX
   uint32_t par_parity; // parity of the next wait on sm.par_bar
   unsigned long long wait_ns;  // profiling: time thread 0 spent waiting for weight tiles in the current phase
 };
@@ -464,6 +469,7 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
     for (int r = 0; r < XR; ++r)
       if ((pending & (1u << r)) && try_x4(p, a.xsrc, a.layer0, 0, cx.tid + r * NCONS, xtag, xv[r])) pending &= ~(1u << r);
   } while (pending && poll.keep_waiting(cx));
+  if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // PROFX
   const float piv = pv.x;
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -492,6 +498,7 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   float var = sc * inv - m * m;
   var = var > 0.f ? var : 0.f;
   const float mean = piv + m, rstd = rsqrtf(var + 1e-5f);
+  if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // PROFX
   const float *par = cx.sm.par;
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
@@ -520,6 +527,7 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   __syncwarp();
   if (cx.lane == 0) mbar_arrive(cx.sm.par_free);   // this warp is done with sm.par: the producer may refill it
   bar_sync(BAR_CONS, NCONS);
+  if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // PROFX
 }
 
 // LayerNorm + token-shift mix, any number of streams and any width: a statistics pass (which also waits
@@ -631,7 +639,6 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
 #pragma unroll
     for (int r = 0; r < VR; ++r)
       if (base + r * NCONS < total) pending |= 1u << r;
-    int passes = 0; unsigned long long tf = 0;  // PROFX
     do {
 #pragma unroll
       for (int r = 0; r < VR; ++r) {
@@ -641,9 +648,8 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
           if (ex_try4(src + (size_t)b * K + (size_t)i4 * 4, tag, v[r])) pending &= ~(1u << r);
         }
       }
-      if (p.prof) { if (passes == 0) tf = globaltimer_ns(); ++passes; }  // PROFX
     } while (pending && poll.keep_waiting(cx));
-    const long long ca = clock64();  // PROFX
+    if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // PROFX
 #pragma unroll
     for (int r = 0; r < VR; ++r) {
       const int s = base + r * NCONS;
@@ -654,11 +660,10 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
         store_operand4<NB>(cx.sm.xs, plane, i4 * 4, b, v[r].x, v[r].y, v[r].z, v[r].w, valid);
       }
     }
-    const long long cb = clock64();  // PROFX
-    if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; pr[4] = cb - ca; pr[5] = clock64(); }  // PROFX
   }
+  if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // PROFX
   bar_sync(BAR_CONS, NCONS);
-  if (p.prof && cx.tid == 0) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8; const long long cc = clock64(); pr[5] = cc - pr[5]; pr[6] = cc; }  // PROFX
+  if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // PROFX
   (void)SB;
 }
 
@@ -685,7 +690,7 @@ __device__ __forceinline__ void prologue_plain(Ctx &cx, const float *src, int K)
 
 // v5 output projection input: GroupNorm over each head's 64 readout values, times the gate
 template <int NB, int NT>
-__device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly, unsigned otag, unsigned gtag) {
+__device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const PhaseDev &ph, unsigned otag, unsigned gtag) {
   constexpr int SB = n_streams<NB, NT>();
   const DecodeParams &p = *cx.p;
   const size_t plane = (size_t)p.C * NB;
@@ -710,8 +715,8 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const LayerDev &ly, un
       const float rstd = rsqrtf(q * (1.f / 64.f) + 1e-5f);
       float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
       if (ok) {
-        const float4 gw = __ldg(reinterpret_cast<const float4 *>(ly.lnx_w) + i4);
-        const float4 gb = __ldg(reinterpret_cast<const float4 *>(ly.lnx_b) + i4);
+        const float4 gw = __ldg(reinterpret_cast<const float4 *>(ph.aux0) + i4);
+        const float4 gb = __ldg(reinterpret_cast<const float4 *>(ph.aux1) + i4);
         y = make_float4(d0 * rstd * gw.x + gb.x, d1 * rstd * gw.y + gb.y, d2 * rstd * gw.z + gb.z,
                         d3 * rstd * gw.w + gb.w);
         if (p.version >= 51) {
@@ -735,7 +740,7 @@ struct EpiIn {
 };
 
 template <int FMT>
-__device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, const LayerDev *ly, int pi, int it, int row,
+__device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, int pi, int it, int row,
                                                   int b, EpiIn &in) {
   const DecodeParams &p = *cx.p;
   const int C = p.C;
@@ -750,7 +755,7 @@ __device__ __forceinline__ void epilogue_prefetch(Ctx &cx, const PhaseDev &ph, c
       const uint8_t *st = p.state + (size_t)b * p.state_stride + (size_t)ph.layer * p.layer_stride;
       const float *aa = reinterpret_cast<const float *>(st + off_mid(C, p.act_fp16));
       in.a = aa[c]; in.b = aa[C + c]; in.c = aa[2 * C + c];
-      in.d = __ldg(ly->first + c); in.e = __ldg(ly->decay + c);
+      in.d = __ldg(ph.aux0 + c); in.e = __ldg(ph.aux1 + c);
       break;
     }
     case PH_ATT_O: {
@@ -853,32 +858,37 @@ __device__ __forceinline__ void epilogue(Ctx &cx, const PhaseDev &ph, int pi, un
 }
 
 // ---- all row blocks of a phase that belong to this CTA ----------------------------------------------
+// One stream: the per-warp partial sums alternate between two buffers, so a row block needs one barrier (sums
+// written -> sums read); the warps that run ahead write the other buffer, and the barrier of that next row block
+// is what tells them the buffer after it is free again.  More streams: one buffer, a second barrier.
 template <int FMT, int NB, int NT>
-__device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const LayerDev *ly, int pi, int first) {
+__device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, int pi, int first) {
   constexpr int SB = n_streams<NB, NT>();
   constexpr int RN = red_n<NB, NT>();
+  constexpr uint32_t RED_BUF = 3u * NW * RN * 4u;   // bytes of one partial-sum buffer
   const DecodeParams &p = *cx.p;
   const int KT = kt_max(FMT);
   const int nst = num_stages(FMT, ph.K);
-  const size_t plane = (size_t)ph.K * NB;   // halfs per (vector, n-tile)
-  const size_t vstride = plane * NT;
+  const uint32_t plane_b = (uint32_t)ph.K * NB * 2u;   // bytes per (vector, n-tile)
+  const uint32_t vstride_b = plane_b * NT;
   const unsigned tag = phase_tag(p, pi);
   const int g = cx.lane >> 2, q = cx.lane & 3;
   const int erow = cx.tid / SB, eb = cx.tid % SB;
   const bool epi_thread = cx.tid < ROWS * SB && eb < p.B;
   const bool prof = p.prof != nullptr && cx.tid == 0;
-  long long c_st = 0, c_bar = 0, c_epi = 0, c_n = 0;
+  const uint32_t xs_a = smem_u32(cx.sm.xs), ring_a = smem_u32(cx.sm.ring), red_a = smem_u32(cx.sm.red);
+  const int last_kt = ph.K - (nst - 1) * KT;
   unsigned long long best = 0;   // head phase: packed arg-max over this thread's logits
   for (int it = first; it < ph.n_items; it += cx.G) {
-    const long long ck0 = prof ? clock64() : 0;
     EpiIn epi_in;
-    if (epi_thread) epilogue_prefetch<FMT>(cx, ph, ly, pi, it, erow, eb, epi_in);
+    if (epi_thread) epilogue_prefetch<FMT>(cx, ph, pi, it, erow, eb, epi_in);
+    const uint32_t red_it = red_a + (NB == 2 ? cx.red_buf * RED_BUF : 0u);
     for (int u = 0; u < ph.n_sub; ++u) {
       // which operand vector feeds this matrix
       int vec = u;
       if (ph.kind == PH_FFN_KR) vec = it < ph.split[0] ? 0 : 1;
       else if (ph.kind == PH5_KVRG) vec = it / (p.C / ROWS);
-      const __half *xv = cx.sm.xs + (size_t)vec * vstride;
+      const uint32_t xv = xs_a + (uint32_t)vec * vstride_b;
       float acc[2][NT][4];
 #pragma unroll
       for (int e = 0; e < 2; ++e)
@@ -887,30 +897,26 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[e][t][i] = 0.f;
       for (int s = 0; s < nst; ++s) {
-        const int kt = min(KT, ph.K - s * KT);
-        if (prof) {
-          const unsigned long long w0 = globaltimer_ns();
-          mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
-          cx.wait_ns += globaltimer_ns() - w0;
-        } else {
-          mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
-        }
-        process_stage<FMT, NB, NT>(cx.sm.ring + (size_t)cx.slot * cx.slot_b, kt / CHUNK_K, xv, plane / 8,
-                                   s * (KT / CHUNK_K), cx.warp, cx.lane, acc);
+        const int kt = s == nst - 1 ? last_kt : KT;
+        const long long w0 = prof ? clock64() : 0;
+        mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
+        if (prof) cx.wait_ns += clock64() - w0;
+        process_stage<FMT, NB, NT>(ring_a + (uint32_t)cx.slot * cx.slot_b, kt / CHUNK_K, xv, plane_b, s * (KT / CHUNK_K),
+                                   cx.warp, cx.lane, acc);
         __syncwarp();
         if (cx.lane == 0) mbar_arrive(&cx.sm.empty[cx.slot]);
         if (++cx.slot == p.n_stages) { cx.slot = 0; cx.parity ^= 1u; }
       }
       // this warp's share of the K split: hi + lo columns summed, parked in shared memory.
       // Accumulator c0,c1 = row g, columns 2q, 2q+1; c2,c3 = row g+8.
-      float *r = cx.sm.red + ((size_t)u * NW + cx.warp) * RN;
+      const uint32_t r = red_it + (uint32_t)(u * NW + cx.warp) * (RN * 4u);
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         float c0 = acc[0][t][0] + acc[1][t][0], c1 = acc[0][t][1] + acc[1][t][1];
         float c2 = acc[0][t][2] + acc[1][t][2], c3 = acc[0][t][3] + acc[1][t][3];
         if (NB == 2) {
           // columns 0 (hi) and 1 (lo) of the q == 0 lanes
-          if (q == 0) { r[g] = c0 + c1; r[g + 8] = c2 + c3; }
+          if (q == 0) { sts_f32(r + g * 4u, c0 + c1); sts_f32(r + (g + 8) * 4u, c2 + c3); }
         } else {
           // columns 0..3 = hi of streams 0..3 (lanes q = 0,1), columns 4..7 = lo (lanes q = 2,3)
           c0 += __shfl_xor_sync(0xffffffffu, c0, 2);
@@ -919,15 +925,13 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
           c3 += __shfl_xor_sync(0xffffffffu, c3, 2);
           if (q < 2) {
             const int sb = t * 4 + 2 * q;
-            r[g * SB + sb] = c0; r[g * SB + sb + 1] = c1;
-            r[(g + 8) * SB + sb] = c2; r[(g + 8) * SB + sb + 1] = c3;
+            sts_f32(r + (g * SB + sb) * 4u, c0); sts_f32(r + (g * SB + sb + 1) * 4u, c1);
+            sts_f32(r + ((g + 8) * SB + sb) * 4u, c2); sts_f32(r + ((g + 8) * SB + sb + 1) * 4u, c3);
           }
         }
       }
     }
-    const long long ck1 = prof ? clock64() : 0;
     bar_sync(BAR_CONS, NCONS);
-    const long long ck2 = prof ? clock64() : 0;
     if (epi_thread) {
       float val[3] = {0.f, 0.f, 0.f};
 #pragma unroll
@@ -935,7 +939,7 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
         if (u < ph.n_sub) {
           float s = 0.f;
 #pragma unroll
-          for (int w = 0; w < NW; ++w) s += cx.sm.red[((size_t)u * NW + w) * RN + cx.tid];
+          for (int w = 0; w < NW; ++w) s += lds_f32(red_it + (uint32_t)((u * NW + w) * RN + cx.tid) * 4u);
           if (FMT == FMT_INT8) s *= epi_in.rscale[u];
           val[u] = s;
         }
@@ -948,18 +952,14 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, const Lay
         best = w > best ? w : best;
       }
     }
-    // the partial sums are read: the next row block may overwrite them
-    bar_sync(BAR_CONS, NCONS);
-    if (prof) { const long long ck3 = clock64(); c_st += ck1 - ck0; c_bar += ck2 - ck1; c_epi += ck3 - ck2; ++c_n; }
+    if (NB == 2) cx.red_buf ^= 1u;
+    else bar_sync(BAR_CONS, NCONS);   // the partial sums are read: the next row block may overwrite them
   }
   if (ph.kind == PH_HEAD && p.amax && epi_thread && best) atomicMax(p.amax + eb, best);
-  if (prof && (ph.kind == PH_ATT_O || ph.kind == PH_FFN_V)) {
-    p.prof[((size_t)cx.cta * p.n_phases + cx.prof_phase) * 8 + 7] = c_st;  // PROFX
-  }
 }
 
 // ---- v5 state update + readout: units of (stream, head, 16 value columns) ----------------------------
-__device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const LayerDev &ly, int pi) {
+__device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, int pi) {
   const DecodeParams &p = *cx.p;
   const int C = p.C, H = p.H;
   const int units = p.B * H * 4;
@@ -976,8 +976,8 @@ __device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, const La
     const float ki = ex_wait1(cx, p.k5 + (size_t)b * C + h * 64 + i, in_tag);
     const float ri = ex_wait1(cx, p.r5 + (size_t)b * C + h * 64 + i, in_tag);
     const float4 vj = ex_wait4(cx, p.v5 + (size_t)b * C + h * 64 + j0 + jq, in_tag);
-    const float u = p.version == 50 ? __ldg(ly.first + h) : __ldg(ly.first + h * 64 + i);
-    const float w = p.version == 50 ? __ldg(ly.decay + h) : __ldg(ly.decay + h * 64 + i);
+    const float u = p.version == 50 ? __ldg(ph.aux0 + h) : __ldg(ph.aux0 + h * 64 + i);
+    const float w = p.version == 50 ? __ldg(ph.aux1 + h) : __ldg(ph.aux1 + h * 64 + i);
     const float a0 = ki * vj.x, a1 = ki * vj.y, a2 = ki * vj.z, a3 = ki * vj.w;
     float o0 = ri * (u * a0 + s.x), o1 = ri * (u * a1 + s.y), o2 = ri * (u * a2 + s.z), o3 = ri * (u * a3 + s.w);
     s.x = a0 + w * s.x; s.y = a1 + w * s.y; s.z = a2 + w * s.z; s.w = a3 + w * s.w;
@@ -1010,31 +1010,34 @@ template <int FMT, int NB, int NT>
 __device__ __forceinline__ void consumer(Ctx &cx) {
   const DecodeParams &p = *cx.p;
   const bool prof = p.prof != nullptr && cx.tid == 0;
+  // the next phase's descriptor is requested a phase ahead: its load latency is off the hand-over path
+  PhaseDev nxt = p.phases[0];
   for (int pi = 0; pi < p.n_phases; ++pi) {
-    const PhaseDev ph = p.phases[pi];
+    cx.pc[0] = prof ? clock64() : 0;  // PROFX
+    const PhaseDev ph = nxt;
+    if (pi + 1 < p.n_phases) nxt = p.phases[pi + 1];
     const int first = (cx.cta + cx.G - ph.rot) % cx.G;
     if (ph.kind == PH5_WKV) {
-      if (first < p.B * p.H * 4) phase_wkv5(cx, ph, p.layers[ph.layer], pi);
+      if (first < p.B * p.H * 4) phase_wkv5(cx, ph, pi);
       continue;
     }
     if (first >= ph.n_items) continue;   // no row block here: nothing to read, nothing to write
     cx.prof_phase = pi;
     if (prof) p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 0] = globaltimer_ns();
-    const bool layered = ph.kind != PH_HEAD && ph.kind != PH_MATVEC;
-    const LayerDev *ly = layered ? p.layers + ph.layer : nullptr;
+    cx.pc[1] = cx.pc[2] = cx.pc[3] = cx.pc[4] = prof ? clock64() : 0;  // PROFX
     if (is_ln_phase(ph.kind)) {
       prologue_ln<NB, NT>(cx, ph, pi, phase_tag(p, pi - 1));
     } else if (ph.kind == PH_ATT_O) {
       if (p.version == 4) prologue_vec<NB, NT>(cx, p.rwkv, p.C, phase_tag(p, pi - 1));
-      else prologue_gn_gate<NB, NT>(cx, *ly, phase_tag(p, pi - 1), phase_tag(p, pi - 2));
+      else prologue_gn_gate<NB, NT>(cx, ph, phase_tag(p, pi - 1), phase_tag(p, pi - 2));
     } else if (ph.kind == PH_FFN_V) {
       prologue_vec<NB, NT>(cx, p.kk, p.F, phase_tag(p, pi - 1));
     } else if (ph.kind == PH_MATVEC) {
       prologue_plain<NB, NT>(cx, reinterpret_cast<const float *>(p.kk), ph.K);
     }
-    if (prof && (ph.kind == PH_ATT_O || ph.kind == PH_FFN_V)) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + pi) * 8; pr[6] = clock64() - pr[6]; }  // PROFX
+    if (prof) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + pi) * 8; pr[4] = cx.pc[1] - cx.pc[0]; pr[5] = cx.pc[2] - cx.pc[1]; pr[6] = cx.pc[3] - cx.pc[2]; pr[7] = cx.pc[4] - cx.pc[3]; }  // PROFX
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 1] = globaltimer_ns(); cx.wait_ns = 0; }
-    run_items<FMT, NB, NT>(cx, ph, ly, pi, first);
+    run_items<FMT, NB, NT>(cx, ph, pi, first);
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 2] = globaltimer_ns(); p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 3] = cx.wait_ns; }
   }
 }
@@ -1149,7 +1152,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   cx.p = &p;
   cx.tid = threadIdx.x; cx.warp = threadIdx.x >> 5; cx.lane = threadIdx.x & 31;
   cx.cta = blockIdx.x; cx.G = gridDim.x;
-  cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0;
+  cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0; cx.red_buf = 0;
   cx.slot_b = slot_bytes(FMT);
   size_t o_red, o_par, o_xs, o_ring;
   smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, &o_red, &o_par, &o_xs, &o_ring);
@@ -1173,7 +1176,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
     *cx.sm.abort_flag = 0;
     mbar_init(cx.sm.par_bar, 1);
     mbar_init(cx.sm.par_free, NW);
-    reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640)[0] = 0; reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(cx.sm.ln_red) + 640)[1] = 0;  // PROFX
     mbar_fence_init();
   }
   __syncthreads();

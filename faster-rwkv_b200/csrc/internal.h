@@ -38,6 +38,9 @@ struct PhaseDev {
   int split[3];            // item index where class 1, 2, 3 start (PH_FFN_KR, PH5_KVRG)
   int rot;                 // item i runs on CTA (i + rot) % gridDim.x
   int pad;
+  // per-layer vectors the phase's own threads read (saves the hop through the layer table):
+  // PH_ATT_KVR, PH5_WKV: time_first, time_decay; PH_ATT_O of RWKV-5: ln_x weight, bias
+  const float *aux0, *aux1;
 };
 
 // Per-layer vectors (all fp32 on the device) and state offsets.
