@@ -51,7 +51,7 @@ def algorithmic_bytes(shape, fmt: str) -> int:
 
 # DRAM bytes per decode_kernel launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture summarised
 # in profiles/decode_kernel_c1_fp16_launch_list.md; other workloads have no capture yet.
-MEASURED_TRAFFIC = {("c1", "fp16", 1): 2_893_527_000}
+MEASURED_TRAFFIC = {("c1", "fp16", 1): 2_891_602_330}
 
 
 def measured_peak_gbs():

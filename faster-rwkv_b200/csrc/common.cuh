@@ -43,6 +43,17 @@ __device__ __forceinline__ bool mbar_try(uint64_t *b, uint32_t parity) {
   return ok != 0;
 }
 
+// non-blocking look at a barrier phase (never suspends the thread)
+__device__ __forceinline__ bool mbar_test(uint64_t *b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  abort_flag lives in shared memory; once any thread of the CTA sets it every
 // later wait returns at once, so the CTA drains to its end instead of hanging.
 __device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, volatile int *abort_flag, int *status,

@@ -27,9 +27,6 @@ namespace frb {
 
 namespace {
 
-#ifndef PROF_ITEMS
-#define PROF_ITEMS 0   // PROFX
-#endif
 constexpr int BAR_CONS = 1;  // named barrier id of the consumer warps
 
 struct Smem {
@@ -182,9 +179,10 @@ struct Ctx {
   uint32_t slot_b;     // bytes per ring slot
   int prof_phase;
   uint32_t red_buf;    // one stream: partial-sum buffer of the next row block (0 / 1)
-  long long pc[5];   // PROFX
+  bool ready;          // the next stage's tile was seen complete by an earlier look-ahead
+  long long pc[5];     // trace: cycle counter at the prologue's milestones (thread 0)
   uint32_t par_parity; // parity of the next wait on sm.par_bar
-  unsigned long long wait_ns;  // profiling: time thread 0 spent waiting for weight tiles in the current phase
+  unsigned long long wait_ns;  // trace: cycles thread 0 spent waiting for weight tiles in the current phase
 };
 
 __device__ __forceinline__ int token_id(const DecodeParams &p, int b) {
@@ -469,7 +467,7 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
     for (int r = 0; r < XR; ++r)
       if ((pending & (1u << r)) && try_x4(p, a.xsrc, a.layer0, 0, cx.tid + r * NCONS, xtag, xv[r])) pending &= ~(1u << r);
   } while (pending && poll.keep_waiting(cx));
-  if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // PROFX
+  if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // trace
   const float piv = pv.x;
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -498,7 +496,7 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   float var = sc * inv - m * m;
   var = var > 0.f ? var : 0.f;
   const float mean = piv + m, rstd = rsqrtf(var + 1e-5f);
-  if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // PROFX
+  if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // trace
   const float *par = cx.sm.par;
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
@@ -527,7 +525,7 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   __syncwarp();
   if (cx.lane == 0) mbar_arrive(cx.sm.par_free);   // this warp is done with sm.par: the producer may refill it
   bar_sync(BAR_CONS, NCONS);
-  if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // PROFX
+  if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // trace
 }
 
 // LayerNorm + token-shift mix, any number of streams and any width: a statistics pass (which also waits
@@ -649,7 +647,7 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
         }
       }
     } while (pending && poll.keep_waiting(cx));
-    if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // PROFX
+    if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // trace
 #pragma unroll
     for (int r = 0; r < VR; ++r) {
       const int s = base + r * NCONS;
@@ -661,9 +659,9 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
       }
     }
   }
-  if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // PROFX
+  if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // trace
   bar_sync(BAR_CONS, NCONS);
-  if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // PROFX
+  if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // trace
   (void)SB;
 }
 
@@ -898,14 +896,19 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, int pi, i
           for (int i = 0; i < 4; ++i) acc[e][t][i] = 0.f;
       for (int s = 0; s < nst; ++s) {
         const int kt = s == nst - 1 ? last_kt : KT;
-        const long long w0 = prof ? clock64() : 0;
-        mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
-        if (prof) cx.wait_ns += clock64() - w0;
-        process_stage<FMT, NB, NT>(ring_a + (uint32_t)cx.slot * cx.slot_b, kt / CHUNK_K, xv, plane_b, s * (KT / CHUNK_K),
+        if (!cx.ready) {
+          const long long w0 = prof ? clock64() : 0;
+          mbar_wait(&cx.sm.full[cx.slot], cx.parity, cx.sm.abort_flag, p.status, ST_TIMEOUT_FULL);
+          if (prof) cx.wait_ns += clock64() - w0;
+        }
+        // look at the stage after this one now: the answer is back by the time this stage is multiplied
+        const int cur = cx.slot;
+        if (++cx.slot == p.n_stages) { cx.slot = 0; cx.parity ^= 1u; }
+        cx.ready = mbar_test(&cx.sm.full[cx.slot], cx.parity);
+        process_stage<FMT, NB, NT>(ring_a + (uint32_t)cur * cx.slot_b, kt / CHUNK_K, xv, plane_b, s * (KT / CHUNK_K),
                                    cx.warp, cx.lane, acc);
         __syncwarp();
-        if (cx.lane == 0) mbar_arrive(&cx.sm.empty[cx.slot]);
-        if (++cx.slot == p.n_stages) { cx.slot = 0; cx.parity ^= 1u; }
+        if (cx.lane == 0) mbar_arrive(&cx.sm.empty[cur]);
       }
       // this warp's share of the K split: hi + lo columns summed, parked in shared memory.
       // Accumulator c0,c1 = row g, columns 2q, 2q+1; c2,c3 = row g+8.
@@ -1013,7 +1016,7 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
   // the next phase's descriptor is requested a phase ahead: its load latency is off the hand-over path
   PhaseDev nxt = p.phases[0];
   for (int pi = 0; pi < p.n_phases; ++pi) {
-    cx.pc[0] = prof ? clock64() : 0;  // PROFX
+    cx.pc[0] = prof ? clock64() : 0;  // trace
     const PhaseDev ph = nxt;
     if (pi + 1 < p.n_phases) nxt = p.phases[pi + 1];
     const int first = (cx.cta + cx.G - ph.rot) % cx.G;
@@ -1024,7 +1027,7 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
     if (first >= ph.n_items) continue;   // no row block here: nothing to read, nothing to write
     cx.prof_phase = pi;
     if (prof) p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 0] = globaltimer_ns();
-    cx.pc[1] = cx.pc[2] = cx.pc[3] = cx.pc[4] = prof ? clock64() : 0;  // PROFX
+    cx.pc[1] = cx.pc[2] = cx.pc[3] = cx.pc[4] = prof ? clock64() : 0;  // trace
     if (is_ln_phase(ph.kind)) {
       prologue_ln<NB, NT>(cx, ph, pi, phase_tag(p, pi - 1));
     } else if (ph.kind == PH_ATT_O) {
@@ -1035,7 +1038,7 @@ __device__ __forceinline__ void consumer(Ctx &cx) {
     } else if (ph.kind == PH_MATVEC) {
       prologue_plain<NB, NT>(cx, reinterpret_cast<const float *>(p.kk), ph.K);
     }
-    if (prof) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + pi) * 8; pr[4] = cx.pc[1] - cx.pc[0]; pr[5] = cx.pc[2] - cx.pc[1]; pr[6] = cx.pc[3] - cx.pc[2]; pr[7] = cx.pc[4] - cx.pc[3]; }  // PROFX
+    if (prof) { unsigned long long *pr = p.prof + ((size_t)cx.cta * p.n_phases + pi) * 8; pr[4] = cx.pc[1] - cx.pc[0]; pr[5] = cx.pc[2] - cx.pc[1]; pr[6] = cx.pc[3] - cx.pc[2]; pr[7] = cx.pc[4] - cx.pc[3]; }  // trace
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 1] = globaltimer_ns(); cx.wait_ns = 0; }
     run_items<FMT, NB, NT>(cx, ph, pi, first);
     if (prof) { p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 2] = globaltimer_ns(); p.prof[((size_t)cx.cta * p.n_phases + pi) * 8 + 3] = cx.wait_ns; }
@@ -1152,7 +1155,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   cx.p = &p;
   cx.tid = threadIdx.x; cx.warp = threadIdx.x >> 5; cx.lane = threadIdx.x & 31;
   cx.cta = blockIdx.x; cx.G = gridDim.x;
-  cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0; cx.red_buf = 0;
+  cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0; cx.red_buf = 0; cx.ready = false;
   cx.slot_b = slot_bytes(FMT);
   size_t o_red, o_par, o_xs, o_ring;
   smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, &o_red, &o_par, &o_xs, &o_ring);

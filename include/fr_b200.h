@@ -167,8 +167,9 @@ typedef struct fr_b200_info {
 int fr_b200_get_info(const fr_b200_model *m, fr_b200_info *info);
 
 /* One decode step with a per-CTA, per-phase trace: stamps[cta][phase][8] = {phase start, inputs staged, row
- * blocks done (ns of the GPU's global timer), ns spent waiting for weight tiles, cycles in the tile loop, in the
- * reduction barrier, in the epilogue, row blocks processed}; zero where the CTA had no work in the phase.
+ * blocks done (ns of the GPU's global timer), then SM cycles: waiting for weight tiles, phase descriptor ->
+ * phase start, phase start -> inputs arrived, inputs arrived -> statistics / conversion done, -> operands staged};
+ * zero where the CTA had no work in the phase.
  * A tracing aid (the reference has only wall-clock FR_SHOW_SPEED prints, chat.cpp:98-111).
  * stamps: host, n_ctas * n_phases * 8 entries (fr_b200_get_info gives both counts). */
 int fr_b200_decode_profile(fr_b200_model *m, const int32_t *ids, int batch, uint64_t *stamps, int n_stamps);
