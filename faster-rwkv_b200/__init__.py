@@ -73,6 +73,7 @@ SIGNATURES = {
     "fr_b200_dequantize_int4": (_i, [_vp, _vp, _i, _i, _vp, _i]),
     "fr_b200_unpack_matrix": (_i, [_vp, ctypes.c_char_p, _vp, _i, _i]),
     "fr_b200_matvec": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i]),
+    "fr_b200_gemm_f16": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp, ctypes.c_float, _vp, _i]),
     "fr_b200_matvec_noalloc": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp]),
     "fr_b200_noalloc_last_error": (ctypes.c_char_p, []),
     "fr_b200_get_info": (_i, [_vp, ctypes.POINTER(Info)]),
@@ -342,6 +343,21 @@ def dequantize_int4(p: np.ndarray, s: np.ndarray, device: int = 0) -> np.ndarray
     check(lib().fr_b200_dequantize_int4(_np_ptr(p), _np_ptr(s), K2 * 2, N, _np_ptr(W), device),
           "fr_b200_dequantize_int4")
     return W
+
+
+def gemm_f16(A: np.ndarray, W: np.ndarray, epilogue: int = 0, aux0=None, aux1=None, scale: float = 1.0,
+             device: int = 0) -> np.ndarray:
+    """epilogue(A[M,K] @ W[K,N]) through the seq-mode tensor-core GEMM (operands rounded to fp16)."""
+    A = np.ascontiguousarray(A, np.float32)
+    W = np.ascontiguousarray(W, np.float32)
+    M, K = A.shape
+    N = W.shape[1]
+    out = np.empty((M, N), np.float32)
+    a0 = None if aux0 is None else np.ascontiguousarray(aux0, np.float32)
+    a1 = None if aux1 is None else np.ascontiguousarray(aux1, np.float32)
+    check(lib().fr_b200_gemm_f16(_np_ptr(A), _np_ptr(W), M, N, K, epilogue, None if a0 is None else _np_ptr(a0),
+                                 None if a1 is None else _np_ptr(a1), scale, _np_ptr(out), device), "fr_b200_gemm_f16")
+    return out
 
 
 def matvec(W: np.ndarray, x: np.ndarray, weight_format: int, device: int = 0) -> np.ndarray:

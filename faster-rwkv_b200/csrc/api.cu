@@ -802,6 +802,52 @@ int fr_b200_unpack_matrix(fr_b200_model *m, const char *name, float *W, int K, i
   return FR_B200_OK;
 }
 
+int fr_b200_gemm_f16(const float *A, const float *W, int M, int N, int K, int epilogue, const float *aux0,
+                     const float *aux1, float scale, float *out, int device) {
+  if (!A || !W || !out || M < 1 || N < 1 || K < 64 || K % 64) return fail(FR_B200_E_ARG, "bad argument (K must be a positive multiple of 64)");
+  if (epilogue < 0 || epilogue > GEMM_EPI_PLAIN_F16) return fail(FR_B200_E_ARG, "bad epilogue");
+  if ((epilogue == GEMM_EPI_ADD_F32 || epilogue == GEMM_EPI_MULADD_F32) && !aux0) return fail(FR_B200_E_ARG, "aux0 missing");
+  if (epilogue == GEMM_EPI_MULADD_F32 && !aux1) return fail(FR_B200_E_ARG, "aux1 missing");
+  CU(cudaSetDevice(device));
+  const size_t na = (size_t)M * K, nw = (size_t)K * N, no = (size_t)M * N;
+  DevBuf a32, a16, w32, w16, wt, o, x0, r32, r16, st;
+  CU(a32.alloc(na * 4)); CU(a16.alloc(na * 2)); CU(w32.alloc(nw * 4)); CU(w16.alloc(nw * 2)); CU(wt.alloc(nw * 2));
+  CU(o.alloc(no * 4)); CU(st.alloc(4));
+  CU(cudaMemset(st.p, 0, 4));
+  CU(cudaMemcpy(a32.p, A, na * 4, cudaMemcpyDefault));
+  CU(cudaMemcpy(w32.p, W, nw * 4, cudaMemcpyDefault));
+  CU(launch_f32_to_f16((const float *)a32.p, (__half *)a16.p, na, 0));
+  CU(launch_f32_to_f16((const float *)w32.p, (__half *)w16.p, nw, 0));
+  CU(launch_transpose_f16((const __half *)w16.p, K, N, (__half *)wt.p, 0));
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.A = (const __half *)a16.p; g.Bt = (const __half *)wt.p; g.M = M; g.N = N; g.K = K; g.epi = epilogue;
+  g.out = o.p; g.ldo = N; g.scale = scale; g.status = (int *)st.p;
+  if (aux0) { CU(x0.alloc(no * 4)); CU(cudaMemcpy(x0.p, aux0, no * 4, cudaMemcpyDefault)); g.aux0 = x0.p; }
+  if (aux1) {
+    CU(r32.alloc(no * 4)); CU(r16.alloc(no * 2));
+    CU(cudaMemcpy(r32.p, aux1, no * 4, cudaMemcpyDefault));
+    CU(launch_f32_to_f16((const float *)r32.p, (__half *)r16.p, no, 0));
+    g.aux1 = r16.p;
+  }
+  const bool half_out = epilogue == GEMM_EPI_SILU_F16 || epilogue == GEMM_EPI_SIGMOID_F16 || epilogue == GEMM_EPI_RELU2_F16 ||
+                        epilogue == GEMM_EPI_PLAIN_F16;
+  CU(launch_gemm_f16(g, 0));
+  CU(cudaDeviceSynchronize());
+  int status = 0;
+  CU(cudaMemcpy(&status, st.p, 4, cudaMemcpyDeviceToHost));
+  if (status) return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(status) + ")");
+  if (half_out) {
+    DevBuf o32;
+    CU(o32.alloc(no * 4));
+    CU(launch_f16_to_f32((const __half *)o.p, (float *)o32.p, no, 0));
+    CU(cudaMemcpy(out, o32.p, no * 4, cudaMemcpyDefault));
+  } else {
+    CU(cudaMemcpy(out, o.p, no * 4, cudaMemcpyDefault));
+  }
+  return FR_B200_OK;
+}
+
 int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float *x, int batch, float *y, int device) {
   if (!W || !x || !y || K <= 0 || N <= 0 || K % 64) return fail(FR_B200_E_ARG, "bad argument (K must be a positive multiple of 64)");
   if (weight_format < 0 || weight_format > 2) return fail(FR_B200_E_ARG, "bad weight_format");

@@ -103,6 +103,30 @@ FRB_HD size_t off_ffn_sx(int C, int H, int v5, int act_fp16, int par) {
   return off_mid(C, act_fp16) + mid_bytes(C, H, v5) + (size_t)par * C * act_bytes(act_fp16);
 }
 
+// ---- seq-mode GEMM (prefill.cu) --------------------------------------------------------------------
+enum GemmEpilogue {
+  GEMM_EPI_F32 = 0,         // out f32 = acc
+  GEMM_EPI_SILU_F16,        // out f16 = acc * sigmoid(acc)
+  GEMM_EPI_SIGMOID_F16,     // out f16 = sigmoid(acc)
+  GEMM_EPI_RELU2_F16,       // out f16 = max(acc, 0)^2
+  GEMM_EPI_ADD_F32,         // out f32 = (aux0 + acc) * scale                (aux0 f32 [M, N])
+  GEMM_EPI_MULADD_F32,      // out f32 = (aux0 + aux1 * acc) * scale         (aux1 f16 [M, N])
+  GEMM_EPI_PLAIN_F16        // out f16 = acc
+};
+struct GemmArgs {
+  const __half *A;     // [M, K] row-major
+  const __half *Bt;    // [N, K] row-major (the weight matrix transposed: one row per output channel)
+  int M, N, K;         // K a multiple of 64
+  int epi;
+  void *out;           // [M, ldo]
+  int ldo;
+  const void *aux0, *aux1;   // [M, ldo] like out
+  float scale;
+  int *status;         // device word: set when a bounded wait gives up
+};
+cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);
+cudaError_t launch_transpose_f16(const __half *src, int K, int N, __half *dst, cudaStream_t st);   // [K,N] -> [N,K]
+
 // ---- launchers implemented in the .cu files ------------------------------------------------------
 // mode = how many streams one launch carries: 0 -> 1, 1 -> up to 4, 2 -> up to 8
 inline int decode_mode(int batch) { return batch == 1 ? 0 : batch <= 4 ? 1 : 2; }

@@ -158,6 +158,15 @@ int fr_b200_matvec_noalloc(const float *W, int K, int N, int weight_format, cons
                            int device, void *stream);
 const char *fr_b200_noalloc_last_error(void);
 
+/* out[M,N] = epilogue(A[M,K] @ W[K,N]) on the tcgen05 tensor cores, fp16 operands, fp32 accumulate: the seq-mode
+ * replacement of gemm_cublas_tensor (kernels/cuda/matmul.cpp:105-122) with the element-wise kernels that follow
+ * it in the reference fused as the epilogue (att_seq.cu:368-423, ffn_seq.cu:65-87).  A: [M,K] fp32, rounded to
+ * fp16; W: [K,N] fp32, rounded to fp16; out, aux0, aux1: [M,N] fp32, host or device.  K a multiple of 64.
+ * epilogue: 0 acc | 1 silu(acc) | 2 sigmoid(acc) | 3 relu(acc)^2 | 4 (aux0 + acc) * scale |
+ *           5 (aux0 + aux1 * acc) * scale | 6 acc rounded to fp16.   For unit tests. */
+int fr_b200_gemm_f16(const float *A, const float *W, int M, int N, int K, int epilogue, const float *aux0,
+                     const float *aux1, float scale, float *out, int device);
+
 /* ---- introspection ---- */
 typedef struct fr_b200_info {
   int n_ctas, n_threads, smem_bytes, n_stages, stage_bytes, n_phases;
