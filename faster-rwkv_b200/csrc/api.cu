@@ -35,6 +35,8 @@ struct MatrixSlot {       // where a projection matrix lives inside the packed w
   size_t rscale_stride = 0;
   int K = 0, N = 0;
   bool set = false;
+  bool has_plain = false; // seq mode keeps the matrix a second time as W^T [N, K] fp16 row-major
+  size_t plain_off = 0;   // offset of that copy in halfs
 };
 
 struct VecSlot {
@@ -67,6 +69,11 @@ struct fr_b200_model {
   uint8_t *h_out = nullptr;      // pinned mirror of d_out
   unsigned long long *d_hist = nullptr; size_t hist_n = 0;   // packed arg-max words of decode_greedy, [tokens][batch]
   unsigned long long *d_amax = nullptr;   // packed arg-max words of a single decode, [max_batch]
+  // seq mode (RWKV-5.x with fp16 weights): plain copies of the projection matrices, activation buffers for seq_T tokens
+  __half *d_plain = nullptr;     size_t plain_halfs = 0;
+  uint8_t *d_seq = nullptr;      size_t seq_bytes = 0; int seq_T = 0;
+  PhaseDev *d_head_phase = nullptr;   // the head as a stand-alone matvec phase
+  float *d_lnvec = nullptr;           // ln_out of the last prompt token
   // scratch for uploads
   void *d_scratch[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t scratch_bytes[4] = {0, 0, 0, 0};
@@ -184,6 +191,14 @@ void plan(fr_b200_model *m) {
   phase(PH_HEAD, 0, C, nbV, 1, woff, roff);
   woff += (size_t)nbV * rbC; roff += (size_t)nbV * ROWS;
   m->weights_bytes = woff; m->rscale_n = roff; m->vecs_n = voff;
+  m->plain_halfs = 0;
+  if (m->v5 && fmt == FMT_FP16)
+    for (auto &kv : m->mats) {
+      if (kv.first == "head.weight") continue;   // the head stays a matvec over the last token
+      kv.second.has_plain = true;
+      kv.second.plain_off = m->plain_halfs;
+      m->plain_halfs += ((size_t)kv.second.K * kv.second.N + 127) / 128 * 128;
+    }
   m->stream_bytes = (long long)woff + (fmt == FMT_INT8 ? (long long)roff * 2 : 0);
 }
 
@@ -208,6 +223,7 @@ int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int d
       src = reinterpret_cast<const __half *>(m->d_scratch[1]);
     }
     CU(launch_pack(FMT_FP16, src, nullptr, s.K, s.N, dst, s.item_stride, nullptr, 0, 0));
+    if (s.has_plain && m->d_plain) CU(launch_transpose_f16(src, s.K, s.N, m->d_plain + s.plain_off, 0));
   } else {
     const float *w32 = reinterpret_cast<const float *>(m->d_scratch[0]);
     if (dtype == FR_B200_T_F16) {
@@ -338,6 +354,9 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
   if (!rc) rc = alloc((void **)&m->d_amax, (size_t)B * 8);
+  if (!rc && m->plain_halfs) rc = alloc((void **)&m->d_plain, m->plain_halfs * 2);
+  if (!rc) rc = alloc((void **)&m->d_head_phase, sizeof(PhaseDev));
+  if (!rc) rc = alloc((void **)&m->d_lnvec, (size_t)m->C * 4);
   if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
   if (!rc) rc = alloc((void **)&m->d_phases, sizeof(PhaseDev) * m->phases.size());
   if (!rc && cudaMallocHost((void **)&m->h_out, m->out_bytes()) != cudaSuccess) rc = fail(FR_B200_E_NOMEM, "cudaMallocHost failed");
@@ -357,7 +376,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   cudaSetDevice(m->device);
   free_scratch(m);
   void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
-                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax};
+                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_seq, m->d_head_phase, m->d_lnvec};
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);
@@ -484,6 +503,11 @@ int fr_b200_finalize(fr_b200_model *m) {
     if (ph[i].kind == PH_ATT_O && m->v5) { ph[i].aux0 = layers[ph[i].layer].lnx_w; ph[i].aux1 = layers[ph[i].layer].lnx_b; }
   }
   CU(cudaMemcpy(m->d_phases, ph.data(), sizeof(PhaseDev) * ph.size(), cudaMemcpyHostToDevice));
+  {
+    PhaseDev hp = ph.back();   // the head, as the one phase of a stand-alone matvec launch
+    hp.kind = PH_MATVEC; hp.rot = 0;
+    CU(cudaMemcpy(m->d_head_phase, &hp, sizeof(hp), cudaMemcpyHostToDevice));
+  }
   m->finalized = true;
   return fr_b200_state_reset(m, -1);
 }
@@ -638,16 +662,145 @@ int fr_b200_logits_device(fr_b200_model *m, float **ptr) {
 }
 int fr_b200_vocab_padded(const fr_b200_model *m) { return m ? m->Vpad : FR_B200_E_ARG; }
 
+namespace {
+
+// Seq mode for RWKV-5.x with fp16 weights: the whole prompt of one stream through [T, K] x [K, N] GEMMs
+// (def::ModelForwardSeq, kernels/default/model_forward_seq.cpp:48-184).  The residual stream stays fp32 between
+// the layers; GEMM inputs are fp16, as in decode.
+int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStream_t st) {
+  const int C = m->C, F = m->F, H = m->H, af = m->cfg.act_fp16;
+  const size_t TC = (size_t)T * C, TF = (size_t)T * F;
+  // activation buffers: one blob, 256-byte aligned pieces
+  size_t off = 0;
+  auto take = [&](size_t bytes) { const size_t o = off; off += align256(bytes); return o; };
+  const size_t o_ids = take((size_t)T * 4), o_x = take(TC * 4), o_r = take(TC * 4), o_k = take(TC * 4), o_v = take(TC * 4),
+               o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
+               o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2);
+  if (m->seq_bytes < off) {
+    CU(cudaStreamSynchronize(st));
+    if (m->d_seq) cudaFree(m->d_seq);
+    m->d_seq = nullptr; m->seq_bytes = 0;
+    CU(cudaMalloc((void **)&m->d_seq, off));
+    m->seq_bytes = off;
+  }
+  uint8_t *B = m->d_seq;
+  int32_t *d_ids = (int32_t *)(B + o_ids);
+  float *x = (float *)(B + o_x), *r = (float *)(B + o_r), *k = (float *)(B + o_k), *v = (float *)(B + o_v), *y = (float *)(B + o_y);
+  __half *op[4] = {(__half *)(B + o_op0), (__half *)(B + o_op1), (__half *)(B + o_op2), (__half *)(B + o_op3)};
+  __half *g = (__half *)(B + o_g), *yn = (__half *)(B + o_yn), *kk = (__half *)(B + o_kk), *rr = g;   // rr reuses g
+  CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
+  CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
+  auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
+  auto wt = [&](const std::string &n) -> const __half * { return m->d_plain + m->mats[n].plain_off; };
+  auto gemm = [&](const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
+                  float scale) -> cudaError_t {
+    GemmArgs ga;
+    memset(&ga, 0, sizeof(ga));
+    ga.A = A; ga.Bt = wt(w); ga.M = T; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
+    ga.scale = scale; ga.status = m->out_status();
+    m->launches++;
+    return launch_gemm_f16(ga, st);
+  };
+  const int par = (int)m->par[slot];
+  const int nvec = m->gate ? 4 : 3;
+  for (int l = 0; l < m->L; ++l) {
+    const std::string b = "blocks." + std::to_string(l) + ".", a = b + "att.", f = b + "ffn.";
+    uint8_t *stb = m->d_state + (size_t)slot * m->state_stride + (size_t)l * m->layer_stride;
+    // ---- time mix ----
+    SeqLnArgs la;
+    memset(&la, 0, sizeof(la));
+    la.x = x; la.ln_w = vp(b + "ln1.weight"); la.ln_b = vp(b + "ln1.bias");
+    la.mix[0] = vp(a + "time_mix_k"); la.mix[1] = vp(a + "time_mix_v"); la.mix[2] = vp(a + "time_mix_r");
+    if (m->gate) la.mix[3] = vp(a + "time_mix_g");
+    for (int i = 0; i < 4; ++i) la.op[i] = op[i];
+    la.sx_rd = stb + off_sx(C, af, par); la.sx_wr = stb + off_sx(C, af, par ^ 1);
+    la.T = T; la.C = C; la.nvec = nvec; la.act_fp16 = af;
+    CU(launch_ln_mix_seq(la, st));
+    CU(gemm(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f));
+    CU(gemm(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f));
+    CU(gemm(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f));
+    if (m->gate) CU(gemm(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f));
+    SeqWkvArgs wa;
+    memset(&wa, 0, sizeof(wa));
+    wa.r = r; wa.k = k; wa.v = v; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
+    wa.state = reinterpret_cast<float *>(stb + off_mid(C, af)); wa.y = y; wa.T = T; wa.C = C;
+    wa.per_head = m->cfg.version == FR_B200_V5_0;
+    CU(launch_wkv5_seq(wa, H, st));
+    CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
+    CU(gemm(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f));
+    // ---- channel mix ----
+    memset(&la, 0, sizeof(la));
+    la.x = x; la.ln_w = vp(b + "ln2.weight"); la.ln_b = vp(b + "ln2.bias");
+    la.mix[0] = vp(f + "time_mix_k"); la.mix[1] = vp(f + "time_mix_r");
+    la.op[0] = op[0]; la.op[1] = op[1];
+    la.sx_rd = stb + off_ffn_sx(C, H, 1, af, par); la.sx_wr = stb + off_ffn_sx(C, H, 1, af, par ^ 1);
+    la.T = T; la.C = C; la.nvec = 2; la.act_fp16 = af;
+    CU(launch_ln_mix_seq(la, st));
+    CU(gemm(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f));
+    CU(gemm(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f));
+    const bool halve = af && (l + 1) % 6 == 0;   // x / 2 every 6 layers under fp16 activations (model_forward_seq.cpp:165-167)
+    CU(gemm(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f));
+    m->launches += 5;
+  }
+  // last token -> ln_out -> head, as a stand-alone matvec over the head's streaming tiles
+  CU(launch_ln_row(x + (size_t)(T - 1) * C, vp("ln_out.weight"), vp("ln_out.bias"), C, m->d_lnvec, st));
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.version = 4; p.L = 0; p.C = 64; p.F = C; p.V = m->V; p.Vpad = m->Vpad; p.fmt = m->fmt; p.B = 1; p.n_phases = 1;
+  p.phases = m->d_head_phase; p.kk = reinterpret_cast<exch_t *>(m->d_lnvec);   // PH_MATVEC reads kk as plain fp32
+  p.logits = m->d_out + (size_t)slot * m->Vpad; p.status = m->out_status();
+  int optin = 0, stages = 0;
+  CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
+  for (int sg = 6; sg >= 2; --sg)
+    if (decode_smem_bytes(m->fmt, 0, 64, C, 4, sg) <= (size_t)optin) { stages = sg; break; }
+  if (!stages) return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the head matvec");
+  p.n_stages = stages;
+  const size_t smem = decode_smem_bytes(m->fmt, 0, 64, C, 4, stages);
+  int grid = 0;
+  CU(decode_max_grid(m->fmt, 0, smem, m->device, &grid));
+  if (!grid) return fail(FR_B200_E_UNSUPPORTED, "kernel does not fit");
+  CU(launch_decode(p, 0, grid, smem, st));
+  m->launches += 3;
+  m->par[slot] ^= 1u;
+  return 0;
+}
+
+}  // namespace
+
 int fr_b200_run_seq(fr_b200_model *m, int slot, const int32_t *ids, int n, float *last_logits, void *stream) {
   if (!m || !ids || n < 1) return fail(FR_B200_E_ARG, "bad argument");
   if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
-  if (slot != 0) return fail(FR_B200_E_UNSUPPORTED, "run_seq uses stream slot 0");
+  if (slot < 0 || slot >= m->cfg.max_batch) return fail(FR_B200_E_ARG, "slot out of range");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int seq_min = 2;   // shorter prompts take the token loop
+  if (const char *e = getenv("FR_B200_SEQ_MIN")) seq_min = atoi(e);
+  if (m->d_plain && n >= seq_min) {
+    CU(cudaSetDevice(m->device));
+    for (int i = 0; i < n; ++i)
+      if (ids[i] < 0 || ids[i] >= m->V) return fail(FR_B200_E_ARG, "token id out of range");
+    int rc = seq_forward(m, slot, ids, n, st);
+    if (rc) return rc;
+    if (last_logits) {
+      if (is_host_ptr(last_logits)) {
+        CU(cudaMemcpyAsync(m->h_out, m->d_out + (size_t)slot * m->Vpad, (size_t)m->V * 4, cudaMemcpyDeviceToHost, st));
+      } else {
+        CU(cudaMemcpyAsync(last_logits, m->d_out + (size_t)slot * m->Vpad, (size_t)m->V * 4, cudaMemcpyDeviceToDevice, st));
+      }
+    }
+    CU(cudaStreamSynchronize(st));
+    int status = 0;
+    CU(cudaMemcpy(&status, m->out_status(), 4, cudaMemcpyDeviceToHost));
+    if ((rc = check_status(m, status))) return rc;
+    if (last_logits && is_host_ptr(last_logits)) memcpy(last_logits, m->h_out, (size_t)m->V * 4);
+    return FR_B200_OK;
+  }
+  if (slot != 0) return fail(FR_B200_E_UNSUPPORTED, "the token loop of run_seq uses stream slot 0");
   for (int i = 0; i < n; ++i) {
     int rc = fr_b200_decode(m, ids + i, 1, i == n - 1 ? last_logits : nullptr, nullptr, stream);
     if (rc) return rc;
   }
   if (!last_logits) {
-    CU(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+    CU(cudaStreamSynchronize(st));
     int status = 0;
     CU(cudaMemcpy(&status, m->out_status(), 4, cudaMemcpyDeviceToHost));
     return check_status(m, status);

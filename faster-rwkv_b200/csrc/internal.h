@@ -125,6 +125,29 @@ struct GemmArgs {
   int *status;         // device word: set when a bounded wait gives up
 };
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);
+// row kernels of seq mode
+struct SeqLnArgs {
+  const float *x;            // [T, C] residual stream
+  const float *ln_w, *ln_b;  // [C]
+  const float *mix[4];       // nvec mix vectors [C]
+  __half *op[4];             // nvec outputs [T, C]
+  const void *sx_rd;         // shift state read for token 0 (act dtype)
+  void *sx_wr;               // shift state written from token T-1
+  int T, C, nvec, act_fp16;
+};
+struct SeqWkvArgs {
+  const float *r, *k, *v;    // [T, C]
+  const float *decay, *first;  // [H * 64], or [H] when per_head
+  float *state;              // [H, 64 key, 64 value], updated in place
+  float *y;                  // [T, C]
+  int T, C, per_head;
+};
+cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st);
+cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st);
+cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st);
+cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
+                               cudaStream_t st);
+cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st);
 cudaError_t launch_transpose_f16(const __half *src, int K, int N, __half *dst, cudaStream_t st);   // [K,N] -> [N,K]
 
 // ---- launchers implemented in the .cu files ------------------------------------------------------

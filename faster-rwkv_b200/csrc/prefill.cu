@@ -245,6 +245,189 @@ cudaError_t launch_transpose_f16(const __half *src, int K, int N, __half *dst, c
   return cudaGetLastError();
 }
 
+namespace {
+
+// ---- block reductions (blockDim.x = 256) -------------------------------------------------------------
+__device__ __forceinline__ float2 block_sum2(float a, float b, float *red /* [16] */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();   // red may still be read from the previous call
+  if (lane == 0) { red[warp * 2] = a; red[warp * 2 + 1] = b; }
+  __syncthreads();
+  float sa = 0.f, sb = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) { sa += red[w * 2]; sb += red[w * 2 + 1]; }
+  return make_float2(sa, sb);
+}
+
+// mean and 1/std of one fp32 row (shifted single pass, like the decode prologue)
+__device__ __forceinline__ float2 row_stats(const float *x, int C, float *red) {
+  const float piv = x[0];
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    const float d = x[i] - piv;
+    s1 += d; s2 += d * d;
+  }
+  const float2 s = block_sum2(s1, s2, red);
+  const float m = s.x / (float)C;
+  float var = s.y / (float)C - m * m;
+  var = var > 0.f ? var : 0.f;
+  return make_float2(piv + m, rsqrtf(var + 1e-5f));
+}
+
+// x[t, :] = embedding row of ids[t]
+__global__ void gather_emb_kernel(const void *emb, int emb_f32, const int32_t *ids, int C, float *x) {
+  const int t = blockIdx.x;
+  const size_t row = (size_t)ids[t] * C;
+  for (int i = threadIdx.x; i < C; i += blockDim.x)
+    x[(size_t)t * C + i] = emb_f32 ? reinterpret_cast<const float *>(emb)[row + i]
+                                   : __half2float(reinterpret_cast<const __half *>(emb)[row + i]);
+}
+
+// LayerNorm + token shift + mix for every token row (LN of att_seq.cu:375, the shifted cat of :377-381 and the
+// MixWithG of :384; ffn_seq.cu:70-76): op_v[t] = xx[t] * mu_v + prev[t] * (1 - mu_v), prev[0] = the stored shift
+// state, prev[t] = xx[t-1]; the new shift state is xx[T-1].  One CTA per token; it normalises its own row and the
+// row before it, so no CTA waits for another.
+__global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
+  __shared__ float red[16];
+  const int t = blockIdx.x, C = a.C;
+  const float *xr = a.x + (size_t)t * C;
+  const float2 st = row_stats(xr, C, red);
+  float2 sp = make_float2(0.f, 0.f);
+  if (t > 0) sp = row_stats(xr - C, C, red);
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    const float w = a.ln_w[i], b = a.ln_b[i];
+    const float xx = (xr[i] - st.x) * st.y * w + b;
+    float prev;
+    if (t > 0) prev = (xr[i - C] - sp.x) * sp.y * w + b;
+    else prev = a.act_fp16 ? __half2float(reinterpret_cast<const __half *>(a.sx_rd)[i]) : reinterpret_cast<const float *>(a.sx_rd)[i];
+    if (a.act_fp16 && t > 0) prev = __half2float(__float2half_rn(prev));   // what the token loop would have stored as shift state
+    const float xh = xx;
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      if (v < a.nvec) {
+        const float m = a.mix[v][i];
+        a.op[v][(size_t)t * C + i] = __float2half_rn(xh * m + prev * (1.f - m));
+      }
+    if (t == a.T - 1) {
+      if (a.act_fp16) reinterpret_cast<__half *>(a.sx_wr)[i] = __float2half_rn(xx);
+      else reinterpret_cast<float *>(a.sx_wr)[i] = xx;
+    }
+  }
+}
+
+// RWKV-5 state scan over T tokens of one head (rwkv5_2_kernel_forward, att_seq.cu:258-322; per-head decay for 5.0):
+//   y[t, j] = sum_i r[t,i] * (u_i * k[t,i] * v[t,j] + s[i,j]);   s[i,j] = w_i * s[i,j] + k[t,i] * v[t,j]
+// One CTA per head, 256 threads: thread (j, iq) keeps s[16 iq .. 16 iq + 15][j] in registers for the whole
+// sequence; r, k, v of 16 tokens at a time go through shared memory.
+constexpr int WKV_TT = 16;
+__global__ void __launch_bounds__(256) wkv5_seq_kernel(SeqWkvArgs a) {
+  __shared__ __align__(16) float sr[WKV_TT][64], sk[WKV_TT][64], sv[WKV_TT][64];
+  const int h = blockIdx.x, C = a.C;
+  const int j = threadIdx.x >> 2, iq = threadIdx.x & 3;
+  float *S = a.state + (size_t)h * 4096;
+  float s[16], w[16], u[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int ii = iq * 16 + i;
+    s[i] = S[ii * 64 + j];
+    w[i] = a.per_head ? a.decay[h] : a.decay[h * 64 + ii];
+    u[i] = a.per_head ? a.first[h] : a.first[h * 64 + ii];
+  }
+  for (int t0 = 0; t0 < a.T; t0 += WKV_TT) {
+    const int nt = min(WKV_TT, a.T - t0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nt * 64; e += blockDim.x) {
+      const int tt = e >> 6, c = e & 63;
+      const size_t g = (size_t)(t0 + tt) * C + h * 64 + c;
+      sr[tt][c] = a.r[g]; sk[tt][c] = a.k[g]; sv[tt][c] = a.v[g];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vj = sv[tt][j];
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) {
+        const float4 r4 = *reinterpret_cast<const float4 *>(&sr[tt][iq * 16 + i]);
+        const float4 k4 = *reinterpret_cast<const float4 *>(&sk[tt][iq * 16 + i]);
+        float x;
+        x = k4.x * vj; y0 += r4.x * (u[i] * x + s[i]);         s[i] = s[i] * w[i] + x;
+        x = k4.y * vj; y1 += r4.y * (u[i + 1] * x + s[i + 1]); s[i + 1] = s[i + 1] * w[i + 1] + x;
+        x = k4.z * vj; y0 += r4.z * (u[i + 2] * x + s[i + 2]); s[i + 2] = s[i + 2] * w[i + 2] + x;
+        x = k4.w * vj; y1 += r4.w * (u[i + 3] * x + s[i + 3]); s[i + 3] = s[i + 3] * w[i + 3] + x;
+      }
+      float y = y0 + y1;
+      y += __shfl_xor_sync(0xffffffffu, y, 1);
+      y += __shfl_xor_sync(0xffffffffu, y, 2);
+      if (iq == 0) a.y[(size_t)(t0 + tt) * C + h * 64 + j] = y;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) S[(iq * 16 + i) * 64 + j] = s[i];
+}
+
+// GroupNorm over each head's 64 readout values (eps 1e-5, fp32 affine), times the gate where the version has one
+// (att_seq.cu:406-415): one warp per (token, head)
+__global__ void __launch_bounds__(256) gn_gate_seq_kernel(const float *y, const float *lnx_w, const float *lnx_b, const __half *g,
+                                                          int T, int H, __half *out) {
+  const int unit = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (unit >= T * H) return;
+  const int t = unit / H, h = unit - t * H;
+  const size_t o = (size_t)t * H * 64 + h * 64 + lane * 2;
+  const float2 v = *reinterpret_cast<const float2 *>(y + o);
+  float s = v.x + v.y;
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+  const float mean = s * (1.f / 64.f);
+  const float d0 = v.x - mean, d1 = v.y - mean;
+  float q = d0 * d0 + d1 * d1;
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) q += __shfl_xor_sync(0xffffffffu, q, k);
+  const float rstd = rsqrtf(q * (1.f / 64.f) + 1e-5f);
+  const int c = h * 64 + lane * 2;
+  float a0 = d0 * rstd * lnx_w[c] + lnx_b[c], a1 = d1 * rstd * lnx_w[c + 1] + lnx_b[c + 1];
+  if (g) {
+    const float2 gg = __half22float2(*reinterpret_cast<const __half2 *>(g + o));
+    a0 *= gg.x; a1 *= gg.y;
+  }
+  *reinterpret_cast<__half2 *>(out + o) = __floats2half2_rn(a0, a1);
+}
+
+// plain LayerNorm of one row -> fp32 vector (ln_out before the head, model_forward_seq.cpp:171-175)
+__global__ void __launch_bounds__(256) ln_row_kernel(const float *x, const float *w, const float *b, int C, float *out) {
+  __shared__ float red[16];
+  const float2 st = row_stats(x, C, red);
+  for (int i = threadIdx.x; i < C; i += blockDim.x) out[i] = (x[i] - st.x) * st.y * w[i] + b[i];
+}
+
+}  // namespace
+
+cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st) {
+  gather_emb_kernel<<<T, 256, 0, st>>>(emb, emb_f32, ids, C, x);
+  return cudaGetLastError();
+}
+cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
+  ln_mix_seq_kernel<<<a.T, 256, 0, st>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
+  wkv5_seq_kernel<<<H, 256, 0, st>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
+                               cudaStream_t st) {
+  gn_gate_seq_kernel<<<(T * H + 7) / 8, 256, 0, st>>>(y, lnx_w, lnx_b, g, T, H, out);
+  return cudaGetLastError();
+}
+cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st) {
+  ln_row_kernel<<<1, 256, 0, st>>>(x, w, b, C, out);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st) {
   if (g.K % GBK != 0 || g.M < 1 || g.N < 1) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Bt) & 15)) return cudaErrorInvalidValue;
