@@ -84,13 +84,27 @@ def gpu_master_weights(shape, seed: int, device):
         for ln in (b + "ln1", b + "ln2"):
             yield ln + ".weight", torch.ones(C, device=device)
             yield ln + ".bias", torch.zeros(C, device=device)
-        for m in ("k", "v", "r"):
+        v5 = str(shape.version).startswith("5")
+        gate = str(shape.version) in ("5.1", "5.2")
+        if v5:
+            yield a + "ln_x.weight", torch.ones(C, device=device)
+            yield a + "ln_x.bias", torch.zeros(C, device=device)
+        for m in ("k", "v", "r") + (("g",) if gate else ()):
             yield a + "time_mix_" + m, uni(C, 0, 1)
-        yield a + "time_decay", -torch.exp(uni(C, -6, 1))
-        yield a + "time_first", uni(C, -1, 1)
+        if not v5:
+            yield a + "time_decay", -torch.exp(uni(C, -6, 1))
+            yield a + "time_first", uni(C, -1, 1)
+        elif str(shape.version) == "5":
+            yield a + "time_decay", torch.exp(-torch.exp(uni(shape.n_head, -6, 1))).reshape(shape.n_head, 1, 1)
+            yield a + "time_first", uni(shape.n_head, -1, 1).reshape(shape.n_head, 1, 1)
+        else:
+            yield a + "time_decay", torch.exp(-torch.exp(uni(C, -6, 1))).reshape(shape.n_head, C // shape.n_head, 1)
+            yield a + "time_first", uni(C, -1, 1).reshape(shape.n_head, C // shape.n_head, 1)
         yield a + "key.weight", mat(C, C)
         yield a + "value.weight", mat(C, C)
         yield a + "receptance.weight", mat(C, C)
+        if gate:
+            yield a + "gate.weight", mat(C, C)
         yield a + "output.weight", mat(C, C)
         yield f + "time_mix_k", uni(C, 0, 1)
         yield f + "time_mix_r", uni(C, 0, 1)
@@ -113,7 +127,7 @@ def build_model(pkg, shape, fmt: str, max_batch: int, device_index: int, seed: i
             for name, t in gpu_master_weights(shape, seed, dev):
                 if keep_host is not None:
                     keep_host[name] = t.cpu().numpy()
-                if fmt == "fp16" and not name.endswith(("time_decay", "time_first")):
+                if fmt == "fp16" and not name.endswith(("time_decay", "time_first", "ln_x.weight", "ln_x.bias")):
                     if name.endswith(("att.output.weight", "ffn.value.weight")):
                         t = t / float(2 ** (int(name.split(".")[1]) // 6))
                     t = t.half()

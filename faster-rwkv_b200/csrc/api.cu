@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <map>
 #include <string>
 #include <vector>
@@ -676,6 +677,11 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
   const size_t o_ids = take((size_t)T * 4), o_x = take(TC * 4), o_r = take(TC * 4), o_k = take(TC * 4), o_v = take(TC * 4),
                o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
                o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2);
+  // state scan: enough chunks to cover the SMs a few times over, none shorter than 32 tokens
+  int n_chunks = std::max(1, std::min(T / 32, (4 * 148 + H - 1) / H));
+  const int chunk_len = (T + n_chunks - 1) / n_chunks;
+  n_chunks = (T + chunk_len - 1) / chunk_len;
+  const size_t o_e = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0), o_sin = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0);
   if (m->seq_bytes < off) {
     CU(cudaStreamSynchronize(st));
     if (m->d_seq) cudaFree(m->d_seq);
@@ -725,6 +731,7 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     wa.r = r; wa.k = k; wa.v = v; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
     wa.state = reinterpret_cast<float *>(stb + off_mid(C, af)); wa.y = y; wa.T = T; wa.C = C;
     wa.per_head = m->cfg.version == FR_B200_V5_0;
+    wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e); wa.s_in = (float *)(B + o_sin);
     CU(launch_wkv5_seq(wa, H, st));
     CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
     CU(gemm(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f));

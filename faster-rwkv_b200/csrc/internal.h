@@ -141,6 +141,8 @@ struct SeqWkvArgs {
   float *state;              // [H, 64 key, 64 value], updated in place
   float *y;                  // [T, C]
   int T, C, per_head;
+  int n_chunks, chunk_len;   // the sequence is scanned in n_chunks parallel pieces of chunk_len tokens
+  float *e_out, *s_in;       // [H, n_chunks, 64, 64] scratch: chunk end states from zero, chunk start states
 };
 cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st);
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st);

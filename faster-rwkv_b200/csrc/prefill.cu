@@ -69,16 +69,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ float sigmoid_g(float v) { return 1.f / (1.f + expf(-v)); }
+// the result is rounded to fp16: the fast exponential and division are exact enough
+__device__ __forceinline__ float sigmoid_g(float v) { return __fdividef(1.f, 1.f + __expf(-v)); }
 
-// Epilogue of 32 consecutive columns of one output row.
+// Epilogue of 32 consecutive columns of one output row (16-byte accesses when all 32 columns exist).
+__device__ __forceinline__ float epi_half_op(int epi, float a) {
+  if (epi == GEMM_EPI_SILU_F16) return a * sigmoid_g(a);
+  if (epi == GEMM_EPI_SIGMOID_F16) return sigmoid_g(a);
+  if (epi == GEMM_EPI_RELU2_F16) { a = fmaxf(a, 0.f); return a * a; }
+  return a;
+}
 __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, int col0, const uint32_t (&acc)[32]) {
   const int ncol = min(32, g.N - col0);
   if (ncol <= 0) return;
   const size_t o = (size_t)row * g.ldo + col0;
+  const bool full = ncol == 32 && (g.ldo & 7) == 0;
   if (g.epi == GEMM_EPI_F32) {
     float *out = reinterpret_cast<float *>(g.out) + o;
-    if (ncol == 32) {
+    if (full) {
 #pragma unroll
       for (int i = 0; i < 32; i += 4)
         *reinterpret_cast<float4 *>(out + i) = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
@@ -93,21 +101,49 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
     float *out = reinterpret_cast<float *>(g.out) + o;
     const float *x = reinterpret_cast<const float *>(g.aux0) + o;
     const __half *r = reinterpret_cast<const __half *>(g.aux1) + o;
-    for (int i = 0; i < ncol; ++i) {
-      float a = __uint_as_float(acc[i]);
-      if (g.epi == GEMM_EPI_MULADD_F32) a *= __half2float(r[i]);
-      out[i] = (x[i] + a) * g.scale;
+    const bool mul = g.epi == GEMM_EPI_MULADD_F32;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        const float4 x0 = *reinterpret_cast<const float4 *>(x + i), x1 = *reinterpret_cast<const float4 *>(x + i + 4);
+        float rr[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+        if (mul) {
+          const uint4 rw = *reinterpret_cast<const uint4 *>(r + i);
+          const float2 r0 = __half22float2(*reinterpret_cast<const __half2 *>(&rw.x)), r1 = __half22float2(*reinterpret_cast<const __half2 *>(&rw.y));
+          const float2 r2 = __half22float2(*reinterpret_cast<const __half2 *>(&rw.z)), r3 = __half22float2(*reinterpret_cast<const __half2 *>(&rw.w));
+          rr[0] = r0.x; rr[1] = r0.y; rr[2] = r1.x; rr[3] = r1.y; rr[4] = r2.x; rr[5] = r2.y; rr[6] = r3.x; rr[7] = r3.y;
+        }
+        float4 y0, y1;
+        y0.x = (x0.x + rr[0] * __uint_as_float(acc[i])) * g.scale;     y0.y = (x0.y + rr[1] * __uint_as_float(acc[i + 1])) * g.scale;
+        y0.z = (x0.z + rr[2] * __uint_as_float(acc[i + 2])) * g.scale; y0.w = (x0.w + rr[3] * __uint_as_float(acc[i + 3])) * g.scale;
+        y1.x = (x1.x + rr[4] * __uint_as_float(acc[i + 4])) * g.scale; y1.y = (x1.y + rr[5] * __uint_as_float(acc[i + 5])) * g.scale;
+        y1.z = (x1.z + rr[6] * __uint_as_float(acc[i + 6])) * g.scale; y1.w = (x1.w + rr[7] * __uint_as_float(acc[i + 7])) * g.scale;
+        *reinterpret_cast<float4 *>(out + i) = y0;
+        *reinterpret_cast<float4 *>(out + i + 4) = y1;
+      }
+    } else {
+      for (int i = 0; i < ncol; ++i) {
+        float a = __uint_as_float(acc[i]);
+        if (mul) a *= __half2float(r[i]);
+        out[i] = (x[i] + a) * g.scale;
+      }
     }
     return;
   }
   __half *out = reinterpret_cast<__half *>(g.out) + o;
-  for (int i = 0; i < ncol; i += 2) {
-    float a = __uint_as_float(acc[i]), b = i + 1 < ncol ? __uint_as_float(acc[i + 1]) : 0.f;
-    if (g.epi == GEMM_EPI_SILU_F16) { a = a * sigmoid_g(a); b = b * sigmoid_g(b); }
-    else if (g.epi == GEMM_EPI_SIGMOID_F16) { a = sigmoid_g(a); b = sigmoid_g(b); }
-    else if (g.epi == GEMM_EPI_RELU2_F16) { a = fmaxf(a, 0.f); a *= a; b = fmaxf(b, 0.f); b *= b; }
-    if (i + 1 < ncol) *reinterpret_cast<__half2 *>(out + i) = __floats2half2_rn(a, b);
-    else out[i] = __float2half_rn(a);
+  if (full) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      uint4 w;
+      __half2 h;
+      h = __floats2half2_rn(epi_half_op(g.epi, __uint_as_float(acc[i])), epi_half_op(g.epi, __uint_as_float(acc[i + 1])));     w.x = *reinterpret_cast<uint32_t *>(&h);
+      h = __floats2half2_rn(epi_half_op(g.epi, __uint_as_float(acc[i + 2])), epi_half_op(g.epi, __uint_as_float(acc[i + 3]))); w.y = *reinterpret_cast<uint32_t *>(&h);
+      h = __floats2half2_rn(epi_half_op(g.epi, __uint_as_float(acc[i + 4])), epi_half_op(g.epi, __uint_as_float(acc[i + 5]))); w.z = *reinterpret_cast<uint32_t *>(&h);
+      h = __floats2half2_rn(epi_half_op(g.epi, __uint_as_float(acc[i + 6])), epi_half_op(g.epi, __uint_as_float(acc[i + 7]))); w.w = *reinterpret_cast<uint32_t *>(&h);
+      *reinterpret_cast<uint4 *>(out + i) = w;
+    }
+  } else {
+    for (int i = 0; i < ncol; ++i) out[i] = __float2half_rn(epi_half_op(g.epi, __uint_as_float(acc[i])));
   }
 }
 
@@ -320,54 +356,108 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
   }
 }
 
-// RWKV-5 state scan over T tokens of one head (rwkv5_2_kernel_forward, att_seq.cu:258-322; per-head decay for 5.0):
+// RWKV-5 state scan over the tokens of one head (rwkv5_2_kernel_forward, att_seq.cu:258-322; per-head decay for 5.0):
 //   y[t, j] = sum_i r[t,i] * (u_i * k[t,i] * v[t,j] + s[i,j]);   s[i,j] = w_i * s[i,j] + k[t,i] * v[t,j]
-// One CTA per head, 256 threads: thread (j, iq) keeps s[16 iq .. 16 iq + 15][j] in registers for the whole
-// sequence; r, k, v of 16 tokens at a time go through shared memory.
+// 256 threads per CTA: thread (j, iq) keeps s[16 iq .. 16 iq + 15][j] in registers; r, k, v of 16 tokens at a time
+// arrive in shared memory by cp.async, the next 16 while the current ones are used.
+// The sequence is cut into n_chunks pieces that run in parallel (the reference walks it serially):
+//   mode 0  state only, from zero, over chunk c               -> E[h][c]        (grid H x n_chunks)
+//   mode 1  S_in[h][0] = state; S_in[h][c+1] = w^len(c) * S_in[h][c] + E[h][c]; state = the last one   (grid H)
+//   mode 2  full recurrence over chunk c from S_in[h][c]       -> y              (grid H x n_chunks)
+// With n_chunks == 1 mode 2 alone reads and writes the model state directly.
 constexpr int WKV_TT = 16;
+
+__device__ __forceinline__ void wkv_stage(float (*sr)[64], float (*sk)[64], float (*sv)[64], const SeqWkvArgs &a, int h, int t0,
+                                          int nt, bool with_r) {
+  // 16 floats = 4 x 16 bytes per (token, vector) quarter row: 3 vectors x nt tokens x 16 pieces
+  for (int e = threadIdx.x; e < nt * 16; e += blockDim.x) {
+    const int tt = e >> 4, c = (e & 15) * 4;
+    const size_t g = (size_t)(t0 + tt) * a.C + h * 64 + c;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&sk[tt][c])), "l"(a.k + g) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&sv[tt][c])), "l"(a.v + g) : "memory");
+    if (with_r) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&sr[tt][c])), "l"(a.r + g) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(256) wkv5_seq_kernel(SeqWkvArgs a) {
-  __shared__ __align__(16) float sr[WKV_TT][64], sk[WKV_TT][64], sv[WKV_TT][64];
-  const int h = blockIdx.x, C = a.C;
+  __shared__ __align__(16) float sr[2][WKV_TT][64], sk[2][WKV_TT][64], sv[2][WKV_TT][64];
+  const int h = blockIdx.x, c = blockIdx.y, C = a.C;
   const int j = threadIdx.x >> 2, iq = threadIdx.x & 3;
-  float *S = a.state + (size_t)h * 4096;
+  const int t_begin = c * a.chunk_len, t_end = min(a.T, t_begin + a.chunk_len);
   float s[16], w[16], u[16];
+  const float *Sin = a.n_chunks == 1 ? a.state + (size_t)h * 4096 : a.s_in + ((size_t)h * a.n_chunks + c) * 4096;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int ii = iq * 16 + i;
-    s[i] = S[ii * 64 + j];
+    s[i] = MODE == 0 ? 0.f : Sin[ii * 64 + j];
     w[i] = a.per_head ? a.decay[h] : a.decay[h * 64 + ii];
     u[i] = a.per_head ? a.first[h] : a.first[h * 64 + ii];
   }
-  for (int t0 = 0; t0 < a.T; t0 += WKV_TT) {
-    const int nt = min(WKV_TT, a.T - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nt * 64; e += blockDim.x) {
-      const int tt = e >> 6, c = e & 63;
-      const size_t g = (size_t)(t0 + tt) * C + h * 64 + c;
-      sr[tt][c] = a.r[g]; sk[tt][c] = a.k[g]; sv[tt][c] = a.v[g];
+  int buf = 0;
+  if (t_begin < t_end) wkv_stage(sr[0], sk[0], sv[0], a, h, t_begin, min(WKV_TT, t_end - t_begin), MODE == 2);
+  for (int t0 = t_begin; t0 < t_end; t0 += WKV_TT) {
+    const int nt = min(WKV_TT, t_end - t0);
+    const int tn = t0 + WKV_TT;
+    if (tn < t_end) {
+      wkv_stage(sr[buf ^ 1], sk[buf ^ 1], sv[buf ^ 1], a, h, tn, min(WKV_TT, t_end - tn), MODE == 2);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float vj = sv[tt][j];
+      const float vj = sv[buf][tt][j];
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
-        const float4 r4 = *reinterpret_cast<const float4 *>(&sr[tt][iq * 16 + i]);
-        const float4 k4 = *reinterpret_cast<const float4 *>(&sk[tt][iq * 16 + i]);
+        const float4 k4 = *reinterpret_cast<const float4 *>(&sk[buf][tt][iq * 16 + i]);
+        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE == 2) r4 = *reinterpret_cast<const float4 *>(&sr[buf][tt][iq * 16 + i]);
         float x;
-        x = k4.x * vj; y0 += r4.x * (u[i] * x + s[i]);         s[i] = s[i] * w[i] + x;
-        x = k4.y * vj; y1 += r4.y * (u[i + 1] * x + s[i + 1]); s[i + 1] = s[i + 1] * w[i + 1] + x;
-        x = k4.z * vj; y0 += r4.z * (u[i + 2] * x + s[i + 2]); s[i + 2] = s[i + 2] * w[i + 2] + x;
-        x = k4.w * vj; y1 += r4.w * (u[i + 3] * x + s[i + 3]); s[i + 3] = s[i + 3] * w[i + 3] + x;
+        x = k4.x * vj; if (MODE == 2) y0 += r4.x * (u[i] * x + s[i]);         s[i] = s[i] * w[i] + x;
+        x = k4.y * vj; if (MODE == 2) y1 += r4.y * (u[i + 1] * x + s[i + 1]); s[i + 1] = s[i + 1] * w[i + 1] + x;
+        x = k4.z * vj; if (MODE == 2) y0 += r4.z * (u[i + 2] * x + s[i + 2]); s[i + 2] = s[i + 2] * w[i + 2] + x;
+        x = k4.w * vj; if (MODE == 2) y1 += r4.w * (u[i + 3] * x + s[i + 3]); s[i + 3] = s[i + 3] * w[i + 3] + x;
       }
-      float y = y0 + y1;
-      y += __shfl_xor_sync(0xffffffffu, y, 1);
-      y += __shfl_xor_sync(0xffffffffu, y, 2);
-      if (iq == 0) a.y[(size_t)(t0 + tt) * C + h * 64 + j] = y;
+      if (MODE == 2) {
+        float y = y0 + y1;
+        y += __shfl_xor_sync(0xffffffffu, y, 1);
+        y += __shfl_xor_sync(0xffffffffu, y, 2);
+        if (iq == 0) a.y[(size_t)(t0 + tt) * C + h * 64 + j] = y;
+      }
     }
+    __syncthreads();   // the buffer just read is the one the next staging overwrites
+    buf ^= 1;
   }
+  if (MODE == 0) {
+    float *E = a.e_out + ((size_t)h * a.n_chunks + c) * 4096;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) S[(iq * 16 + i) * 64 + j] = s[i];
+    for (int i = 0; i < 16; ++i) E[(iq * 16 + i) * 64 + j] = s[i];
+  } else if (a.n_chunks == 1) {
+    float *S = a.state + (size_t)h * 4096;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) S[(iq * 16 + i) * 64 + j] = s[i];
+  }
+}
+
+// mode 1: chain the chunk states of one head
+__global__ void __launch_bounds__(256) wkv5_combine_kernel(SeqWkvArgs a) {
+  const int h = blockIdx.x;
+  float *S = a.state + (size_t)h * 4096;
+  for (int e = threadIdx.x; e < 4096; e += blockDim.x) {
+    const int i = e >> 6;
+    const float w = a.per_head ? a.decay[h] : a.decay[h * 64 + i];
+    const float lw = log2f(w);
+    float s = S[e];
+    for (int c = 0; c < a.n_chunks; ++c) {
+      a.s_in[((size_t)h * a.n_chunks + c) * 4096 + e] = s;
+      const int len = min(a.T, (c + 1) * a.chunk_len) - c * a.chunk_len;
+      s = exp2f(lw * (float)len) * s + a.e_out[((size_t)h * a.n_chunks + c) * 4096 + e];
+    }
+    S[e] = s;
+  }
 }
 
 // GroupNorm over each head's 64 readout values (eps 1e-5, fp32 affine), times the gate where the version has one
@@ -415,7 +505,13 @@ cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
   return cudaGetLastError();
 }
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
-  wkv5_seq_kernel<<<H, 256, 0, st>>>(a);
+  if (a.n_chunks <= 1) {
+    wkv5_seq_kernel<2><<<dim3(H, 1), 256, 0, st>>>(a);
+    return cudaGetLastError();
+  }
+  wkv5_seq_kernel<0><<<dim3(H, a.n_chunks), 256, 0, st>>>(a);
+  wkv5_combine_kernel<<<H, 256, 0, st>>>(a);
+  wkv5_seq_kernel<2><<<dim3(H, a.n_chunks), 256, 0, st>>>(a);
   return cudaGetLastError();
 }
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
