@@ -676,7 +676,7 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
   auto take = [&](size_t bytes) { const size_t o = off; off += align256(bytes); return o; };
   const size_t o_ids = take((size_t)T * 4), o_x = take(TC * 4), o_r = take(TC * 4), o_k = take(TC * 4), o_v = take(TC * 4),
                o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
-               o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2);
+               o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2), o_lo0 = take(TC * 2), o_lo1 = take(TC * 2);
   // state scan: enough chunks to cover the SMs a few times over, none shorter than 32 tokens
   int n_chunks = std::max(1, std::min(T / 32, (4 * 148 + H - 1) / H));
   const int chunk_len = (T + n_chunks - 1) / n_chunks;
@@ -694,15 +694,16 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
   float *x = (float *)(B + o_x), *r = (float *)(B + o_r), *k = (float *)(B + o_k), *v = (float *)(B + o_v), *y = (float *)(B + o_y);
   __half *op[4] = {(__half *)(B + o_op0), (__half *)(B + o_op1), (__half *)(B + o_op2), (__half *)(B + o_op3)};
   __half *g = (__half *)(B + o_g), *yn = (__half *)(B + o_yn), *kk = (__half *)(B + o_kk), *rr = g;   // rr reuses g
+  __half *lo0 = (__half *)(B + o_lo0), *lo1 = (__half *)(B + o_lo1);
   CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
   CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
   auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
   auto wt = [&](const std::string &n) -> const __half * { return m->d_plain + m->mats[n].plain_off; };
   auto gemm = [&](const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
-                  float scale) -> cudaError_t {
+                  float scale, const __half *A2 = nullptr) -> cudaError_t {
     GemmArgs ga;
     memset(&ga, 0, sizeof(ga));
-    ga.A = A; ga.Bt = wt(w); ga.M = T; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
+    ga.A = A; ga.A2 = A2; ga.Bt = wt(w); ga.M = T; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
     ga.scale = scale; ga.status = m->out_status();
     m->launches++;
     return launch_gemm_f16(ga, st);
@@ -721,9 +722,12 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     for (int i = 0; i < 4; ++i) la.op[i] = op[i];
     la.sx_rd = stb + off_sx(C, af, par); la.sx_wr = stb + off_sx(C, af, par ^ 1);
     la.T = T; la.C = C; la.nvec = nvec; la.act_fp16 = af;
+    // k and v build the recurrent state, which keeps growing with the prompt: their projections take the
+    // activations as hi + lo fp16 pairs (a second pass over K), like every decode matvec does
+    la.op_lo[0] = lo0; la.op_lo[1] = lo1;
     CU(launch_ln_mix_seq(la, st));
-    CU(gemm(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f));
-    CU(gemm(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f));
+    CU(gemm(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0));
+    CU(gemm(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f, lo1));
     CU(gemm(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f));
     if (m->gate) CU(gemm(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f));
     SeqWkvArgs wa;

@@ -115,6 +115,7 @@ enum GemmEpilogue {
 };
 struct GemmArgs {
   const __half *A;     // [M, K] row-major
+  const __half *A2;    // optional [M, K]: low halves of the activations (A + A2 is the fp32 value to ~22 bits)
   const __half *Bt;    // [N, K] row-major (the weight matrix transposed: one row per output channel)
   int M, N, K;         // K a multiple of 64
   int epi;
@@ -131,6 +132,7 @@ struct SeqLnArgs {
   const float *ln_w, *ln_b;  // [C]
   const float *mix[4];       // nvec mix vectors [C]
   __half *op[4];             // nvec outputs [T, C]
+  __half *op_lo[4];          // optional: what the fp16 rounding of op[v] lost (null = not wanted)
   const void *sx_rd;         // shift state read for token 0 (act dtype)
   void *sx_wr;               // shift state written from token T-1
   int T, C, nvec, act_fp16;

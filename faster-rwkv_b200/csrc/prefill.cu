@@ -19,7 +19,8 @@ namespace frb {
 namespace {
 
 // ------------------------------------------------------------------------------------------------
-// tcgen05 GEMM: out[M, N] = epilogue(A[M, K] . Bt[N, K]^T), fp16 operands (both K-major), fp32 accumulate.
+// tcgen05 GEMM: out[M, N] = epilogue((A + A2)[M, K] . Bt[N, K]^T), fp16 operands (both K-major), fp32 accumulate.
+// A2 (optional) holds what rounding the activations to fp16 lost; it makes a second pass over K.
 // One CTA per 128 x 256 output tile; K is walked in 64-wide slices through a 4-deep TMA ring.
 //   warp 0 (one lane): TMA producer          warp 1 (one lane): MMA issue; the warp owns the TMEM allocation
 //   warps 2..5: epilogue, one TMEM lane quadrant (32 rows) each
@@ -148,7 +149,8 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
 }
 
 __global__ void __launch_bounds__(G_THREADS, 1)
-gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmArgs g) {
+gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_a2,
+                const __grid_constant__ CUtensorMap tma_b, const GemmArgs g) {
   extern __shared__ uint8_t gsm_raw[];
   // barriers in the first KB, tiles from the next 1024-byte boundary
   uint8_t *gsm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
@@ -160,7 +162,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const uint32_t tiles = smem_u32(gsm + 1024);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_m = blockIdx.y, tile_n = blockIdx.x;
-  const int num_k = g.K / GBK;
+  const int num_k1 = g.K / GBK;
+  const int num_k = g.A2 ? 2 * num_k1 : num_k1;   // a second pass over K with the low halves of A, same accumulator
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GSTAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -185,8 +188,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         if (!mbar_wait(&empty[s], parity, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
         mbar_expect_tx(&full[s], G_STAGE_BYTES);
         const uint32_t a_dst = tiles + (uint32_t)s * G_STAGE_BYTES;
-        tma_load_2d(a_dst, &tma_a, kb * GBK, tile_m * GBM, &full[s]);
-        tma_load_2d(a_dst + G_A_BYTES, &tma_b, kb * GBK, tile_n * GBN, &full[s]);
+        const int kk = kb < num_k1 ? kb : kb - num_k1;
+        tma_load_2d(a_dst, kb < num_k1 ? &tma_a : &tma_a2, kk * GBK, tile_m * GBM, &full[s]);
+        tma_load_2d(a_dst + G_A_BYTES, &tma_b, kk * GBK, tile_n * GBN, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -347,7 +351,10 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
     for (int v = 0; v < 4; ++v)
       if (v < a.nvec) {
         const float m = a.mix[v][i];
-        a.op[v][(size_t)t * C + i] = __float2half_rn(xh * m + prev * (1.f - m));
+        const float val = xh * m + prev * (1.f - m);
+        const __half hi = __float2half_rn(val);
+        a.op[v][(size_t)t * C + i] = hi;
+        if (a.op_lo[v]) a.op_lo[v][(size_t)t * C + i] = __float2half_rn(val - __half2float(hi));
       }
     if (t == a.T - 1) {
       if (a.act_fp16) reinterpret_cast<__half *>(a.sx_wr)[i] = __float2half_rn(xx);
@@ -527,12 +534,13 @@ cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C,
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st) {
   if (g.K % GBK != 0 || g.M < 1 || g.N < 1) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Bt) & 15)) return cudaErrorInvalidValue;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, ma2, mb;
   if (!make_map(&ma, g.A, g.M, g.K, GBM) || !make_map(&mb, g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
+  if (!make_map(&ma2, g.A2 ? g.A2 : g.A, g.M, g.K, GBM)) return cudaErrorNotSupported;
   cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM);
   if (e != cudaSuccess) return e;
   dim3 grid((g.N + GBN - 1) / GBN, (g.M + GBM - 1) / GBM);
-  gemm_f16_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ma, mb, g);
+  gemm_f16_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ma, ma2, mb, g);
   return cudaGetLastError();
 }
 

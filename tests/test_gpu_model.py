@@ -98,14 +98,18 @@ def test_reset_is_bit_identical_and_deterministic(pkg, orc, synth):
 
 def test_seq_equals_token_loop(pkg, orc, synth):
     """kernels/default/model_forward_seq.cpp:34-46: Run([a,b,c]) == Run(a); Run(b); Run(c)."""
-    shape, tensors, m, ref = _pair(pkg, orc, synth, "tiny52", STRATS[0])
-    ids = [int(t) for t in synth.token_ids(shape, 7, seed=4)]
-    a = m.run(ids)
-    m.reset_states()
-    for t in ids:
-        b = m.run(t)
-    assert np.array_equal(a, b)
-    m.close()
+    for name in ("tiny4", "tiny52"):
+        shape, tensors, m, ref = _pair(pkg, orc, synth, name, STRATS[0])
+        ids = [int(t) for t in synth.token_ids(shape, 7, seed=4)]
+        a = m.run(ids)
+        m.reset_states()
+        for t in ids:
+            b = m.run(t)
+        if name == "tiny4":
+            assert np.array_equal(a, b)       # RWKV-4 has no seq kernel: Run(vector) is the token loop itself
+        else:
+            _close(a, b, "seq kernels vs token loop")   # RWKV-5.x prompts go through the GEMM path (fp16 operands)
+        m.close()
 
 
 def test_state_save_load_roundtrip(pkg, orc, synth, tmp_path):
