@@ -678,7 +678,7 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
                o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
                o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2), o_lo0 = take(TC * 2), o_lo1 = take(TC * 2);
   // state scan: enough chunks to cover the SMs a few times over, none shorter than 32 tokens
-  int n_chunks = std::max(1, std::min(T / 32, (4 * 148 + H - 1) / H));
+  int n_chunks = std::max(1, std::min(T / 32, (8 * 148 + H - 1) / H));
   const int chunk_len = (T + n_chunks - 1) / n_chunks;
   n_chunks = (T + chunk_len - 1) / chunk_len;
   const size_t o_e = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0), o_sin = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0);

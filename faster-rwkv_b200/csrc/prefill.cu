@@ -365,8 +365,7 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
 
 // RWKV-5 state scan over the tokens of one head (rwkv5_2_kernel_forward, att_seq.cu:258-322; per-head decay for 5.0):
 //   y[t, j] = sum_i r[t,i] * (u_i * k[t,i] * v[t,j] + s[i,j]);   s[i,j] = w_i * s[i,j] + k[t,i] * v[t,j]
-// 256 threads per CTA: thread (j, iq) keeps s[16 iq .. 16 iq + 15][j] in registers; r, k, v of 16 tokens at a time
-// arrive in shared memory by cp.async, the next 16 while the current ones are used.
+// r, k, v of 16 tokens at a time arrive in shared memory by cp.async, the next 16 while the current ones are used.
 // The sequence is cut into n_chunks pieces that run in parallel (the reference walks it serially):
 //   mode 0  state only, from zero, over chunk c               -> E[h][c]        (grid H x n_chunks)
 //   mode 1  S_in[h][0] = state; S_in[h][c+1] = w^len(c) * S_in[h][c] + E[h][c]; state = the last one   (grid H)
@@ -387,18 +386,22 @@ __device__ __forceinline__ void wkv_stage(float (*sr)[64], float (*sk)[64], floa
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// 64 threads per CTA: thread (jg, iq) owns value columns jg, jg + 16, jg + 32, jg + 48 and key rows 16 iq .. 16 iq + 15,
+// i.e. 64 state entries in registers; the r / k values it reads from shared memory serve four columns each.
+constexpr int WKV_THREADS = 64;
 template <int MODE>
-__global__ void __launch_bounds__(256) wkv5_seq_kernel(SeqWkvArgs a) {
+__global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
   __shared__ __align__(16) float sr[2][WKV_TT][64], sk[2][WKV_TT][64], sv[2][WKV_TT][64];
   const int h = blockIdx.x, c = blockIdx.y, C = a.C;
-  const int j = threadIdx.x >> 2, iq = threadIdx.x & 3;
+  const int jg = threadIdx.x >> 2, iq = threadIdx.x & 3;
   const int t_begin = c * a.chunk_len, t_end = min(a.T, t_begin + a.chunk_len);
-  float s[16], w[16], u[16];
+  float s[4][16], w[16], u[16];
   const float *Sin = a.n_chunks == 1 ? a.state + (size_t)h * 4096 : a.s_in + ((size_t)h * a.n_chunks + c) * 4096;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int ii = iq * 16 + i;
-    s[i] = MODE == 0 ? 0.f : Sin[ii * 64 + j];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s[q][i] = MODE == 0 ? 0.f : Sin[ii * 64 + jg + 16 * q];
     w[i] = a.per_head ? a.decay[h] : a.decay[h * 64 + ii];
     u[i] = a.per_head ? a.first[h] : a.first[h * 64 + ii];
   }
@@ -415,56 +418,74 @@ __global__ void __launch_bounds__(256) wkv5_seq_kernel(SeqWkvArgs a) {
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float vj = sv[buf][tt][j];
-      float y0 = 0.f, y1 = 0.f;
+      float vj[4], y[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) vj[q] = sv[buf][tt][jg + 16 * q];
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
         const float4 k4 = *reinterpret_cast<const float4 *>(&sk[buf][tt][iq * 16 + i]);
         float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (MODE == 2) r4 = *reinterpret_cast<const float4 *>(&sr[buf][tt][iq * 16 + i]);
-        float x;
-        x = k4.x * vj; if (MODE == 2) y0 += r4.x * (u[i] * x + s[i]);         s[i] = s[i] * w[i] + x;
-        x = k4.y * vj; if (MODE == 2) y1 += r4.y * (u[i + 1] * x + s[i + 1]); s[i + 1] = s[i + 1] * w[i + 1] + x;
-        x = k4.z * vj; if (MODE == 2) y0 += r4.z * (u[i + 2] * x + s[i + 2]); s[i + 2] = s[i + 2] * w[i + 2] + x;
-        x = k4.w * vj; if (MODE == 2) y1 += r4.w * (u[i + 3] * x + s[i + 3]); s[i + 3] = s[i + 3] * w[i + 3] + x;
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float x = kk[e] * vj[q];
+            if (MODE == 2) y[q] += rr[e] * (u[i + e] * x + s[q][i + e]);
+            s[q][i + e] = s[q][i + e] * w[i + e] + x;
+          }
       }
       if (MODE == 2) {
-        float y = y0 + y1;
-        y += __shfl_xor_sync(0xffffffffu, y, 1);
-        y += __shfl_xor_sync(0xffffffffu, y, 2);
-        if (iq == 0) a.y[(size_t)(t0 + tt) * C + h * 64 + j] = y;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          y[q] += __shfl_xor_sync(0xffffffffu, y[q], 1);
+          y[q] += __shfl_xor_sync(0xffffffffu, y[q], 2);
+        }
+        if (iq == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) a.y[(size_t)(t0 + tt) * C + h * 64 + jg + 16 * q] = y[q];
+        }
       }
     }
     __syncthreads();   // the buffer just read is the one the next staging overwrites
     buf ^= 1;
   }
-  if (MODE == 0) {
-    float *E = a.e_out + ((size_t)h * a.n_chunks + c) * 4096;
+  if (MODE == 0 || a.n_chunks == 1) {
+    float *S = MODE == 0 ? a.e_out + ((size_t)h * a.n_chunks + c) * 4096 : a.state + (size_t)h * 4096;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) E[(iq * 16 + i) * 64 + j] = s[i];
-  } else if (a.n_chunks == 1) {
-    float *S = a.state + (size_t)h * 4096;
+    for (int i = 0; i < 16; ++i)
 #pragma unroll
-    for (int i = 0; i < 16; ++i) S[(iq * 16 + i) * 64 + j] = s[i];
+      for (int q = 0; q < 4; ++q) S[(iq * 16 + i) * 64 + jg + 16 * q] = s[q][i];
   }
 }
 
-// mode 1: chain the chunk states of one head
+// mode 1: chain the chunk states; one thread per state entry (grid = H * 16 CTAs of 256 threads), the chunk end
+// states are fetched eight at a time ahead of the dependent multiply-adds
 __global__ void __launch_bounds__(256) wkv5_combine_kernel(SeqWkvArgs a) {
-  const int h = blockIdx.x;
+  const int h = blockIdx.x >> 4, e = (blockIdx.x & 15) * 256 + threadIdx.x;
+  const int i = e >> 6;
+  const float w = a.per_head ? a.decay[h] : a.decay[h * 64 + i];
+  const float lw = log2f(w);
+  const float wl = exp2f(lw * (float)a.chunk_len);
   float *S = a.state + (size_t)h * 4096;
-  for (int e = threadIdx.x; e < 4096; e += blockDim.x) {
-    const int i = e >> 6;
-    const float w = a.per_head ? a.decay[h] : a.decay[h * 64 + i];
-    const float lw = log2f(w);
-    float s = S[e];
-    for (int c = 0; c < a.n_chunks; ++c) {
-      a.s_in[((size_t)h * a.n_chunks + c) * 4096 + e] = s;
-      const int len = min(a.T, (c + 1) * a.chunk_len) - c * a.chunk_len;
-      s = exp2f(lw * (float)len) * s + a.e_out[((size_t)h * a.n_chunks + c) * 4096 + e];
+  float s = S[e];
+  const size_t base = (size_t)h * a.n_chunks * 4096 + e;
+  for (int c0 = 0; c0 < a.n_chunks; c0 += 8) {
+    float ev[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) ev[q] = c0 + q < a.n_chunks ? a.e_out[base + (size_t)(c0 + q) * 4096] : 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int c = c0 + q;
+      if (c < a.n_chunks) {
+        a.s_in[base + (size_t)c * 4096] = s;
+        const int len = min(a.T, (c + 1) * a.chunk_len) - c * a.chunk_len;
+        s = (len == a.chunk_len ? wl : exp2f(lw * (float)len)) * s + ev[q];
+      }
     }
-    S[e] = s;
   }
+  S[e] = s;
 }
 
 // GroupNorm over each head's 64 readout values (eps 1e-5, fp32 affine), times the gate where the version has one
@@ -513,12 +534,12 @@ cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
 }
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
   if (a.n_chunks <= 1) {
-    wkv5_seq_kernel<2><<<dim3(H, 1), 256, 0, st>>>(a);
+    wkv5_seq_kernel<2><<<dim3(H, 1), WKV_THREADS, 0, st>>>(a);
     return cudaGetLastError();
   }
-  wkv5_seq_kernel<0><<<dim3(H, a.n_chunks), 256, 0, st>>>(a);
-  wkv5_combine_kernel<<<H, 256, 0, st>>>(a);
-  wkv5_seq_kernel<2><<<dim3(H, a.n_chunks), 256, 0, st>>>(a);
+  wkv5_seq_kernel<0><<<dim3(H, a.n_chunks), WKV_THREADS, 0, st>>>(a);
+  wkv5_combine_kernel<<<H * 16, 256, 0, st>>>(a);
+  wkv5_seq_kernel<2><<<dim3(H, a.n_chunks), WKV_THREADS, 0, st>>>(a);
   return cudaGetLastError();
 }
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
