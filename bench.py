@@ -137,6 +137,55 @@ def build_model(pkg, shape, fmt: str, max_batch: int, device_index: int, seed: i
     return m
 
 
+# ------------------------------------------------------------------ seq mode (prompt processing)
+
+def measured_peak_tflops():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+def prefill_leg(pkg, device_index: int, wl: str = "c3", T: int = 4096, reps: int = 3):
+    """One 4096-token prompt through the seq path of an RWKV-5.2 3B-shaped model (L32 C2560 F8960 H40), fp16 weights:
+    Model.run(ids) with host ids in and host logits out.  FLOPs = 2 * (projection params) * T + the head once."""
+    import torch
+    try:
+        shape = pkg.synth.SHAPES[wl]
+        m = build_model(pkg, shape, "fp16", 1, device_index, seed=0)
+        ids = [int(t) for t in pkg.synth.token_ids(shape, T, seed=1)]
+        C, F, V, L = shape.n_embd, shape.n_ffn, shape.vocab, shape.n_layer
+        P = L * (6 * C * C + 2 * C * F)
+        flops = 2.0 * P * T + 2.0 * C * V
+        m.run(ids)                                   # warm-up (allocates the activation buffers)
+        best = None
+        for _ in range(reps):
+            m.reset_states()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            m.run(ids)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        burst, sustained, kind = measured_peak_tflops()
+        tf = flops / (best * 1e-3) / 1e12
+        out = {"workload": "c3: RWKV-5.2 3B-shaped (L32 C2560 F8960 H40 V65536), one 4096-token prompt, fp16 weights",
+               "ms": best, "tok_s": T / (best * 1e-3), "tflops": tf, "tensor_frac_of_burst_peak": tf / burst,
+               "tensor_frac_of_sustained_peak": tf / sustained, "peak_source": kind,
+               "algorithmic_flops": flops}
+        m.close()
+        del m
+        torch.cuda.empty_cache()
+        return out
+    except Exception as ex:
+        return {"error": str(ex)[:200]}
+
+
 # ------------------------------------------------------------------ clocks
 
 class ClockSampler:
@@ -345,7 +394,9 @@ def main():
             ok = True
             for r in range(1, world):
                 model.reset_states()
-                again = model.decode_greedy(pkg.synth.token_ids(shape, B, seed=r), min(K, 16))
+                first_r = pkg.synth.token_ids(shape, B, seed=r)
+                model.decode_greedy(first_r, W)          # the timed run followed W warm-up tokens from the same start
+                again = model.decode_greedy(first_r, min(K, 16))
                 ok = ok and np.array_equal(again, allv[r].cpu().numpy())
             check = "sampled ids of every rank reproduced on rank 0" if ok else "MISMATCH"
 
@@ -377,6 +428,8 @@ def main():
                 torch.cuda.empty_cache()
             except Exception as ex:  # a variant must not lose the headline
                 variants[f"{fmt}_b{vb}"] = {"error": str(ex)[:200]}
+
+        variants["prefill_c3_T4096"] = prefill_leg(pkg, local_rank)
 
     cb = None
     if host_master is not None:

@@ -213,7 +213,7 @@ Tensor model_forward(Model *model, Device device, int id) {
 }
 
 // replaces def::ModelForwardSeq (kernels/default/model_forward_seq.cpp:48-184).  RWKV-4 has no seq kernel
-// upstream (it throws, :111-112); here every version runs the token loop of :34-46.
+// upstream (it throws, :111-112); here it runs the token loop of :34-46, RWKV-5.x prompts the seq kernels.
 Tensor model_forward_seq(Model *model, Device device, const std::vector<int> &ids, bool full_output) {
   RV_CHECK(!ids.empty());
   auto ex = get_extra(model);
@@ -221,10 +221,15 @@ Tensor model_forward_seq(Model *model, Device device, const std::vector<int> &id
   const LengthType V = ex->vocab, T = (LengthType)ids.size();
   Tensor out = full_output ? Tensor::Empty({T, V}, DType::kFloat32, Device::kCPU)
                            : Tensor::Empty({V}, DType::kFloat32, Device::kCPU);
-  for (LengthType t = 0; t < T; ++t) {
-    const int32_t tid = ids[t];
-    float *dst = full_output ? out.data_ptr<float>() + t * V : (t == T - 1 ? out.data_ptr<float>() : nullptr);
-    FRB_CALL(fr_b200_decode(ex->h, &tid, 1, dst, nullptr, nullptr));
+  if (!full_output) {
+    // the whole prompt at once: RWKV-5.x with fp16 weights runs the seq kernels, everything else the token loop
+    std::vector<int32_t> tids(ids.begin(), ids.end());
+    FRB_CALL(fr_b200_run_seq(ex->h, 0, tids.data(), (int)T, out.data_ptr<float>(), nullptr));
+  } else {
+    for (LengthType t = 0; t < T; ++t) {
+      const int32_t tid = ids[t];
+      FRB_CALL(fr_b200_decode(ex->h, &tid, 1, out.data_ptr<float>() + t * V, nullptr, nullptr));
+    }
   }
   publish_states(model, *ex);
   return out;

@@ -699,15 +699,15 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
   CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
   auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
   auto wt = [&](const std::string &n) -> const __half * { return m->d_plain + m->mats[n].plain_off; };
-  auto gemm = [&](const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
-                  float scale, const __half *A2 = nullptr) -> cudaError_t {
+  auto mk = [&](const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
+                float scale, const __half *A2 = nullptr) -> GemmArgs {
     GemmArgs ga;
     memset(&ga, 0, sizeof(ga));
     ga.A = A; ga.A2 = A2; ga.Bt = wt(w); ga.M = T; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
     ga.scale = scale; ga.status = m->out_status();
-    m->launches++;
-    return launch_gemm_f16(ga, st);
+    return ga;
   };
+  const int mt = T > 128 ? 2 : 1;   // 256-row tiles once the prompt fills them
   const int par = (int)m->par[slot];
   const int nvec = m->gate ? 4 : 3;
   for (int l = 0; l < m->L; ++l) {
@@ -726,10 +726,15 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     // activations as hi + lo fp16 pairs (a second pass over K), like every decode matvec does
     la.op_lo[0] = lo0; la.op_lo[1] = lo1;
     CU(launch_ln_mix_seq(la, st));
-    CU(gemm(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0));
-    CU(gemm(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f, lo1));
-    CU(gemm(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f));
-    if (m->gate) CU(gemm(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f));
+    {
+      // the attention projections in one launch; the two with a second pass over K first
+      GemmArgs grp[4] = {mk(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0),
+                         mk(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f, lo1),
+                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f),
+                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f)};
+      if (m->gate) grp[3] = mk(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f);
+      CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st));
+    }
     SeqWkvArgs wa;
     memset(&wa, 0, sizeof(wa));
     wa.r = r; wa.k = k; wa.v = v; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
@@ -738,7 +743,10 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e); wa.s_in = (float *)(B + o_sin);
     CU(launch_wkv5_seq(wa, H, st));
     CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
-    CU(gemm(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f));
+    {
+      const GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f);
+      CU(launch_gemm_group(&go, 1, 1, st));
+    }
     // ---- channel mix ----
     memset(&la, 0, sizeof(la));
     la.x = x; la.ln_w = vp(b + "ln2.weight"); la.ln_b = vp(b + "ln2.bias");
@@ -747,11 +755,15 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     la.sx_rd = stb + off_ffn_sx(C, H, 1, af, par); la.sx_wr = stb + off_ffn_sx(C, H, 1, af, par ^ 1);
     la.T = T; la.C = C; la.nvec = 2; la.act_fp16 = af;
     CU(launch_ln_mix_seq(la, st));
-    CU(gemm(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f));
-    CU(gemm(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f));
     const bool halve = af && (l + 1) % 6 == 0;   // x / 2 every 6 layers under fp16 activations (model_forward_seq.cpp:165-167)
-    CU(gemm(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f));
-    m->launches += 5;
+    {
+      const GemmArgs grp[2] = {mk(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f),
+                               mk(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f)};
+      CU(launch_gemm_group(grp, 2, mt, st));
+      const GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f);
+      CU(launch_gemm_group(&gv, 1, 1, st));
+    }
+    m->launches += 9;
   }
   // last token -> ln_out -> head, as a stand-alone matvec over the head's streaming tiles
   CU(launch_ln_row(x + (size_t)(T - 1) * C, vp("ln_out.weight"), vp("ln_out.bias"), C, m->d_lnvec, st));

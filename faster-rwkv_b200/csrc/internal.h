@@ -125,7 +125,10 @@ struct GemmArgs {
   float scale;
   int *status;         // device word: set when a bounded wait gives up
 };
-cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);
+constexpr int GEMM_GROUP_MAX = 4;
+cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);   // one GEMM; 256-row tiles when M > 128
+// n <= 4 GEMMs with equal M in one launch; mt = 128-row sub-tiles per CTA (1 or 2)
+cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st);
 // row kernels of seq mode
 struct SeqLnArgs {
   const float *x;            // [T, C] residual stream

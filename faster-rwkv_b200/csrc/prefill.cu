@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstring>
 
 #include "common.cuh"
 #include "internal.h"
@@ -24,10 +25,9 @@ namespace {
 // One CTA per 128 x 256 output tile; K is walked in 64-wide slices through a 4-deep TMA ring.
 //   warp 0 (one lane): TMA producer          warp 1 (one lane): MMA issue; the warp owns the TMEM allocation
 //   warps 2..5: epilogue, one TMEM lane quadrant (32 rows) each
-constexpr int GBM = 128, GBN = 256, GBK = 64, GSTAGES = 4;
+constexpr int GBM = 128, GBN = 256, GBK = 64;
 constexpr int G_THREADS = 192;
-constexpr uint32_t G_A_BYTES = GBM * GBK * 2, G_B_BYTES = GBN * GBK * 2, G_STAGE_BYTES = G_A_BYTES + G_B_BYTES;
-constexpr size_t G_SMEM = 1024 /* barriers */ + (size_t)GSTAGES * G_STAGE_BYTES + 1024 /* alignment slack */;
+constexpr uint32_t G_A_BYTES = GBM * GBK * 2, G_B_BYTES = GBN * GBK * 2;
 constexpr int ST_GEMM_TIMEOUT = 201;
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -148,31 +148,50 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
   }
 }
 
+// Up to four GEMMs with the same M in one launch (grid.x walks their N tiles back to back, heaviest first): the
+// attention projections of a layer, or the two channel-mix projections that read the LayerNorm output.
+struct GemmGroup {
+  int n;
+  int tile_start[GEMM_GROUP_MAX + 1];   // first grid.x index of each problem
+  GemmArgs p[GEMM_GROUP_MAX];
+};
+struct alignas(64) GemmMaps {
+  CUtensorMap a[GEMM_GROUP_MAX], a2[GEMM_GROUP_MAX], b[GEMM_GROUP_MAX];
+};
+
+// MT = 128-row sub-tiles per CTA (1: 128 x 256 output tile, 4-deep ring; 2: 256 x 256, two accumulators sharing
+// every B tile, 3-deep ring -- half again as many flops per byte fetched from L2)
+template <int MT>
 __global__ void __launch_bounds__(G_THREADS, 1)
-gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_a2,
-                const __grid_constant__ CUtensorMap tma_b, const GemmArgs g) {
+gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
+  constexpr int STAGES = MT == 1 ? 4 : 3;
+  constexpr uint32_t STAGE_BYTES = MT * G_A_BYTES + G_B_BYTES;
+  constexpr uint32_t TMEM_COLS = MT * GBN;
   extern __shared__ uint8_t gsm_raw[];
   // barriers in the first KB, tiles from the next 1024-byte boundary
   uint8_t *gsm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *full = reinterpret_cast<uint64_t *>(gsm);
-  uint64_t *empty = full + GSTAGES;
-  uint64_t *acc_full = empty + GSTAGES;
+  uint64_t *empty = full + 4;
+  uint64_t *acc_full = empty + 4;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t tiles = smem_u32(gsm + 1024);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_m = blockIdx.y, tile_n = blockIdx.x;
+  int pi = 0;
+  while (pi + 1 < grp.n && (int)blockIdx.x >= grp.tile_start[pi + 1]) ++pi;
+  const GemmArgs &g = grp.p[pi];
+  const int tile_m = blockIdx.y, tile_n = blockIdx.x - grp.tile_start[pi];
   const int num_k1 = g.K / GBK;
   const int num_k = g.A2 ? 2 * num_k1 : num_k1;   // a second pass over K with the low halves of A, same accumulator
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < GSTAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)GBN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -183,44 +202,54 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % GSTAGES;
-        const uint32_t parity = ((kb / GSTAGES) & 1) ^ 1;   // a fresh barrier reads as "previous phase complete"
+        const int s = kb % STAGES;
+        const uint32_t parity = ((kb / STAGES) & 1) ^ 1;   // a fresh barrier reads as "previous phase complete"
         if (!mbar_wait(&empty[s], parity, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
-        mbar_expect_tx(&full[s], G_STAGE_BYTES);
-        const uint32_t a_dst = tiles + (uint32_t)s * G_STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        const uint32_t a_dst = tiles + (uint32_t)s * STAGE_BYTES;
         const int kk = kb < num_k1 ? kb : kb - num_k1;
-        tma_load_2d(a_dst, kb < num_k1 ? &tma_a : &tma_a2, kk * GBK, tile_m * GBM, &full[s]);
-        tma_load_2d(a_dst + G_A_BYTES, &tma_b, kk * GBK, tile_n * GBN, &full[s]);
+        const CUtensorMap *ma = kb < num_k1 ? &maps.a[pi] : &maps.a2[pi];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(a_dst + (uint32_t)mt * G_A_BYTES, ma, kk * GBK, (tile_m * MT + mt) * GBM, &full[s]);
+        tma_load_2d(a_dst + MT * G_A_BYTES, &maps.b[pi], kk * GBK, tile_n * GBN, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool live = true;
-      for (int kb = 0; kb < num_k && live; ++kb) {
-        const int s = kb % GSTAGES;
-        if (!mbar_wait(&full[s], (kb / GSTAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) { live = false; break; }
+      for (int kb = 0; kb < num_k; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
         tc_fence_after();
-        const uint32_t a_addr = tiles + (uint32_t)s * G_STAGE_BYTES;
-        const uint64_t ad = umma_desc_k128(a_addr), bd = umma_desc_k128(a_addr + G_A_BYTES);
+        const uint32_t a_addr = tiles + (uint32_t)s * STAGE_BYTES;
+        const uint64_t bd = umma_desc_k128(a_addr + MT * G_A_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < GBK / 16; ++k4)   // 16 inputs = 32 bytes further along the swizzled rows
-          umma_f16(tmem_base, ad + (uint64_t)(k4 * 2), bd + (uint64_t)(k4 * 2), G_IDESC, (kb | k4) != 0);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint64_t ad = umma_desc_k128(a_addr + (uint32_t)mt * G_A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < GBK / 16; ++k4)   // 16 inputs = 32 bytes further along the swizzled rows
+            umma_f16(tmem_base + (uint32_t)mt * GBN, ad + (uint64_t)(k4 * 2), bd + (uint64_t)(k4 * 2), G_IDESC, (kb | k4) != 0);
+        }
         umma_commit(&empty[s]);   // the slot is free once these MMAs have read it
       }
-      umma_commit(acc_full);      // the accumulator is complete once every MMA has retired
+      umma_commit(acc_full);      // the accumulators are complete once every MMA has retired
     }
   } else {
     // epilogue warps 2..5 -> TMEM lane quadrants 2, 3, 0, 1
     const int quad = warp & 3;
     const bool ok = mbar_wait(acc_full, 0, abort_flag, g.status, ST_GEMM_TIMEOUT);
     tc_fence_after();
-    const int row = tile_m * GBM + quad * 32 + lane;
     if (ok) {
-      for (int c0 = 0; c0 < GBN; c0 += 32) {
-        if (tile_n * GBN + c0 >= g.N) break;   // warp-uniform
-        uint32_t acc[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
-        if (row < g.M) gemm_epilogue_row(g, row, tile_n * GBN + c0, acc);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = (tile_m * MT + mt) * GBM + quad * 32 + lane;
+        if ((tile_m * MT + mt) * GBM >= g.M) break;   // warp-uniform
+        for (int c0 = 0; c0 < GBN; c0 += 32) {
+          if (tile_n * GBN + c0 >= g.N) break;   // warp-uniform
+          uint32_t acc[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * GBN + c0), acc);
+          if (row < g.M) gemm_epilogue_row(g, row, tile_n * GBN + c0, acc);
+        }
       }
     }
   }
@@ -228,7 +257,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)GBN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -552,17 +581,43 @@ cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C,
   return cudaGetLastError();
 }
 
-cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st) {
-  if (g.K % GBK != 0 || g.M < 1 || g.N < 1) return cudaErrorInvalidValue;
-  if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Bt) & 15)) return cudaErrorInvalidValue;
-  CUtensorMap ma, ma2, mb;
-  if (!make_map(&ma, g.A, g.M, g.K, GBM) || !make_map(&mb, g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
-  if (!make_map(&ma2, g.A2 ? g.A2 : g.A, g.M, g.K, GBM)) return cudaErrorNotSupported;
-  cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G_SMEM);
-  if (e != cudaSuccess) return e;
-  dim3 grid((g.N + GBN - 1) / GBN, (g.M + GBM - 1) / GBM);
-  gemm_f16_kernel<<<grid, G_THREADS, G_SMEM, st>>>(ma, ma2, mb, g);
+cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st) {
+  if (n < 1 || n > GEMM_GROUP_MAX || (mt != 1 && mt != 2)) return cudaErrorInvalidValue;
+  GemmMaps maps;
+  GemmGroup grp;
+  memset(&grp, 0, sizeof(grp));
+  grp.n = n;
+  int tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    const GemmArgs &g = probs[i];
+    if (g.K % GBK != 0 || g.M < 1 || g.N < 1 || g.M != probs[0].M) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Bt) & 15) || (reinterpret_cast<uintptr_t>(g.A2) & 15))
+      return cudaErrorInvalidValue;
+    if (!make_map(&maps.a[i], g.A, g.M, g.K, GBM) || !make_map(&maps.b[i], g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
+    if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, GBM)) return cudaErrorNotSupported;
+    grp.p[i] = g;
+    grp.tile_start[i] = tiles;
+    tiles += (g.N + GBN - 1) / GBN;
+  }
+  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; }
+  grp.tile_start[n] = tiles;
+  const size_t smem = 1024 + (mt == 1 ? 4 * (size_t)(G_A_BYTES + G_B_BYTES) : 3 * (size_t)(2 * G_A_BYTES + G_B_BYTES)) + 1024;
+  dim3 grid(tiles, (probs[0].M + mt * GBM - 1) / (mt * GBM));
+  cudaError_t e;
+  if (mt == 1) {
+    e = cudaFuncSetAttribute(gemm_f16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    gemm_f16_kernel<1><<<grid, G_THREADS, smem, st>>>(maps, grp);
+  } else {
+    e = cudaFuncSetAttribute(gemm_f16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    gemm_f16_kernel<2><<<grid, G_THREADS, smem, st>>>(maps, grp);
+  }
   return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st) {
+  return launch_gemm_group(&g, 1, g.M > GBM ? 2 : 1, st);
 }
 
 }  // namespace frb
