@@ -300,6 +300,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-tokens", type=int, default=24)
     ap.add_argument("--no-variants", action="store_true")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="run only the seq-mode leg (c3, one 4096-token prompt) and print its JSON; for profiling")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ref-gpu", action="store_true")
     args = ap.parse_args()
@@ -327,6 +329,11 @@ def main():
                 "data": "synthetic", "config": config, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
+        return
+
+    if args.prefill_only:
+        if rank == 0:
+            print(json.dumps({"metric": "prefill_tokens_per_s", "n_gpus": 1, "data": "synthetic", **prefill_leg(pkg, local_rank)}))
         return
 
     import torch

@@ -745,7 +745,7 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
     {
       const GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f);
-      CU(launch_gemm_group(&go, 1, 1, st));
+      CU(launch_gemm_group(&go, 1, 1, st));   // few tiles: 128-row tiles fill the SMs better (measured)
     }
     // ---- channel mix ----
     memset(&la, 0, sizeof(la));
