@@ -63,7 +63,7 @@ struct fr_b200_model {
   exch_t *d_v5buf = nullptr;     // k5, v5, r5, g5, o5
   int exch_batch = 0;            // streams the last launch wrote into the exchange vectors (0: clear them first)
   unsigned seq = 0;              // phases launched so far (tags continue across launches)
-  unsigned par[MAX_B] = {0, 0, 0, 0, 0, 0, 0, 0};   // which copy of the token-shift states each slot reads next
+  std::vector<unsigned> par;     // per stream slot: which copy of the token-shift states it reads next
   float *d_out = nullptr;        // [B][Vpad] logits, then [B] argmax ints, then status int
   LayerDev *d_layers = nullptr;
   PhaseDev *d_phases = nullptr;
@@ -193,9 +193,12 @@ void plan(fr_b200_model *m) {
   woff += (size_t)nbV * rbC; roff += (size_t)nbV * ROWS;
   m->weights_bytes = woff; m->rscale_n = roff; m->vecs_n = voff;
   m->plain_halfs = 0;
-  if (m->v5 && fmt == FMT_FP16)
+  // the GEMM path needs every projection again as W^T fp16 (dequantised for int8 / int4): seq mode of RWKV-5.x fp16
+  // models, and decode of more than 8 streams at once for every model (then the head too: all rows want logits)
+  const bool big = m->cfg.max_batch > MAX_B;
+  if ((m->v5 && fmt == FMT_FP16) || big)
     for (auto &kv : m->mats) {
-      if (kv.first == "head.weight") continue;   // the head stays a matvec over the last token
+      if (kv.first == "head.weight" && !big) continue;   // seq mode: the head is a matvec over the last token
       kv.second.has_plain = true;
       kv.second.plain_off = m->plain_halfs;
       m->plain_halfs += ((size_t)kv.second.K * kv.second.N + 127) / 128 * 128;
@@ -238,12 +241,28 @@ int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int d
       CU(launch_quant_int8(w32, s.K, s.N, reinterpret_cast<int8_t *>(m->d_scratch[2]), reinterpret_cast<__half *>(m->d_scratch[3]), 0));
       CU(launch_pack(FMT_INT8, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
                      s.item_stride, m->d_rscale + s.rscale_off, s.rscale_stride, 0));
+      if (s.has_plain && m->d_plain) {
+        if ((rc = ensure_scratch(m, 0, n * 4))) return rc;   // the input is packed: its buffer takes the dequantised matrix
+        if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
+        CU(launch_dequant_int8(reinterpret_cast<const int8_t *>(m->d_scratch[2]), reinterpret_cast<const __half *>(m->d_scratch[3]),
+                               s.K, s.N, reinterpret_cast<float *>(m->d_scratch[0]), 0));
+        CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]), n, 0));
+        CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[1]), s.K, s.N, m->d_plain + s.plain_off, 0));
+      }
     } else {
       if ((rc = ensure_scratch(m, 2, n / 2))) return rc;
       if ((rc = ensure_scratch(m, 3, (size_t)s.N * (s.K / 32) * 2))) return rc;
       CU(launch_quant_int4(w32, s.K, s.N, reinterpret_cast<uint8_t *>(m->d_scratch[2]), reinterpret_cast<__half *>(m->d_scratch[3]), 0));
       CU(launch_pack(FMT_INT4, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
                      s.item_stride, nullptr, 0, 0));
+      if (s.has_plain && m->d_plain) {
+        if ((rc = ensure_scratch(m, 0, n * 4))) return rc;
+        if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
+        CU(launch_dequant_int4(reinterpret_cast<const uint8_t *>(m->d_scratch[2]), reinterpret_cast<const __half *>(m->d_scratch[3]),
+                               s.K, s.N, reinterpret_cast<float *>(m->d_scratch[0]), 0));
+        CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]), n, 0));
+        CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[1]), s.K, s.N, m->d_plain + s.plain_off, 0));
+      }
     }
   }
   CU(cudaDeviceSynchronize());
@@ -308,7 +327,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (cfg->n_embd <= 0 || cfg->n_embd % 64 || cfg->n_ffn <= 0 || cfg->n_ffn % 64)
     return fail(FR_B200_E_UNSUPPORTED, "n_embd and n_ffn must be positive multiples of 64");
   if (cfg->weight_format < 0 || cfg->weight_format > 2) return fail(FR_B200_E_ARG, "bad weight_format");
-  if (cfg->max_batch < 1 || cfg->max_batch > MAX_B) return fail(FR_B200_E_UNSUPPORTED, "max_batch must be 1..8");
+  if (cfg->max_batch < 1 || cfg->max_batch > 4096) return fail(FR_B200_E_UNSUPPORTED, "max_batch must be 1..4096");
   if (v != FR_B200_V4 && (cfg->n_head <= 0 || cfg->n_embd != cfg->n_head * 64))
     return fail(FR_B200_E_UNSUPPORTED, "RWKV-5 needs n_embd == 64 * n_head");
   int ndev = 0;
@@ -328,6 +347,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   m->v5 = v != FR_B200_V4;
   m->gate = v == FR_B200_V5_1 || v == FR_B200_V5_2;
   m->device = cfg->device;
+  m->par.assign(cfg->max_batch, 0u);
   if ((m->C + prop.multiProcessorCount - 1) / prop.multiProcessorCount > 128) {
     delete m;
     return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the shift-state stash");
@@ -477,14 +497,16 @@ int fr_b200_finalize(fr_b200_model *m) {
   if (want < 2) want = 2;
   if (want > MAX_STAGES) want = MAX_STAGES;
   const int ver = m->v5 ? 5 : 4;
-  const int max_mode = decode_mode(m->cfg.max_batch);
+  const int max_mode = decode_mode(std::min(m->cfg.max_batch, MAX_B));
   for (int mode = 0; mode <= max_mode; ++mode) {
     int st = 0;
     for (int s = want; s >= 2; --s)
       if (decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, s) <= (size_t)optin) { st = s; break; }
-    if (st == 0)
+    if (st == 0) {
+      if (m->cfg.max_batch > MAX_B && mode > 0) { m->n_stages[mode] = 0; continue; }   // such batches take the GEMM path
       return fail(FR_B200_E_UNSUPPORTED, "model too wide for shared memory at this batch size (max_batch " +
                                              std::to_string(m->cfg.max_batch) + ")");
+    }
     m->n_stages[mode] = st;
     m->smem[mode] = decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, st);
     int g = 0;
@@ -512,6 +534,20 @@ int fr_b200_finalize(fr_b200_model *m) {
   m->finalized = true;
   return fr_b200_state_reset(m, -1);
 }
+
+namespace {
+int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids, int R, cudaStream_t st);
+// more streams than the persistent kernel carries (or a model too wide for that many): the GEMM path decodes them
+bool decode_by_rows(const fr_b200_model *m, int batch) { return batch > MAX_B || m->n_stages[decode_mode(batch)] == 0; }
+int rows_decode_check(fr_b200_model *m, const int32_t *ids_host, int batch) {
+  if (!m->d_plain) return fail(FR_B200_E_UNSUPPORTED, "this batch size needs a model created with max_batch > 8");
+  for (int b = 0; b < batch; ++b) {
+    if (ids_host && (ids_host[b] < 0 || ids_host[b] >= m->V)) return fail(FR_B200_E_ARG, "token id out of range");
+    if (m->par[b] != m->par[0]) return fail(FR_B200_E_STATE, "streams decoded together must have seen the same number of tokens since their last reset");
+  }
+  return 0;
+}
+}  // namespace
 
 static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned long long *ids_packed, int batch,
                        cudaStream_t st, unsigned long long *amax, unsigned long long *prof = nullptr) {
@@ -573,12 +609,22 @@ int fr_b200_decode(fr_b200_model *m, const int32_t *ids, int batch, float *logit
   if (batch < 1 || batch > m->cfg.max_batch) return fail(FR_B200_E_ARG, "batch must be 1..max_batch");
   CU(cudaSetDevice(m->device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (argmax) CU(cudaMemsetAsync(m->d_amax, 0, (size_t)batch * 8, st));
-  int rc = decode_impl(m, ids, nullptr, batch, st, argmax ? m->d_amax : nullptr);
-  if (rc) return rc;
-  if (argmax) {
-    CU(launch_unpack_ids(m->d_amax, batch, m->out_argmax(), st));
-    m->launches++;
+  int rc;
+  if (decode_by_rows(m, batch)) {
+    if ((rc = rows_decode_check(m, ids, batch))) return rc;
+    if ((rc = rows_forward(m, true, 0, ids, batch, st))) return rc;
+    if (argmax) {
+      CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), st));
+      m->launches++;
+    }
+  } else {
+    if (argmax) CU(cudaMemsetAsync(m->d_amax, 0, (size_t)batch * 8, st));
+    rc = decode_impl(m, ids, nullptr, batch, st, argmax ? m->d_amax : nullptr);
+    if (rc) return rc;
+    if (argmax) {
+      CU(launch_unpack_ids(m->d_amax, batch, m->out_argmax(), st));
+      m->launches++;
+    }
   }
   const bool lh = logits && is_host_ptr(logits), ah = argmax && is_host_ptr(argmax);
   if (logits && !lh)
@@ -616,6 +662,25 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
     CU(cudaMalloc((void **)&m->d_hist, need * 12));
     m->hist_n = need;
   }
+  if (decode_by_rows(m, batch)) {
+    // GEMM path: ids stay on the device, row t of the history feeds step t + 1
+    int rc = rows_decode_check(m, first_ids, batch);
+    if (rc) return rc;
+    int32_t *hist32 = reinterpret_cast<int32_t *>(m->d_hist + need);
+    for (int t = 0; t < n_tokens; ++t) {
+      if ((rc = rows_forward(m, true, 0, t == 0 ? first_ids : hist32 + (size_t)(t - 1) * batch, batch, st))) return rc;
+      CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, hist32 + (size_t)t * batch, st));
+      m->launches++;
+    }
+    CU(cudaMemcpyAsync(out_ids, hist32, need * 4, cudaMemcpyDefault, st));
+    if (is_host_ptr(out_ids)) {
+      int status = 0;
+      CU(cudaMemcpyAsync(&status, m->out_status(), 4, cudaMemcpyDeviceToHost, st));
+      CU(cudaStreamSynchronize(st));
+      return check_status(m, status);
+    }
+    return FR_B200_OK;
+  }
   // one packed arg-max word per (token, stream), all cleared up front; token t+1 reads its ids from row t
   CU(cudaMemsetAsync(m->d_hist, 0, need * 8, st));
   for (int t = 0; t < n_tokens; ++t) {
@@ -641,6 +706,7 @@ int fr_b200_decode_profile(fr_b200_model *m, const int32_t *ids, int batch, uint
   if (!m || !ids || !stamps) return fail(FR_B200_E_ARG, "null argument");
   if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
   if (batch < 1 || batch > m->cfg.max_batch) return fail(FR_B200_E_ARG, "batch must be 1..max_batch");
+  if (decode_by_rows(m, batch)) return fail(FR_B200_E_UNSUPPORTED, "the trace exists for the persistent kernel (at most 8 streams) only");
   const int need = (int)m->phases.size() * 8 * m->grid;
   if (n_stamps < need) return fail(FR_B200_E_ARG, "stamps must hold 8 * n_phases * n_ctas entries");
   CU(cudaSetDevice(m->device));
@@ -665,11 +731,14 @@ int fr_b200_vocab_padded(const fr_b200_model *m) { return m ? m->Vpad : FR_B200_
 
 namespace {
 
-// Seq mode for RWKV-5.x with fp16 weights: the whole prompt of one stream through [T, K] x [K, N] GEMMs
-// (def::ModelForwardSeq, kernels/default/model_forward_seq.cpp:48-184).  The residual stream stays fp32 between
-// the layers; GEMM inputs are fp16, as in decode.
-int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStream_t st) {
-  const int C = m->C, F = m->F, H = m->H, af = m->cfg.act_fp16;
+// The forward pass over R rows through [R, K] x [K, N] tensor-core GEMMs and row kernels.
+//   seq mode   (batch_mode = false): the rows are the tokens of one prompt of stream `slot`
+//              (def::ModelForwardSeq, kernels/default/model_forward_seq.cpp:48-184); logits of the last row only.
+//   batch mode (batch_mode = true):  row b is the next token of stream b, b < R (the batched decode the reference
+//              lacks); logits of every row into d_out.
+// ids: host or device.  The residual stream stays fp32 between the layers; GEMM inputs are fp16.
+int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids, int R, cudaStream_t st) {
+  const int C = m->C, F = m->F, H = m->H, af = m->cfg.act_fp16, T = R;
   const size_t TC = (size_t)T * C, TF = (size_t)T * F;
   // activation buffers: one blob, 256-byte aligned pieces
   size_t off = 0;
@@ -677,10 +746,13 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
   const size_t o_ids = take((size_t)T * 4), o_x = take(TC * 4), o_r = take(TC * 4), o_k = take(TC * 4), o_v = take(TC * 4),
                o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
                o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2), o_lo0 = take(TC * 2), o_lo1 = take(TC * 2);
-  // state scan: enough chunks to cover the SMs a few times over, none shorter than 32 tokens
-  int n_chunks = std::max(1, std::min(T / 32, (8 * 148 + H - 1) / H));
-  const int chunk_len = (T + n_chunks - 1) / n_chunks;
-  n_chunks = (T + chunk_len - 1) / chunk_len;
+  // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
+  int n_chunks = 1, chunk_len = T;
+  if (!batch_mode && m->v5) {
+    n_chunks = std::max(1, std::min(T / 32, (8 * 148 + H - 1) / H));
+    chunk_len = (T + n_chunks - 1) / n_chunks;
+    n_chunks = (T + chunk_len - 1) / chunk_len;
+  }
   const size_t o_e = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0), o_sin = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0);
   if (m->seq_bytes < off) {
     CU(cudaStreamSynchronize(st));
@@ -707,12 +779,13 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     ga.scale = scale; ga.status = m->out_status();
     return ga;
   };
-  const int mt = T > 128 ? 2 : 1;   // 256-row tiles once the prompt fills them
-  const int par = (int)m->par[slot];
-  const int nvec = m->gate ? 4 : 3;
+  const int mt = T > 128 ? 2 : 1;   // 256-row tiles once the rows fill them
+  const int par = (int)m->par[batch_mode ? 0 : slot];
+  const int nvec = m->v5 ? (m->gate ? 4 : 3) : 3;
+  uint8_t *st0 = m->d_state + (batch_mode ? 0 : (size_t)slot * m->state_stride);
   for (int l = 0; l < m->L; ++l) {
     const std::string b = "blocks." + std::to_string(l) + ".", a = b + "att.", f = b + "ffn.";
-    uint8_t *stb = m->d_state + (size_t)slot * m->state_stride + (size_t)l * m->layer_stride;
+    uint8_t *stb = st0 + (size_t)l * m->layer_stride;
     // ---- time mix ----
     SeqLnArgs la;
     memset(&la, 0, sizeof(la));
@@ -722,6 +795,7 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     for (int i = 0; i < 4; ++i) la.op[i] = op[i];
     la.sx_rd = stb + off_sx(C, af, par); la.sx_wr = stb + off_sx(C, af, par ^ 1);
     la.T = T; la.C = C; la.nvec = nvec; la.act_fp16 = af;
+    la.batch_mode = batch_mode; la.state_stride = m->state_stride;
     // k and v build the recurrent state, which keeps growing with the prompt: their projections take the
     // activations as hi + lo fp16 pairs (a second pass over K), like every decode matvec does
     la.op_lo[0] = lo0; la.op_lo[1] = lo1;
@@ -735,14 +809,23 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
       if (m->gate) grp[3] = mk(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f);
       CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st));
     }
-    SeqWkvArgs wa;
-    memset(&wa, 0, sizeof(wa));
-    wa.r = r; wa.k = k; wa.v = v; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
-    wa.state = reinterpret_cast<float *>(stb + off_mid(C, af)); wa.y = y; wa.T = T; wa.C = C;
-    wa.per_head = m->cfg.version == FR_B200_V5_0;
-    wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e); wa.s_in = (float *)(B + o_sin);
-    CU(launch_wkv5_seq(wa, H, st));
-    CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
+    if (m->v5) {
+      SeqWkvArgs wa;
+      memset(&wa, 0, sizeof(wa));
+      wa.r = r; wa.k = k; wa.v = v; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
+      wa.state = reinterpret_cast<float *>(stb + off_mid(C, af)); wa.y = y; wa.T = T; wa.C = C;
+      wa.per_head = m->cfg.version == FR_B200_V5_0;
+      wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e); wa.s_in = (float *)(B + o_sin);
+      wa.batch_mode = batch_mode; wa.state_stride = m->state_stride / 4;
+      CU(launch_wkv5_seq(wa, H, st));
+      CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
+    } else {
+      Wkv4Args wa;
+      memset(&wa, 0, sizeof(wa));
+      wa.k = k; wa.v = v; wa.r = r; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
+      wa.state = stb + off_mid(C, af); wa.state_stride = m->state_stride; wa.out = yn; wa.T = T; wa.C = C; wa.batch_mode = batch_mode;
+      CU(launch_wkv4_rows(wa, st));
+    }
     {
       const GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f);
       CU(launch_gemm_group(&go, 1, 1, st));   // few tiles: 128-row tiles fill the SMs better (measured)
@@ -752,8 +835,9 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
     la.x = x; la.ln_w = vp(b + "ln2.weight"); la.ln_b = vp(b + "ln2.bias");
     la.mix[0] = vp(f + "time_mix_k"); la.mix[1] = vp(f + "time_mix_r");
     la.op[0] = op[0]; la.op[1] = op[1];
-    la.sx_rd = stb + off_ffn_sx(C, H, 1, af, par); la.sx_wr = stb + off_ffn_sx(C, H, 1, af, par ^ 1);
+    la.sx_rd = stb + off_ffn_sx(C, H, m->v5, af, par); la.sx_wr = stb + off_ffn_sx(C, H, m->v5, af, par ^ 1);
     la.T = T; la.C = C; la.nvec = 2; la.act_fp16 = af;
+    la.batch_mode = batch_mode; la.state_stride = m->state_stride;
     CU(launch_ln_mix_seq(la, st));
     const bool halve = af && (l + 1) % 6 == 0;   // x / 2 every 6 layers under fp16 activations (model_forward_seq.cpp:165-167)
     {
@@ -763,7 +847,21 @@ int seq_forward(fr_b200_model *m, int slot, const int32_t *ids, int T, cudaStrea
       const GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f);
       CU(launch_gemm_group(&gv, 1, 1, st));
     }
-    m->launches += 9;
+    m->launches += m->v5 ? 9 : 7;
+  }
+  if (batch_mode) {
+    // every row: ln_out, then the head as one more GEMM -> fp32 logits [R, Vpad]
+    SeqLnArgs la;
+    memset(&la, 0, sizeof(la));
+    la.x = x; la.ln_w = vp("ln_out.weight"); la.ln_b = vp("ln_out.bias"); la.op[0] = op[0];
+    la.T = T; la.C = C; la.nvec = 0; la.act_fp16 = af; la.batch_mode = 1;
+    CU(launch_ln_mix_seq(la, st));
+    GemmArgs gh = mk(op[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f);
+    gh.ldo = m->Vpad;
+    CU(launch_gemm_group(&gh, 1, mt, st));
+    m->launches += 2;
+    for (int bq = 0; bq < R; ++bq) m->par[bq] ^= 1u;
+    return 0;
   }
   // last token -> ln_out -> head, as a stand-alone matvec over the head's streaming tiles
   CU(launch_ln_row(x + (size_t)(T - 1) * C, vp("ln_out.weight"), vp("ln_out.bias"), C, m->d_lnvec, st));
@@ -801,7 +899,7 @@ int fr_b200_run_seq(fr_b200_model *m, int slot, const int32_t *ids, int n, float
     CU(cudaSetDevice(m->device));
     for (int i = 0; i < n; ++i)
       if (ids[i] < 0 || ids[i] >= m->V) return fail(FR_B200_E_ARG, "token id out of range");
-    int rc = seq_forward(m, slot, ids, n, st);
+    int rc = rows_forward(m, false, slot, ids, n, st);
     if (rc) return rc;
     if (last_logits) {
       if (is_host_ptr(last_logits)) {

@@ -139,6 +139,8 @@ struct SeqLnArgs {
   const void *sx_rd;         // shift state read for token 0 (act dtype)
   void *sx_wr;               // shift state written from token T-1
   int T, C, nvec, act_fp16;
+  int batch_mode;            // rows are streams: shift states are per row, state_stride bytes apart
+  size_t state_stride;
 };
 struct SeqWkvArgs {
   const float *r, *k, *v;    // [T, C]
@@ -148,12 +150,24 @@ struct SeqWkvArgs {
   int T, C, per_head;
   int n_chunks, chunk_len;   // the sequence is scanned in n_chunks parallel pieces of chunk_len tokens
   float *e_out, *s_in;       // [H, n_chunks, 64, 64] scratch: chunk end states from zero, chunk start states
+  int batch_mode;            // rows are streams (T of them, one token each); n_chunks must be 1
+  size_t state_stride;       // floats between the states of consecutive streams
+};
+struct Wkv4Args {
+  const float *k, *v, *r;    // [rows, C]; r before the sigmoid
+  const float *decay, *first;  // [C]
+  void *state;               // aa[C], bb[C], pp[C] of stream 0; state_stride bytes to the next stream
+  size_t state_stride;
+  __half *out;               // [rows, C] sigmoid(r) * wkv
+  int T, C, batch_mode;      // seq: T rows of one stream; batch: T streams, one row each
 };
 cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st);
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st);
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st);
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
                                cudaStream_t st);
+cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st);
+cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, cudaStream_t st);
 cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st);
 cudaError_t launch_transpose_f16(const __half *src, int K, int N, __half *dst, cudaStream_t st);   // [K,N] -> [N,K]
 

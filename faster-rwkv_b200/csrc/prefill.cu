@@ -361,34 +361,96 @@ __global__ void gather_emb_kernel(const void *emb, int emb_f32, const int32_t *i
 // MixWithG of :384; ffn_seq.cu:70-76): op_v[t] = xx[t] * mu_v + prev[t] * (1 - mu_v), prev[0] = the stored shift
 // state, prev[t] = xx[t-1]; the new shift state is xx[T-1].  One CTA per token; it normalises its own row and the
 // row before it, so no CTA waits for another.
+// Batch mode (rows = independent streams, one token each): prev of row b is stream b's stored shift state and every
+// row writes its new one.  nvec == 0: plain LayerNorm into op[0] (ln_out before the head).
 __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
   __shared__ float red[16];
   const int t = blockIdx.x, C = a.C;
   const float *xr = a.x + (size_t)t * C;
   const float2 st = row_stats(xr, C, red);
+  const bool from_row = !a.batch_mode && t > 0;
   float2 sp = make_float2(0.f, 0.f);
-  if (t > 0) sp = row_stats(xr - C, C, red);
+  if (from_row && a.nvec > 0) sp = row_stats(xr - C, C, red);
+  const uint8_t *srd = reinterpret_cast<const uint8_t *>(a.sx_rd) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
+  uint8_t *swr = reinterpret_cast<uint8_t *>(a.sx_wr) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
   for (int i = threadIdx.x; i < C; i += blockDim.x) {
     const float w = a.ln_w[i], b = a.ln_b[i];
     const float xx = (xr[i] - st.x) * st.y * w + b;
+    if (a.nvec == 0) {
+      a.op[0][(size_t)t * C + i] = __float2half_rn(xx);
+      continue;
+    }
     float prev;
-    if (t > 0) prev = (xr[i - C] - sp.x) * sp.y * w + b;
-    else prev = a.act_fp16 ? __half2float(reinterpret_cast<const __half *>(a.sx_rd)[i]) : reinterpret_cast<const float *>(a.sx_rd)[i];
-    if (a.act_fp16 && t > 0) prev = __half2float(__float2half_rn(prev));   // what the token loop would have stored as shift state
-    const float xh = xx;
+    if (from_row) prev = (xr[i - C] - sp.x) * sp.y * w + b;
+    else prev = a.act_fp16 ? __half2float(reinterpret_cast<const __half *>(srd)[i]) : reinterpret_cast<const float *>(srd)[i];
+    if (a.act_fp16 && from_row) prev = __half2float(__float2half_rn(prev));   // what the token loop would have stored as shift state
 #pragma unroll
     for (int v = 0; v < 4; ++v)
       if (v < a.nvec) {
         const float m = a.mix[v][i];
-        const float val = xh * m + prev * (1.f - m);
+        const float val = xx * m + prev * (1.f - m);
         const __half hi = __float2half_rn(val);
         a.op[v][(size_t)t * C + i] = hi;
         if (a.op_lo[v]) a.op_lo[v][(size_t)t * C + i] = __float2half_rn(val - __half2float(hi));
       }
-    if (t == a.T - 1) {
-      if (a.act_fp16) reinterpret_cast<__half *>(a.sx_wr)[i] = __float2half_rn(xx);
-      else reinterpret_cast<float *>(a.sx_wr)[i] = xx;
+    if (a.batch_mode || t == a.T - 1) {
+      if (a.act_fp16) reinterpret_cast<__half *>(swr)[i] = __float2half_rn(xx);
+      else reinterpret_cast<float *>(swr)[i] = xx;
     }
+  }
+}
+
+// RWKV-4 WKV over rows (WkvForwardOne, att.cu:30-62, with the sigmoid of att.cu:154-159 fused): one thread per
+// (stream, channel).  Seq mode: one stream, T rows in order; batch mode: row b is the one token of stream b.
+//   out[row, c] = sigmoid(r) * wkv (fp16, the operand of the output projection); aa, bb, pp updated in place.
+__global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (c >= a.C) return;
+  float *st = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.state) + (size_t)b * a.state_stride);
+  float aa = st[c], bb = st[a.C + c], pp = st[2 * a.C + c];
+  const float u = a.first[c], w = a.decay[c];
+  const int t0 = a.batch_mode ? b : 0, t1 = a.batch_mode ? b + 1 : a.T;
+  for (int t = t0; t < t1; ++t) {
+    const size_t o = (size_t)t * a.C + c;
+    const float k = a.k[o], v = a.v[o], r = 1.f / (1.f + expf(-a.r[o]));
+    float ww = u + k;
+    float pm = fmaxf(pp, ww);
+    float e1 = expf(pp - pm), e2 = expf(ww - pm);
+    const float wkv = (e1 * aa + e2 * v) / (e1 * bb + e2);
+    a.out[o] = __float2half_rn(r * wkv);
+    ww = w + pp;
+    pm = fmaxf(ww, k);
+    e1 = expf(ww - pm);
+    e2 = expf(k - pm);
+    aa = e1 * aa + e2 * v;
+    bb = e1 * bb + e2;
+    pp = pm;
+  }
+  st[c] = aa; st[a.C + c] = bb; st[2 * a.C + c] = pp;
+}
+
+// greedy sample of every row: index of the largest logit (lowest index on ties)
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, int V, int ld, int32_t *out) {
+  __shared__ unsigned long long best[8];
+  const float *row = logits + (size_t)blockIdx.x * ld;
+  unsigned long long m = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    unsigned u = __float_as_uint(row[i]);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    const unsigned long long w = ((unsigned long long)u << 32) | (0xffffffffu - (unsigned)i);
+    m = w > m ? w : m;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, m, o);
+    m = other > m ? other : m;
+  }
+  if ((threadIdx.x & 31) == 0) best[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w8 = 1; w8 < 8; ++w8) m = best[w8] > m ? best[w8] : m;
+    out[blockIdx.x] = (int32_t)(0xffffffffu - (unsigned)m);
   }
 }
 
@@ -423,9 +485,11 @@ __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
   __shared__ __align__(16) float sr[2][WKV_TT][64], sk[2][WKV_TT][64], sv[2][WKV_TT][64];
   const int h = blockIdx.x, c = blockIdx.y, C = a.C;
   const int jg = threadIdx.x >> 2, iq = threadIdx.x & 3;
-  const int t_begin = c * a.chunk_len, t_end = min(a.T, t_begin + a.chunk_len);
+  // batch mode: blockIdx.y is the stream, its one token is row c, its state lies state_stride floats further
+  const int t_begin = a.batch_mode ? c : c * a.chunk_len, t_end = a.batch_mode ? c + 1 : min(a.T, t_begin + a.chunk_len);
   float s[4][16], w[16], u[16];
-  const float *Sin = a.n_chunks == 1 ? a.state + (size_t)h * 4096 : a.s_in + ((size_t)h * a.n_chunks + c) * 4096;
+  float *Sown = a.state + (a.batch_mode ? (size_t)c * a.state_stride : 0) + (size_t)h * 4096;
+  const float *Sin = a.n_chunks == 1 ? Sown : a.s_in + ((size_t)h * a.n_chunks + c) * 4096;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int ii = iq * 16 + i;
@@ -481,7 +545,7 @@ __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
     buf ^= 1;
   }
   if (MODE == 0 || a.n_chunks == 1) {
-    float *S = MODE == 0 ? a.e_out + ((size_t)h * a.n_chunks + c) * 4096 : a.state + (size_t)h * 4096;
+    float *S = MODE == 0 ? a.e_out + ((size_t)h * a.n_chunks + c) * 4096 : Sown;
 #pragma unroll
     for (int i = 0; i < 16; ++i)
 #pragma unroll
@@ -562,6 +626,10 @@ cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
   return cudaGetLastError();
 }
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
+  if (a.batch_mode) {
+    wkv5_seq_kernel<2><<<dim3(H, a.T), WKV_THREADS, 0, st>>>(a);   // n_chunks == 1: every stream reads and writes its own state
+    return cudaGetLastError();
+  }
   if (a.n_chunks <= 1) {
     wkv5_seq_kernel<2><<<dim3(H, 1), WKV_THREADS, 0, st>>>(a);
     return cudaGetLastError();
@@ -569,6 +637,15 @@ cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
   wkv5_seq_kernel<0><<<dim3(H, a.n_chunks), WKV_THREADS, 0, st>>>(a);
   wkv5_combine_kernel<<<H * 16, 256, 0, st>>>(a);
   wkv5_seq_kernel<2><<<dim3(H, a.n_chunks), WKV_THREADS, 0, st>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st) {
+  dim3 grid((a.C + 255) / 256, a.batch_mode ? a.T : 1);
+  wkv4_rows_kernel<<<grid, 256, 0, st>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, cudaStream_t st) {
+  argmax_rows_kernel<<<rows, 256, 0, st>>>(logits, V, ld, out);
   return cudaGetLastError();
 }
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,

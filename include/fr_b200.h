@@ -55,7 +55,9 @@ typedef struct fr_b200_config {
   int weight_format;  /* FR_B200_W_* */
   int act_fp16;       /* 1: "cuda fp16" semantics — fp16 token-shift states and x /= 2 every 6 layers
                          (kernels/default/model_forward.cpp:173-175); 0: fp32 activations ("int8"/"int4") */
-  int max_batch;      /* streams decoded per call, 1..8 */
+  int max_batch;      /* stream slots, 1..4096.  Up to 8 streams per call run in the persistent kernel; a model created
+                       * with max_batch > 8 also keeps every projection as fp16 W^T (dequantised for int8 / int4) and
+                       * decodes larger batches through tensor-core GEMMs, one row per stream */
   int device;         /* CUDA device ordinal */
 } fr_b200_config;
 
