@@ -437,6 +437,20 @@ def main():
                 variants[f"{fmt}_b{vb}"] = {"error": str(ex)[:200]}
 
         variants["prefill_c3_T4096"] = prefill_leg(pkg, local_rank)
+        # many streams at once: one row per stream through the tensor-core GEMM path (c2-shaped: int4 weights, 256 streams)
+        for fmt, vb in (("int4", 256), ("fp16", 256)):
+            try:
+                mv = build_model(pkg, shape, fmt, vb, local_rank, seed=0)
+                vms, _, _ = timed_greedy(mv, pkg.synth.token_ids(shape, vb, seed=0), 32, W)
+                P = algorithmic_bytes(shape, "fp16") // 2          # projection parameters
+                tf = 2.0 * P * vb * 32 / (vms * 1e-3) / 1e12
+                variants[f"{fmt}_b{vb}_gemm"] = {"tok_s": vb * 32 / (vms * 1e-3), "ms_per_step": vms / 32, "tflops": tf,
+                                                 "note": "weights held as fp16 W^T (dequantised) for the GEMM path"}
+                mv.close()
+                del mv
+                torch.cuda.empty_cache()
+            except Exception as ex:
+                variants[f"{fmt}_b{vb}_gemm"] = {"error": str(ex)[:200]}
 
     cb = None
     if host_master is not None:

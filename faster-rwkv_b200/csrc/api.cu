@@ -38,6 +38,7 @@ struct MatrixSlot {       // where a projection matrix lives inside the packed w
   bool set = false;
   bool has_plain = false; // seq mode keeps the matrix a second time as W^T [N, K] fp16 row-major
   size_t plain_off = 0;   // offset of that copy in halfs
+  size_t pscale_off = 0;  // int8: offset of the [N] output-row scales that go with the copy (the copy holds the codes)
 };
 
 struct VecSlot {
@@ -71,7 +72,9 @@ struct fr_b200_model {
   unsigned long long *d_hist = nullptr; size_t hist_n = 0;   // packed arg-max words of decode_greedy, [tokens][batch]
   unsigned long long *d_amax = nullptr;   // packed arg-max words of a single decode, [max_batch]
   // seq mode (RWKV-5.x with fp16 weights): plain copies of the projection matrices, activation buffers for seq_T tokens
-  __half *d_plain = nullptr;     size_t plain_halfs = 0;
+  __half *d_plain = nullptr;     size_t plain_halfs = 0;   // fp16: W^T; int8: the integer codes as fp16; int4: hi(q * scale)
+  __half *d_plain2 = nullptr;    // int4: lo(q * scale), what fp16 rounding of the dequantised weight lost
+  __half *d_pscale = nullptr;    size_t pscale_halfs = 0;  // int8: per output row scales, per matrix
   uint8_t *d_seq = nullptr;      size_t seq_bytes = 0; int seq_T = 0;
   PhaseDev *d_head_phase = nullptr;   // the head as a stand-alone matvec phase
   float *d_lnvec = nullptr;           // ln_out of the last prompt token
@@ -192,7 +195,7 @@ void plan(fr_b200_model *m) {
   phase(PH_HEAD, 0, C, nbV, 1, woff, roff);
   woff += (size_t)nbV * rbC; roff += (size_t)nbV * ROWS;
   m->weights_bytes = woff; m->rscale_n = roff; m->vecs_n = voff;
-  m->plain_halfs = 0;
+  m->plain_halfs = 0; m->pscale_halfs = 0;
   // the GEMM path needs every projection again as W^T fp16 (dequantised for int8 / int4): seq mode of RWKV-5.x fp16
   // models, and decode of more than 8 streams at once for every model (then the head too: all rows want logits)
   const bool big = m->cfg.max_batch > MAX_B;
@@ -202,6 +205,8 @@ void plan(fr_b200_model *m) {
       kv.second.has_plain = true;
       kv.second.plain_off = m->plain_halfs;
       m->plain_halfs += ((size_t)kv.second.K * kv.second.N + 127) / 128 * 128;
+      kv.second.pscale_off = m->pscale_halfs;
+      if (fmt == FMT_INT8) m->pscale_halfs += ((size_t)kv.second.N + 7) / 8 * 8;
     }
   m->stream_bytes = (long long)woff + (fmt == FMT_INT8 ? (long long)roff * 2 : 0);
 }
@@ -242,12 +247,9 @@ int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int d
       CU(launch_pack(FMT_INT8, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
                      s.item_stride, m->d_rscale + s.rscale_off, s.rscale_stride, 0));
       if (s.has_plain && m->d_plain) {
-        if ((rc = ensure_scratch(m, 0, n * 4))) return rc;   // the input is packed: its buffer takes the dequantised matrix
-        if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
-        CU(launch_dequant_int8(reinterpret_cast<const int8_t *>(m->d_scratch[2]), reinterpret_cast<const __half *>(m->d_scratch[3]),
-                               s.K, s.N, reinterpret_cast<float *>(m->d_scratch[0]), 0));
-        CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]), n, 0));
-        CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[1]), s.K, s.N, m->d_plain + s.plain_off, 0));
+        // the codes are [N, K] already and exact in fp16; the row scale is applied to the accumulator
+        CU(launch_i8_to_f16(reinterpret_cast<const int8_t *>(m->d_scratch[2]), m->d_plain + s.plain_off, n, 0));
+        CU(cudaMemcpy(m->d_pscale + s.pscale_off, m->d_scratch[3], (size_t)s.N * 2, cudaMemcpyDeviceToDevice));
       }
     } else {
       if ((rc = ensure_scratch(m, 2, n / 2))) return rc;
@@ -256,12 +258,16 @@ int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int d
       CU(launch_pack(FMT_INT4, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
                      s.item_stride, nullptr, 0, 0));
       if (s.has_plain && m->d_plain) {
-        if ((rc = ensure_scratch(m, 0, n * 4))) return rc;
-        if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
+        // q * scale needs up to 14 significant bits: kept as an fp16 pair (hi, lo), exact
+        if ((rc = ensure_scratch(m, 0, n * 4))) return rc;   // the input is packed: its buffer takes the dequantised matrix
         CU(launch_dequant_int4(reinterpret_cast<const uint8_t *>(m->d_scratch[2]), reinterpret_cast<const __half *>(m->d_scratch[3]),
                                s.K, s.N, reinterpret_cast<float *>(m->d_scratch[0]), 0));
-        CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]), n, 0));
+        if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
+        if ((rc = ensure_scratch(m, 2, n * 2))) return rc;
+        CU(launch_f32_split_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]),
+                                reinterpret_cast<__half *>(m->d_scratch[2]), n, 0));
         CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[1]), s.K, s.N, m->d_plain + s.plain_off, 0));
+        CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[2]), s.K, s.N, m->d_plain2 + s.plain_off, 0));
       }
     }
   }
@@ -376,6 +382,8 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
   if (!rc) rc = alloc((void **)&m->d_amax, (size_t)B * 8);
   if (!rc && m->plain_halfs) rc = alloc((void **)&m->d_plain, m->plain_halfs * 2);
+  if (!rc && m->plain_halfs && m->fmt == FMT_INT4) rc = alloc((void **)&m->d_plain2, m->plain_halfs * 2);
+  if (!rc && m->pscale_halfs) rc = alloc((void **)&m->d_pscale, m->pscale_halfs * 2);
   if (!rc) rc = alloc((void **)&m->d_head_phase, sizeof(PhaseDev));
   if (!rc) rc = alloc((void **)&m->d_lnvec, (size_t)m->C * 4);
   if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
@@ -397,7 +405,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   cudaSetDevice(m->device);
   free_scratch(m);
   void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
-                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_seq, m->d_head_phase, m->d_lnvec};
+                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_plain2, m->d_pscale, m->d_seq, m->d_head_phase, m->d_lnvec};
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);
@@ -745,7 +753,9 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   auto take = [&](size_t bytes) { const size_t o = off; off += align256(bytes); return o; };
   const size_t o_ids = take((size_t)T * 4), o_x = take(TC * 4), o_r = take(TC * 4), o_k = take(TC * 4), o_v = take(TC * 4),
                o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
-               o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2), o_lo0 = take(TC * 2), o_lo1 = take(TC * 2);
+               o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2), o_lo0 = take(TC * 2), o_lo1 = take(TC * 2),
+               o_lo2 = take(batch_mode ? TC * 2 : 0), o_lo3 = take(batch_mode ? TC * 2 : 0), o_ynlo = take(batch_mode ? TC * 2 : 0),
+               o_kklo = take(batch_mode ? TF * 2 : 0), o_glo = take(batch_mode ? TC * 2 : 0);
   // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
   int n_chunks = 1, chunk_len = T;
   if (!batch_mode && m->v5) {
@@ -767,6 +777,11 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   __half *op[4] = {(__half *)(B + o_op0), (__half *)(B + o_op1), (__half *)(B + o_op2), (__half *)(B + o_op3)};
   __half *g = (__half *)(B + o_g), *yn = (__half *)(B + o_yn), *kk = (__half *)(B + o_kk), *rr = g;   // rr reuses g
   __half *lo0 = (__half *)(B + o_lo0), *lo1 = (__half *)(B + o_lo1);
+  // batch mode keeps every GEMM input as a hi + lo pair: the steps are bound by weight bytes, not flops, and the
+  // per-stream error must not depend on how many streams share the step
+  __half *lo2 = batch_mode ? (__half *)(B + o_lo2) : nullptr, *lo3 = batch_mode ? (__half *)(B + o_lo3) : nullptr;
+  __half *yn_lo = batch_mode ? (__half *)(B + o_ynlo) : nullptr, *kk_lo = batch_mode ? (__half *)(B + o_kklo) : nullptr;
+  __half *g_lo = batch_mode ? (__half *)(B + o_glo) : nullptr, *rr_lo = g_lo;   // like rr reuses g
   CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
   CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
   auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
@@ -775,7 +790,9 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
                 float scale, const __half *A2 = nullptr) -> GemmArgs {
     GemmArgs ga;
     memset(&ga, 0, sizeof(ga));
-    ga.A = A; ga.A2 = A2; ga.Bt = wt(w); ga.M = T; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
+    ga.A = A; ga.A2 = A2; ga.Bt = wt(w); ga.M = T;
+    if (m->d_plain2) ga.Bt2 = m->d_plain2 + m->mats[w].plain_off;
+    if (m->d_pscale) ga.col_scale = m->d_pscale + m->mats[w].pscale_off; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
     ga.scale = scale; ga.status = m->out_status();
     return ga;
   };
@@ -798,15 +815,15 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     la.batch_mode = batch_mode; la.state_stride = m->state_stride;
     // k and v build the recurrent state, which keeps growing with the prompt: their projections take the
     // activations as hi + lo fp16 pairs (a second pass over K), like every decode matvec does
-    la.op_lo[0] = lo0; la.op_lo[1] = lo1;
+    la.op_lo[0] = lo0; la.op_lo[1] = lo1; la.op_lo[2] = lo2; la.op_lo[3] = lo3;
     CU(launch_ln_mix_seq(la, st));
     {
       // the attention projections in one launch; the two with a second pass over K first
       GemmArgs grp[4] = {mk(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0),
                          mk(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f, lo1),
-                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f),
-                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f)};
-      if (m->gate) grp[3] = mk(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f);
+                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2),
+                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2)};
+      if (m->gate) { grp[3] = mk(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f, lo3); grp[3].out_lo = g_lo; }
       CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st));
     }
     if (m->v5) {
@@ -818,16 +835,16 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e); wa.s_in = (float *)(B + o_sin);
       wa.batch_mode = batch_mode; wa.state_stride = m->state_stride / 4;
       CU(launch_wkv5_seq(wa, H, st));
-      CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, T, H, yn, st));
+      CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, m->gate ? g_lo : nullptr, T, H, yn, yn_lo, st));
     } else {
       Wkv4Args wa;
       memset(&wa, 0, sizeof(wa));
       wa.k = k; wa.v = v; wa.r = r; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
-      wa.state = stb + off_mid(C, af); wa.state_stride = m->state_stride; wa.out = yn; wa.T = T; wa.C = C; wa.batch_mode = batch_mode;
+      wa.state = stb + off_mid(C, af); wa.state_stride = m->state_stride; wa.out = yn; wa.out_lo = yn_lo; wa.T = T; wa.C = C; wa.batch_mode = batch_mode;
       CU(launch_wkv4_rows(wa, st));
     }
     {
-      const GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f);
+      const GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
       CU(launch_gemm_group(&go, 1, 1, st));   // few tiles: 128-row tiles fill the SMs better (measured)
     }
     // ---- channel mix ----
@@ -835,16 +852,19 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     la.x = x; la.ln_w = vp(b + "ln2.weight"); la.ln_b = vp(b + "ln2.bias");
     la.mix[0] = vp(f + "time_mix_k"); la.mix[1] = vp(f + "time_mix_r");
     la.op[0] = op[0]; la.op[1] = op[1];
+    la.op_lo[0] = batch_mode ? lo0 : nullptr; la.op_lo[1] = batch_mode ? lo1 : nullptr;
     la.sx_rd = stb + off_ffn_sx(C, H, m->v5, af, par); la.sx_wr = stb + off_ffn_sx(C, H, m->v5, af, par ^ 1);
     la.T = T; la.C = C; la.nvec = 2; la.act_fp16 = af;
     la.batch_mode = batch_mode; la.state_stride = m->state_stride;
     CU(launch_ln_mix_seq(la, st));
     const bool halve = af && (l + 1) % 6 == 0;   // x / 2 every 6 layers under fp16 activations (model_forward_seq.cpp:165-167)
     {
-      const GemmArgs grp[2] = {mk(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f),
-                               mk(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f)};
+      GemmArgs grp[2] = {mk(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f, batch_mode ? lo0 : nullptr),
+                         mk(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f, batch_mode ? lo1 : nullptr)};
+      grp[0].out_lo = kk_lo; grp[1].out_lo = rr_lo;
       CU(launch_gemm_group(grp, 2, mt, st));
-      const GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f);
+      GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f, kk_lo);
+      gv.aux1_lo = rr_lo;
       CU(launch_gemm_group(&gv, 1, 1, st));
     }
     m->launches += m->v5 ? 9 : 7;
@@ -853,10 +873,10 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     // every row: ln_out, then the head as one more GEMM -> fp32 logits [R, Vpad]
     SeqLnArgs la;
     memset(&la, 0, sizeof(la));
-    la.x = x; la.ln_w = vp("ln_out.weight"); la.ln_b = vp("ln_out.bias"); la.op[0] = op[0];
+    la.x = x; la.ln_w = vp("ln_out.weight"); la.ln_b = vp("ln_out.bias"); la.op[0] = op[0]; la.op_lo[0] = lo0;
     la.T = T; la.C = C; la.nvec = 0; la.act_fp16 = af; la.batch_mode = 1;
     CU(launch_ln_mix_seq(la, st));
-    GemmArgs gh = mk(op[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f);
+    GemmArgs gh = mk(op[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f, lo0);
     gh.ldo = m->Vpad;
     CU(launch_gemm_group(&gh, 1, mt, st));
     m->launches += 2;

@@ -117,11 +117,15 @@ struct GemmArgs {
   const __half *A;     // [M, K] row-major
   const __half *A2;    // optional [M, K]: low halves of the activations (A + A2 is the fp32 value to ~22 bits)
   const __half *Bt;    // [N, K] row-major (the weight matrix transposed: one row per output channel)
+  const __half *Bt2;   // optional [N, K]: what rounding the weights to fp16 lost (int4: q * scale needs 14 bits); third pass
+  const __half *col_scale;   // optional [N]: acc *= col_scale[n] before the epilogue (int8: Bt holds the integer codes)
   int M, N, K;         // K a multiple of 64
   int epi;
   void *out;           // [M, ldo]
+  void *out_lo;        // optional, fp16 epilogues: what rounding out to fp16 lost, same shape
   int ldo;
   const void *aux0, *aux1;   // [M, ldo] like out
+  const void *aux1_lo;       // optional: fp16 rounding remainder of aux1
   float scale;
   int *status;         // device word: set when a bounded wait gives up
 };
@@ -159,13 +163,14 @@ struct Wkv4Args {
   void *state;               // aa[C], bb[C], pp[C] of stream 0; state_stride bytes to the next stream
   size_t state_stride;
   __half *out;               // [rows, C] sigmoid(r) * wkv
+  __half *out_lo;            // optional: its fp16 rounding remainder
   int T, C, batch_mode;      // seq: T rows of one stream; batch: T streams, one row each
 };
 cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st);
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st);
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st);
-cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
-                               cudaStream_t st);
+cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
+                               int H, __half *out, __half *out_lo, cudaStream_t st);
 cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st);
 cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, cudaStream_t st);
 cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st);
@@ -184,6 +189,8 @@ cudaError_t launch_unpack_ids(const unsigned long long *packed, int n, int32_t *
 // quantise / pack (pack.cu); all pointers device
 cudaError_t launch_f16_to_f32(const __half *src, float *dst, size_t n, cudaStream_t st);
 cudaError_t launch_f32_to_f16(const float *src, __half *dst, size_t n, cudaStream_t st);
+cudaError_t launch_i8_to_f16(const int8_t *src, __half *dst, size_t n, cudaStream_t st);
+cudaError_t launch_f32_split_f16(const float *src, __half *hi, __half *lo, size_t n, cudaStream_t st);
 cudaError_t launch_quant_int8(const float *W, int K, int N, int8_t *q, __half *scales, cudaStream_t st);
 cudaError_t launch_quant_int4(const float *W, int K, int N, uint8_t *packed, __half *scales, cudaStream_t st);
 cudaError_t launch_dequant_int8(const int8_t *q, const __half *scales, int K, int N, float *W, cudaStream_t st);

@@ -198,6 +198,29 @@ cudaError_t launch_f16_to_f32(const __half *src, float *dst, size_t n, cudaStrea
   if (n) k_f16_to_f32<<<blocks_for(n, 256), 256, 0, st>>>(src, dst, n);
   return cudaGetLastError();
 }
+namespace {
+__global__ void k_i8_to_f16(const int8_t *src, __half *dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __int2half_rn((int)src[i]);
+}
+// hi = fp16(x), lo = fp16(x - hi): together they carry ~22 bits of x
+__global__ void k_f32_split_f16(const float *src, __half *hi, __half *lo, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const __half h = __float2half_rn(src[i]);
+    hi[i] = h;
+    lo[i] = __float2half_rn(src[i] - __half2float(h));
+  }
+}
+}  // namespace
+cudaError_t launch_i8_to_f16(const int8_t *src, __half *dst, size_t n, cudaStream_t st) {
+  if (n) k_i8_to_f16<<<blocks_for(n, 256), 256, 0, st>>>(src, dst, n);
+  return cudaGetLastError();
+}
+cudaError_t launch_f32_split_f16(const float *src, __half *hi, __half *lo, size_t n, cudaStream_t st) {
+  if (n) k_f32_split_f16<<<blocks_for(n, 256), 256, 0, st>>>(src, hi, lo, n);
+  return cudaGetLastError();
+}
 cudaError_t launch_f32_to_f16(const float *src, __half *dst, size_t n, cudaStream_t st) {
   if (n) k_f32_to_f16<<<blocks_for(n, 256), 256, 0, st>>>(src, dst, n);
   return cudaGetLastError();

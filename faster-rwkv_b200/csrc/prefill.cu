@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 
@@ -20,8 +21,9 @@ namespace frb {
 namespace {
 
 // ------------------------------------------------------------------------------------------------
-// tcgen05 GEMM: out[M, N] = epilogue((A + A2)[M, K] . Bt[N, K]^T), fp16 operands (both K-major), fp32 accumulate.
-// A2 (optional) holds what rounding the activations to fp16 lost; it makes a second pass over K.
+// tcgen05 GEMM: out[M, N] = epilogue((A + A2)[M, K] . (Bt + Bt2)[N, K]^T), fp16 operands (both K-major), fp32
+// accumulate.  A2 (optional) holds what rounding the activations to fp16 lost: its tiles travel in the same ring slot
+// and multiply the same B tile.  Bt2 (optional, int4 weights) is a second pass over K.
 // One CTA per 128 x 256 output tile; K is walked in 64-wide slices through a 4-deep TMA ring.
 //   warp 0 (one lane): TMA producer          warp 1 (one lane): MMA issue; the warp owns the TMEM allocation
 //   warps 2..5: epilogue, one TMEM lane quadrant (32 rows) each
@@ -103,6 +105,12 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
     const float *x = reinterpret_cast<const float *>(g.aux0) + o;
     const __half *r = reinterpret_cast<const __half *>(g.aux1) + o;
     const bool mul = g.epi == GEMM_EPI_MULADD_F32;
+    if (mul && g.aux1_lo) {
+      const __half *rl = reinterpret_cast<const __half *>(g.aux1_lo) + o;
+      for (int i = 0; i < ncol; ++i)
+        out[i] = (x[i] + (__half2float(r[i]) + __half2float(rl[i])) * __uint_as_float(acc[i])) * g.scale;
+      return;
+    }
     if (full) {
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
@@ -132,6 +140,17 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
     return;
   }
   __half *out = reinterpret_cast<__half *>(g.out) + o;
+  if (g.out_lo) {
+    // the consumer of this output wants it as a hi + lo pair (batched decode keeps ~22 bits between projections)
+    __half *lo = reinterpret_cast<__half *>(g.out_lo) + o;
+    for (int i = 0; i < ncol; ++i) {
+      const float v = epi_half_op(g.epi, __uint_as_float(acc[i]));
+      const __half h = __float2half_rn(v);
+      out[i] = h;
+      lo[i] = __float2half_rn(v - __half2float(h));
+    }
+    return;
+  }
   if (full) {
 #pragma unroll
     for (int i = 0; i < 32; i += 8) {
@@ -152,11 +171,16 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
 // attention projections of a layer, or the two channel-mix projections that read the LayerNorm output.
 struct GemmGroup {
   int n;
+  int stages;                           // ring depth (2..4)
+  uint32_t stage_bytes;                 // bytes per ring slot: [A hi tiles][A lo tiles, if any problem has them][B tile]
+  int dual;                             // 1: the slot has room for the low halves of A (128-row tiles);
+                                        // 0: low halves of A, if any, are a further pass over K (256-row tiles: a
+                                        //    slot with both would leave a 2-deep ring)
   int tile_start[GEMM_GROUP_MAX + 1];   // first grid.x index of each problem
   GemmArgs p[GEMM_GROUP_MAX];
 };
 struct alignas(64) GemmMaps {
-  CUtensorMap a[GEMM_GROUP_MAX], a2[GEMM_GROUP_MAX], b[GEMM_GROUP_MAX];
+  CUtensorMap a[GEMM_GROUP_MAX], a2[GEMM_GROUP_MAX], b[GEMM_GROUP_MAX], b2[GEMM_GROUP_MAX];
 };
 
 // MT = 128-row sub-tiles per CTA (1: 128 x 256 output tile, 4-deep ring; 2: 256 x 256, two accumulators sharing
@@ -164,8 +188,9 @@ struct alignas(64) GemmMaps {
 template <int MT>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
-  constexpr int STAGES = MT == 1 ? 4 : 3;
-  constexpr uint32_t STAGE_BYTES = MT * G_A_BYTES + G_B_BYTES;
+  const int STAGES = grp.stages;
+  const uint32_t STAGE_BYTES = grp.stage_bytes;
+  const uint32_t B_OFF = (uint32_t)(grp.dual ? 2 : 1) * MT * G_A_BYTES;   // the B tile follows the A tiles
   constexpr uint32_t TMEM_COLS = MT * GBN;
   extern __shared__ uint8_t gsm_raw[];
   // barriers in the first KB, tiles from the next 1024-byte boundary
@@ -182,7 +207,10 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
   const GemmArgs &g = grp.p[pi];
   const int tile_m = blockIdx.y, tile_n = blockIdx.x - grp.tile_start[pi];
   const int num_k1 = g.K / GBK;
-  const int num_k = g.A2 ? 2 * num_k1 : num_k1;   // a second pass over K with the low halves of A, same accumulator
+  // the low halves of A (A2) ride in the same ring slot as the high halves and meet the same B tile; the low
+  // halves of B (Bt2) are a second pass over K into the same accumulator
+  const bool has_lo = g.A2 != nullptr && grp.dual, lo_pass = g.A2 != nullptr && !grp.dual;
+  const int num_k = num_k1 * (1 + (lo_pass ? 1 : 0) + (g.Bt2 ? 1 : 0));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -205,14 +233,17 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         const int s = kb % STAGES;
         const uint32_t parity = ((kb / STAGES) & 1) ^ 1;   // a fresh barrier reads as "previous phase complete"
         if (!mbar_wait(&empty[s], parity, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
+        const int pass = kb / num_k1, kk = kb - pass * num_k1;
+        const bool lo_now = has_lo && pass == 0;   // the (lo A) x (lo B) term is below fp32 resolution: skipped
+        const bool a_is_lo = lo_pass && pass == 1, b_is_lo = pass > 0 && !a_is_lo;
+        mbar_expect_tx(&full[s], (uint32_t)(lo_now ? 2 : 1) * MT * G_A_BYTES + G_B_BYTES);
         const uint32_t a_dst = tiles + (uint32_t)s * STAGE_BYTES;
-        const int kk = kb < num_k1 ? kb : kb - num_k1;
-        const CUtensorMap *ma = kb < num_k1 ? &maps.a[pi] : &maps.a2[pi];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(a_dst + (uint32_t)mt * G_A_BYTES, ma, kk * GBK, (tile_m * MT + mt) * GBM, &full[s]);
-        tma_load_2d(a_dst + MT * G_A_BYTES, &maps.b[pi], kk * GBK, tile_n * GBN, &full[s]);
+        for (int mt = 0; mt < MT; ++mt) {
+          tma_load_2d(a_dst + (uint32_t)mt * G_A_BYTES, a_is_lo ? &maps.a2[pi] : &maps.a[pi], kk * GBK, (tile_m * MT + mt) * GBM, &full[s]);
+          if (lo_now) tma_load_2d(a_dst + (uint32_t)(MT + mt) * G_A_BYTES, &maps.a2[pi], kk * GBK, (tile_m * MT + mt) * GBM, &full[s]);
+        }
+        tma_load_2d(a_dst + B_OFF, b_is_lo ? &maps.b2[pi] : &maps.b[pi], kk * GBK, tile_n * GBN, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -222,13 +253,20 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
         tc_fence_after();
         const uint32_t a_addr = tiles + (uint32_t)s * STAGE_BYTES;
-        const uint64_t bd = umma_desc_k128(a_addr + MT * G_A_BYTES);
+        const uint64_t bd = umma_desc_k128(a_addr + B_OFF);
+        const bool lo_now = has_lo && kb < num_k1;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const uint64_t ad = umma_desc_k128(a_addr + (uint32_t)mt * G_A_BYTES);
 #pragma unroll
           for (int k4 = 0; k4 < GBK / 16; ++k4)   // 16 inputs = 32 bytes further along the swizzled rows
             umma_f16(tmem_base + (uint32_t)mt * GBN, ad + (uint64_t)(k4 * 2), bd + (uint64_t)(k4 * 2), G_IDESC, (kb | k4) != 0);
+          if (lo_now) {
+            const uint64_t al = umma_desc_k128(a_addr + (uint32_t)(MT + mt) * G_A_BYTES);
+#pragma unroll
+            for (int k4 = 0; k4 < GBK / 16; ++k4)
+              umma_f16(tmem_base + (uint32_t)mt * GBN, al + (uint64_t)(k4 * 2), bd + (uint64_t)(k4 * 2), G_IDESC, 1u);
+          }
         }
         umma_commit(&empty[s]);   // the slot is free once these MMAs have read it
       }
@@ -248,6 +286,13 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
           if (tile_n * GBN + c0 >= g.N) break;   // warp-uniform
           uint32_t acc[32];
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * GBN + c0), acc);
+          if (g.col_scale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = tile_n * GBN + c0 + i;
+              acc[i] = __float_as_uint(__uint_as_float(acc[i]) * (col < g.N ? __half2float(g.col_scale[col]) : 0.f));
+            }
+          }
           if (row < g.M) gemm_epilogue_row(g, row, tile_n * GBN + c0, acc);
         }
       }
@@ -377,7 +422,9 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
     const float w = a.ln_w[i], b = a.ln_b[i];
     const float xx = (xr[i] - st.x) * st.y * w + b;
     if (a.nvec == 0) {
-      a.op[0][(size_t)t * C + i] = __float2half_rn(xx);
+      const __half hi = __float2half_rn(xx);
+      a.op[0][(size_t)t * C + i] = hi;
+      if (a.op_lo[0]) a.op_lo[0][(size_t)t * C + i] = __float2half_rn(xx - __half2float(hi));
       continue;
     }
     float prev;
@@ -418,7 +465,9 @@ __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
     float pm = fmaxf(pp, ww);
     float e1 = expf(pp - pm), e2 = expf(ww - pm);
     const float wkv = (e1 * aa + e2 * v) / (e1 * bb + e2);
-    a.out[o] = __float2half_rn(r * wkv);
+    const __half oh = __float2half_rn(r * wkv);
+    a.out[o] = oh;
+    if (a.out_lo) a.out_lo[o] = __float2half_rn(r * wkv - __half2float(oh));
     ww = w + pp;
     pm = fmaxf(ww, k);
     e1 = expf(ww - pm);
@@ -584,7 +633,7 @@ __global__ void __launch_bounds__(256) wkv5_combine_kernel(SeqWkvArgs a) {
 // GroupNorm over each head's 64 readout values (eps 1e-5, fp32 affine), times the gate where the version has one
 // (att_seq.cu:406-415): one warp per (token, head)
 __global__ void __launch_bounds__(256) gn_gate_seq_kernel(const float *y, const float *lnx_w, const float *lnx_b, const __half *g,
-                                                          int T, int H, __half *out) {
+                                                          const __half *g_lo, int T, int H, __half *out, __half *out_lo) {
   const int unit = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (unit >= T * H) return;
   const int t = unit / H, h = unit - t * H;
@@ -602,10 +651,19 @@ __global__ void __launch_bounds__(256) gn_gate_seq_kernel(const float *y, const 
   const int c = h * 64 + lane * 2;
   float a0 = d0 * rstd * lnx_w[c] + lnx_b[c], a1 = d1 * rstd * lnx_w[c + 1] + lnx_b[c + 1];
   if (g) {
-    const float2 gg = __half22float2(*reinterpret_cast<const __half2 *>(g + o));
+    float2 gg = __half22float2(*reinterpret_cast<const __half2 *>(g + o));
+    if (g_lo) {
+      const float2 gl = __half22float2(*reinterpret_cast<const __half2 *>(g_lo + o));
+      gg.x += gl.x; gg.y += gl.y;
+    }
     a0 *= gg.x; a1 *= gg.y;
   }
-  *reinterpret_cast<__half2 *>(out + o) = __floats2half2_rn(a0, a1);
+  const __half2 hh = __floats2half2_rn(a0, a1);
+  *reinterpret_cast<__half2 *>(out + o) = hh;
+  if (out_lo) {
+    const float2 hf = __half22float2(hh);
+    *reinterpret_cast<__half2 *>(out_lo + o) = __floats2half2_rn(a0 - hf.x, a1 - hf.y);
+  }
 }
 
 // plain LayerNorm of one row -> fp32 vector (ln_out before the head, model_forward_seq.cpp:171-175)
@@ -648,9 +706,9 @@ cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int
   argmax_rows_kernel<<<rows, 256, 0, st>>>(logits, V, ld, out);
   return cudaGetLastError();
 }
-cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, int T, int H, __half *out,
-                               cudaStream_t st) {
-  gn_gate_seq_kernel<<<(T * H + 7) / 8, 256, 0, st>>>(y, lnx_w, lnx_b, g, T, H, out);
+cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
+                               int H, __half *out, __half *out_lo, cudaStream_t st) {
+  gn_gate_seq_kernel<<<(T * H + 7) / 8, 256, 0, st>>>(y, lnx_w, lnx_b, g, g_lo, T, H, out, out_lo);
   return cudaGetLastError();
 }
 cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st) {
@@ -672,13 +730,18 @@ cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t
       return cudaErrorInvalidValue;
     if (!make_map(&maps.a[i], g.A, g.M, g.K, GBM) || !make_map(&maps.b[i], g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
     if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, GBM)) return cudaErrorNotSupported;
+    if (!make_map(&maps.b2[i], g.Bt2 ? g.Bt2 : g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
     grp.p[i] = g;
     grp.tile_start[i] = tiles;
     tiles += (g.N + GBN - 1) / GBN;
   }
-  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; }
+  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; maps.b2[i] = maps.b2[0]; }
   grp.tile_start[n] = tiles;
-  const size_t smem = 1024 + (mt == 1 ? 4 * (size_t)(G_A_BYTES + G_B_BYTES) : 3 * (size_t)(2 * G_A_BYTES + G_B_BYTES)) + 1024;
+  if (mt == 1)
+    for (int i = 0; i < n; ++i) grp.dual |= probs[i].A2 != nullptr;
+  grp.stage_bytes = (uint32_t)(grp.dual ? 2 : 1) * mt * G_A_BYTES + G_B_BYTES;
+  grp.stages = (int)std::min<size_t>(4, (192u << 10) / grp.stage_bytes);
+  const size_t smem = 1024 + (size_t)grp.stages * grp.stage_bytes + 1024;
   dim3 grid(tiles, (probs[0].M + mt * GBM - 1) / (mt * GBM));
   cudaError_t e;
   if (mt == 1) {

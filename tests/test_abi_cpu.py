@@ -36,8 +36,8 @@ def test_strerror_and_argument_errors(pkg):
     assert L.fr_b200_create(ctypes.byref(bad), ctypes.byref(h)) == -2      # unknown version
     bad = pkg.Config(4, 1, 100, 64, 0, 10, 0, 1, 1, 0)
     assert L.fr_b200_create(ctypes.byref(bad), ctypes.byref(h)) == -2      # n_embd not a multiple of 64
-    bad = pkg.Config(4, 1, 64, 64, 0, 10, 0, 1, 9, 0)
-    assert L.fr_b200_create(ctypes.byref(bad), ctypes.byref(h)) == -2      # batch > 8
+    bad = pkg.Config(4, 1, 64, 64, 0, 10, 0, 1, 5000, 0)
+    assert L.fr_b200_create(ctypes.byref(bad), ctypes.byref(h)) == -2      # more than 4096 stream slots
     assert b"max_batch" in L.fr_b200_last_error()
 
 
