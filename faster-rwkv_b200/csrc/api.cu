@@ -77,6 +77,12 @@ struct fr_b200_model {
   __half *d_pscale = nullptr;    size_t pscale_halfs = 0;  // int8: per output row scales, per matrix
   uint8_t *d_seq = nullptr;      size_t seq_bytes = 0; int seq_T = 0;
   PhaseDev *d_head_phase = nullptr;   // the head as a stand-alone matvec phase
+  // greedy runs of many streams: two decode steps captured as a CUDA graph and replayed (the step is ~170 launches)
+  GreedyCtl *d_ctl = nullptr;
+  cudaStream_t gstream = nullptr;
+  cudaEvent_t gev = nullptr;
+  cudaGraphExec_t gexec = nullptr;
+  int g_batch = 0; unsigned g_par = 0; const void *g_seq = nullptr;   // what the captured graph was built for
   float *d_lnvec = nullptr;           // ln_out of the last prompt token
   // scratch for uploads
   void *d_scratch[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -385,6 +391,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc && m->plain_halfs && m->fmt == FMT_INT4) rc = alloc((void **)&m->d_plain2, m->plain_halfs * 2);
   if (!rc && m->pscale_halfs) rc = alloc((void **)&m->d_pscale, m->pscale_halfs * 2);
   if (!rc) rc = alloc((void **)&m->d_head_phase, sizeof(PhaseDev));
+  if (!rc) rc = alloc((void **)&m->d_ctl, sizeof(GreedyCtl));
   if (!rc) rc = alloc((void **)&m->d_lnvec, (size_t)m->C * 4);
   if (!rc) rc = alloc((void **)&m->d_layers, sizeof(LayerDev) * m->L);
   if (!rc) rc = alloc((void **)&m->d_phases, sizeof(PhaseDev) * m->phases.size());
@@ -409,6 +416,10 @@ void fr_b200_destroy(fr_b200_model *m) {
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);
+  if (m->gexec) cudaGraphExecDestroy(m->gexec);
+  if (m->gev) cudaEventDestroy(m->gev);
+  if (m->gstream) cudaStreamDestroy(m->gstream);
+  if (m->d_ctl) cudaFree(m->d_ctl);
   if (m->d_hist) cudaFree(m->d_hist);
   delete m;
 }
@@ -622,7 +633,7 @@ int fr_b200_decode(fr_b200_model *m, const int32_t *ids, int batch, float *logit
     if ((rc = rows_decode_check(m, ids, batch))) return rc;
     if ((rc = rows_forward(m, true, 0, ids, batch, st))) return rc;
     if (argmax) {
-      CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), st));
+      CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), nullptr, st));
       m->launches++;
     }
   } else {
@@ -675,10 +686,56 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
     int rc = rows_decode_check(m, first_ids, batch);
     if (rc) return rc;
     int32_t *hist32 = reinterpret_cast<int32_t *>(m->d_hist + need);
-    for (int t = 0; t < n_tokens; ++t) {
-      if ((rc = rows_forward(m, true, 0, t == 0 ? first_ids : hist32 + (size_t)(t - 1) * batch, batch, st))) return rc;
-      CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, hist32 + (size_t)t * batch, st));
-      m->launches++;
+    GreedyCtl ctl;
+    ctl.hist = hist32; ctl.step = 0;
+    CU(cudaMemcpyAsync(m->d_ctl, &ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
+    // step 0 from the host ids; every sampled id goes to the row-id buffer of the next step and to the history
+    if ((rc = rows_forward(m, true, 0, first_ids, batch, st))) return rc;
+    int32_t *row_ids = reinterpret_cast<int32_t *>(m->d_seq);   // first piece of the activation blob
+    CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, row_ids, m->d_ctl, st));
+    m->launches += 2;
+    int left = n_tokens - 1;
+    bool graphs = left >= 4;
+    if (const char *e = getenv("FR_B200_GRAPH")) graphs = graphs && atoi(e) != 0;
+    if (graphs) {
+      // two steps (the shift-state copies alternate) as one graph on an internal stream: capture is not allowed on the
+      // legacy default stream, which is what most callers pass
+      if (!m->gstream) {
+        CU(cudaStreamCreateWithFlags(&m->gstream, cudaStreamNonBlocking));
+        CU(cudaEventCreateWithFlags(&m->gev, cudaEventDisableTiming));
+      }
+      if (!m->gexec || m->g_batch != batch || m->g_par != m->par[0] || m->g_seq != m->d_seq) {
+        if (m->gexec) { cudaGraphExecDestroy(m->gexec); m->gexec = nullptr; }
+        const long long l0 = m->launches;
+        cudaGraph_t graph = nullptr;
+        bool ok = cudaStreamBeginCapture(m->gstream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        for (int i = 0; i < 2 && ok; ++i) {
+          ok = rows_forward(m, true, 0, row_ids, batch, m->gstream) == 0 &&
+               launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, row_ids, m->d_ctl, m->gstream) == cudaSuccess;
+        }
+        cudaError_t ce = cudaStreamEndCapture(m->gstream, &graph);
+        ok = ok && ce == cudaSuccess && graph && cudaGraphInstantiate(&m->gexec, graph, 0) == cudaSuccess;
+        if (graph) cudaGraphDestroy(graph);
+        m->launches = l0;
+        if (!ok) { cudaGetLastError(); m->gexec = nullptr; graphs = false; }
+        else { m->g_batch = batch; m->g_par = m->par[0]; m->g_seq = m->d_seq; }
+      }
+    }
+    if (graphs && m->gexec) {
+      const long long per_step = (m->v5 ? 9 : 7) * (long long)m->L + 4;
+      CU(cudaEventRecord(m->gev, st));
+      CU(cudaStreamWaitEvent(m->gstream, m->gev, 0));
+      for (; left >= 2; left -= 2) {
+        CU(cudaGraphLaunch(m->gexec, m->gstream));
+        m->launches += 2 * per_step;
+      }
+      CU(cudaEventRecord(m->gev, m->gstream));
+      CU(cudaStreamWaitEvent(st, m->gev, 0));
+    }
+    for (; left > 0; --left) {
+      if ((rc = rows_forward(m, true, 0, row_ids, batch, st))) return rc;
+      CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, row_ids, m->d_ctl, st));
+      m->launches += 2;
     }
     CU(cudaMemcpyAsync(out_ids, hist32, need * 4, cudaMemcpyDefault, st));
     if (is_host_ptr(out_ids)) {
@@ -782,7 +839,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   __half *lo2 = batch_mode ? (__half *)(B + o_lo2) : nullptr, *lo3 = batch_mode ? (__half *)(B + o_lo3) : nullptr;
   __half *yn_lo = batch_mode ? (__half *)(B + o_ynlo) : nullptr, *kk_lo = batch_mode ? (__half *)(B + o_kklo) : nullptr;
   __half *g_lo = batch_mode ? (__half *)(B + o_glo) : nullptr, *rr_lo = g_lo;   // like rr reuses g
-  CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
+  if (ids != d_ids) CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
   CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
   auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
   auto wt = [&](const std::string &n) -> const __half * { return m->d_plain + m->mats[n].plain_off; };

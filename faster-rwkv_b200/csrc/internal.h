@@ -172,7 +172,11 @@ cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st);
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
                                int H, __half *out, __half *out_lo, cudaStream_t st);
 cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st);
-cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, cudaStream_t st);
+struct GreedyCtl {           // device-side cursor of a greedy run through the GEMM path
+  int32_t *hist;             // [n_tokens][rows] sampled ids
+  int step;                  // next row of hist
+};
+cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, GreedyCtl *ctl, cudaStream_t st);
 cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st);
 cudaError_t launch_transpose_f16(const __half *src, int K, int N, __half *dst, cudaStream_t st);   // [K,N] -> [N,K]
 

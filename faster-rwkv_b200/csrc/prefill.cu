@@ -479,8 +479,9 @@ __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
   st[c] = aa; st[a.C + c] = bb; st[2 * a.C + c] = pp;
 }
 
-// greedy sample of every row: index of the largest logit (lowest index on ties)
-__global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, int V, int ld, int32_t *out) {
+// greedy sample of every row: index of the largest logit (lowest index on ties).  ctl (optional): the id also goes
+// to row ctl->step of the history ctl->hist -- fixed kernel arguments, so that a captured graph can be replayed.
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, int V, int ld, int32_t *out, const GreedyCtl *ctl) {
   __shared__ unsigned long long best[8];
   const float *row = logits + (size_t)blockIdx.x * ld;
   unsigned long long m = 0;
@@ -499,9 +500,13 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, i
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int w8 = 1; w8 < 8; ++w8) m = best[w8] > m ? best[w8] : m;
-    out[blockIdx.x] = (int32_t)(0xffffffffu - (unsigned)m);
+    const int32_t id = (int32_t)(0xffffffffu - (unsigned)m);
+    out[blockIdx.x] = id;
+    if (ctl) ctl->hist[(size_t)ctl->step * gridDim.x + blockIdx.x] = id;
   }
 }
+__global__ void greedy_bump_kernel(GreedyCtl *ctl) { ctl->step += 1; }
+
 
 // RWKV-5 state scan over the tokens of one head (rwkv5_2_kernel_forward, att_seq.cu:258-322; per-head decay for 5.0):
 //   y[t, j] = sum_i r[t,i] * (u_i * k[t,i] * v[t,j] + s[i,j]);   s[i,j] = w_i * s[i,j] + k[t,i] * v[t,j]
@@ -702,8 +707,9 @@ cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st) {
   wkv4_rows_kernel<<<grid, 256, 0, st>>>(a);
   return cudaGetLastError();
 }
-cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, cudaStream_t st) {
-  argmax_rows_kernel<<<rows, 256, 0, st>>>(logits, V, ld, out);
+cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, GreedyCtl *ctl, cudaStream_t st) {
+  argmax_rows_kernel<<<rows, 256, 0, st>>>(logits, V, ld, out, ctl);
+  if (ctl) greedy_bump_kernel<<<1, 1, 0, st>>>(ctl);
   return cudaGetLastError();
 }
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
