@@ -717,7 +717,10 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
         ok = ok && ce == cudaSuccess && graph && cudaGraphInstantiate(&m->gexec, graph, 0) == cudaSuccess;
         if (graph) cudaGraphDestroy(graph);
         m->launches = l0;
-        if (!ok) { cudaGetLastError(); m->gexec = nullptr; graphs = false; }
+        if (!ok) {
+          if (getenv("FR_B200_DEBUG")) fprintf(stderr, "fr_b200: graph capture failed (%s): running the steps one by one\n", cudaGetErrorString(ce));
+          cudaGetLastError(); m->gexec = nullptr; graphs = false;
+        }
         else { m->g_batch = batch; m->g_par = m->par[0]; m->g_seq = m->d_seq; }
       }
     }
@@ -812,7 +815,8 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
                o_y = take(TC * 4), o_op0 = take(TC * 2), o_op1 = take(TC * 2), o_op2 = take(TC * 2), o_op3 = take(TC * 2),
                o_g = take(TC * 2), o_yn = take(TC * 2), o_kk = take(TF * 2), o_lo0 = take(TC * 2), o_lo1 = take(TC * 2),
                o_lo2 = take(batch_mode ? TC * 2 : 0), o_lo3 = take(batch_mode ? TC * 2 : 0), o_ynlo = take(batch_mode ? TC * 2 : 0),
-               o_kklo = take(batch_mode ? TF * 2 : 0), o_glo = take(batch_mode ? TC * 2 : 0);
+               o_kklo = take(batch_mode ? TF * 2 : 0), o_glo = take(batch_mode ? TC * 2 : 0),
+               o_raw = take(T <= GEMM_SMALL_M ? (size_t)GEMM_SPLIT_MAX * T * std::max(4 * C, F + C) * 4 : 0);   // split-K slabs
   // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
   int n_chunks = 1, chunk_len = T;
   if (!batch_mode && m->v5) {
@@ -854,6 +858,12 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     return ga;
   };
   const int mt = T > 128 ? 2 : 1;   // 256-row tiles once the rows fill them
+  // few rows: every GEMM of a launch gets its own run of split-K slabs
+  auto give_raw = [&](GemmArgs *grp, int n) {
+    if (T > GEMM_SMALL_M) return;
+    float *p = (float *)(B + o_raw);
+    for (int i = 0; i < n; ++i) { grp[i].raw = p; p += (size_t)GEMM_SPLIT_MAX * T * grp[i].N; }
+  };
   const int par = (int)m->par[batch_mode ? 0 : slot];
   const int nvec = m->v5 ? (m->gate ? 4 : 3) : 3;
   uint8_t *st0 = m->d_state + (batch_mode ? 0 : (size_t)slot * m->state_stride);
@@ -881,6 +891,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
                          mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2),
                          mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2)};
       if (m->gate) { grp[3] = mk(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f, lo3); grp[3].out_lo = g_lo; }
+      give_raw(grp, m->gate ? 4 : 3);
       CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st));
     }
     if (m->v5) {
@@ -901,7 +912,8 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       CU(launch_wkv4_rows(wa, st));
     }
     {
-      const GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
+      GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
+      give_raw(&go, 1);
       CU(launch_gemm_group(&go, 1, 1, st));   // few tiles: 128-row tiles fill the SMs better (measured)
     }
     // ---- channel mix ----
@@ -919,9 +931,11 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       GemmArgs grp[2] = {mk(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f, batch_mode ? lo0 : nullptr),
                          mk(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f, batch_mode ? lo1 : nullptr)};
       grp[0].out_lo = kk_lo; grp[1].out_lo = rr_lo;
+      give_raw(grp, 2);
       CU(launch_gemm_group(grp, 2, mt, st));
       GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f, kk_lo);
       gv.aux1_lo = rr_lo;
+      give_raw(&gv, 1);
       CU(launch_gemm_group(&gv, 1, 1, st));
     }
     m->launches += m->v5 ? 9 : 7;
@@ -935,6 +949,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     CU(launch_ln_mix_seq(la, st));
     GemmArgs gh = mk(op[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f, lo0);
     gh.ldo = m->Vpad;
+    // (no split-K scratch for the head: it has a thousand column tiles of its own)
     CU(launch_gemm_group(&gh, 1, mt, st));
     m->launches += 2;
     for (int bq = 0; bq < R; ++bq) m->par[bq] ^= 1u;

@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -27,9 +28,9 @@ namespace {
 // One CTA per 128 x 256 output tile; K is walked in 64-wide slices through a 4-deep TMA ring.
 //   warp 0 (one lane): TMA producer          warp 1 (one lane): MMA issue; the warp owns the TMEM allocation
 //   warps 2..5: epilogue, one TMEM lane quadrant (32 rows) each
-constexpr int GBM = 128, GBN = 256, GBK = 64;
+constexpr int GBM = 128, GBK = 64;
 constexpr int G_THREADS = 192;
-constexpr uint32_t G_A_BYTES = GBM * GBK * 2, G_B_BYTES = GBN * GBK * 2;
+constexpr uint32_t G_A_BYTES = GBM * GBK * 2;
 constexpr int ST_GEMM_TIMEOUT = 201;
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -45,7 +46,7 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
 }
 // instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A = B = f16 (0), both K-major (0), N / 8 in bits 17-22,
 // M / 16 in bits 24-28
-constexpr uint32_t G_IDESC = (1u << 4) | ((uint32_t)(GBN >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
+// (built per tile width inside the kernel)
 
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -173,6 +174,7 @@ struct GemmGroup {
   int n;
   int stages;                           // ring depth (2..4)
   uint32_t stage_bytes;                 // bytes per ring slot: [A hi tiles][A lo tiles, if any problem has them][B tile]
+  int split;                            // split-K factor (grid.z); > 1: CTAs write raw partial sums to GemmArgs::raw
   int dual;                             // 1: the slot has room for the low halves of A (128-row tiles);
                                         // 0: low halves of A, if any, are a further pass over K (256-row tiles: a
                                         //    slot with both would leave a 2-deep ring)
@@ -183,15 +185,21 @@ struct alignas(64) GemmMaps {
   CUtensorMap a[GEMM_GROUP_MAX], a2[GEMM_GROUP_MAX], b[GEMM_GROUP_MAX], b2[GEMM_GROUP_MAX];
 };
 
-// MT = 128-row sub-tiles per CTA (1: 128 x 256 output tile, 4-deep ring; 2: 256 x 256, two accumulators sharing
-// every B tile, 3-deep ring -- half again as many flops per byte fetched from L2)
-template <int MT>
+// MT = 128-row sub-tiles per CTA (1: 128 x BN output tile; 2: 256 x BN, two accumulators sharing every B tile --
+// half again as many flops per byte fetched from L2).  BN = 256 for prompts; BN = 64 with split-K (grid.z) when
+// there are only a few hundred rows (batched decode): the step is bound by streaming the weights, so the number of
+// CTAs that each stream a distinct slice is what counts; the partial sums go to per-split slabs that
+// gemm_finish_kernel adds up in a fixed order before the epilogue.
+template <int MT, int BN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
+  constexpr int GBN = BN;
+  constexpr uint32_t G_B_BYTES = BN * GBK * 2;
+  constexpr uint32_t G_IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
   const int STAGES = grp.stages;
   const uint32_t STAGE_BYTES = grp.stage_bytes;
   const uint32_t B_OFF = (uint32_t)(grp.dual ? 2 : 1) * MT * G_A_BYTES;   // the B tile follows the A tiles
-  constexpr uint32_t TMEM_COLS = MT * GBN;
+  constexpr uint32_t TMEM_COLS = MT * GBN < 32 ? 32 : MT * GBN;
   extern __shared__ uint8_t gsm_raw[];
   // barriers in the first KB, tiles from the next 1024-byte boundary
   uint8_t *gsm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
@@ -210,7 +218,9 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
   // the low halves of A (A2) ride in the same ring slot as the high halves and meet the same B tile; the low
   // halves of B (Bt2) are a second pass over K into the same accumulator
   const bool has_lo = g.A2 != nullptr && grp.dual, lo_pass = g.A2 != nullptr && !grp.dual;
-  const int num_k = num_k1 * (1 + (lo_pass ? 1 : 0) + (g.Bt2 ? 1 : 0));
+  // split-K: this CTA covers K slices [kz0, kz0 + nkz) of every pass
+  const int kz0 = (int)((long long)blockIdx.z * num_k1 / grp.split), nkz = (int)((long long)(blockIdx.z + 1) * num_k1 / grp.split) - kz0;
+  const int num_k = nkz * (1 + (lo_pass ? 1 : 0) + (g.Bt2 ? 1 : 0));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -233,7 +243,7 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         const int s = kb % STAGES;
         const uint32_t parity = ((kb / STAGES) & 1) ^ 1;   // a fresh barrier reads as "previous phase complete"
         if (!mbar_wait(&empty[s], parity, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
-        const int pass = kb / num_k1, kk = kb - pass * num_k1;
+        const int pass = kb / nkz, kk = kz0 + kb - pass * nkz;
         const bool lo_now = has_lo && pass == 0;   // the (lo A) x (lo B) term is below fp32 resolution: skipped
         const bool a_is_lo = lo_pass && pass == 1, b_is_lo = pass > 0 && !a_is_lo;
         mbar_expect_tx(&full[s], (uint32_t)(lo_now ? 2 : 1) * MT * G_A_BYTES + G_B_BYTES);
@@ -254,7 +264,7 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         tc_fence_after();
         const uint32_t a_addr = tiles + (uint32_t)s * STAGE_BYTES;
         const uint64_t bd = umma_desc_k128(a_addr + B_OFF);
-        const bool lo_now = has_lo && kb < num_k1;
+        const bool lo_now = has_lo && kb < nkz;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const uint64_t ad = umma_desc_k128(a_addr + (uint32_t)mt * G_A_BYTES);
@@ -286,6 +296,22 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
           if (tile_n * GBN + c0 >= g.N) break;   // warp-uniform
           uint32_t acc[32];
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * GBN + c0), acc);
+          if (grp.split > 1) {
+            // raw partial sums of this K range: slab blockIdx.z of [split][M][N]
+            if (row < g.M) {
+              float *dst = g.raw + ((size_t)blockIdx.z * g.M + row) * g.N + tile_n * GBN + c0;
+              const int ncol = min(32, g.N - (tile_n * GBN + c0));
+              if (ncol == 32 && (g.N & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                  *reinterpret_cast<float4 *>(dst + i) = make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]),
+                                                                     __uint_as_float(acc[i + 2]), __uint_as_float(acc[i + 3]));
+              } else {
+                for (int i = 0; i < ncol; ++i) dst[i] = __uint_as_float(acc[i]);
+              }
+            }
+            continue;
+          }
           if (g.col_scale) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -303,6 +329,52 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// split-K: sum the slabs in a fixed order, then the same epilogue.  One thread per 4 consecutive columns of a row
+// (coalesced 16-byte reads of every slab); N is a multiple of 4 for every projection (the head never splits).
+__global__ void __launch_bounds__(256) gemm_finish_kernel(const GemmArgs g, int split) {
+  const int n4 = g.N >> 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= g.M * n4) return;
+  const int row = idx / n4, col = (idx - row * n4) * 4;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < split; ++z) {
+    const float4 p = *reinterpret_cast<const float4 *>(g.raw + ((size_t)z * g.M + row) * g.N + col);
+    v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+  }
+  if (g.col_scale) {
+    v.x *= __half2float(g.col_scale[col]); v.y *= __half2float(g.col_scale[col + 1]);
+    v.z *= __half2float(g.col_scale[col + 2]); v.w *= __half2float(g.col_scale[col + 3]);
+  }
+  const size_t o = (size_t)row * g.ldo + col;
+  float a[4] = {v.x, v.y, v.z, v.w};
+  if (g.epi == GEMM_EPI_F32) {
+    *reinterpret_cast<float4 *>(reinterpret_cast<float *>(g.out) + o) = v;
+  } else if (g.epi == GEMM_EPI_ADD_F32 || g.epi == GEMM_EPI_MULADD_F32) {
+    const float4 x = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(g.aux0) + o);
+    float r[4] = {1.f, 1.f, 1.f, 1.f};
+    if (g.epi == GEMM_EPI_MULADD_F32) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        r[i] = __half2float(reinterpret_cast<const __half *>(g.aux1)[o + i]);
+        if (g.aux1_lo) r[i] += __half2float(reinterpret_cast<const __half *>(g.aux1_lo)[o + i]);
+      }
+    }
+    *reinterpret_cast<float4 *>(reinterpret_cast<float *>(g.out) + o) =
+        make_float4((x.x + r[0] * a[0]) * g.scale, (x.y + r[1] * a[1]) * g.scale, (x.z + r[2] * a[2]) * g.scale,
+                    (x.w + r[3] * a[3]) * g.scale);
+  } else {
+    __half *out = reinterpret_cast<__half *>(g.out) + o;
+    __half *lo = g.out_lo ? reinterpret_cast<__half *>(g.out_lo) + o : nullptr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float e = epi_half_op(g.epi, a[i]);
+      const __half h = __float2half_rn(e);
+      out[i] = h;
+      if (lo) lo[i] = __float2half_rn(e - __half2float(h));
+    }
   }
 }
 
@@ -722,48 +794,73 @@ cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C,
   return cudaGetLastError();
 }
 
+namespace {
+template <int MT, int BN>
+cudaError_t launch_gemm_t(const GemmMaps &maps, const GemmGroup &grp, dim3 grid, size_t smem, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  gemm_f16_kernel<MT, BN><<<grid, G_THREADS, smem, st>>>(maps, grp);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st) {
   if (n < 1 || n > GEMM_GROUP_MAX || (mt != 1 && mt != 2)) return cudaErrorInvalidValue;
+  const int M = probs[0].M;
+  // few rows (batched decode): narrow N tiles and split-K, so that a few hundred CTAs stream the weights
+  const bool narrow = M <= GEMM_SMALL_M;
+  const int bn = narrow ? 64 : 256;
   GemmMaps maps;
   GemmGroup grp;
   memset(&grp, 0, sizeof(grp));
   grp.n = n;
-  int tiles = 0;
+  int tiles = 0, min_k1 = 1 << 30;
+  bool raw_ok = true;
   for (int i = 0; i < n; ++i) {
     const GemmArgs &g = probs[i];
-    if (g.K % GBK != 0 || g.M < 1 || g.N < 1 || g.M != probs[0].M) return cudaErrorInvalidValue;
+    if (g.K % GBK != 0 || g.M < 1 || g.N < 1 || g.M != M) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Bt) & 15) || (reinterpret_cast<uintptr_t>(g.A2) & 15))
       return cudaErrorInvalidValue;
-    if (!make_map(&maps.a[i], g.A, g.M, g.K, GBM) || !make_map(&maps.b[i], g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
+    if (!make_map(&maps.a[i], g.A, g.M, g.K, GBM) || !make_map(&maps.b[i], g.Bt, g.N, g.K, bn)) return cudaErrorNotSupported;
     if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, GBM)) return cudaErrorNotSupported;
-    if (!make_map(&maps.b2[i], g.Bt2 ? g.Bt2 : g.Bt, g.N, g.K, GBN)) return cudaErrorNotSupported;
+    if (!make_map(&maps.b2[i], g.Bt2 ? g.Bt2 : g.Bt, g.N, g.K, bn)) return cudaErrorNotSupported;
     grp.p[i] = g;
     grp.tile_start[i] = tiles;
-    tiles += (g.N + GBN - 1) / GBN;
+    tiles += (g.N + bn - 1) / bn;
+    min_k1 = std::min(min_k1, g.K / GBK);
+    raw_ok = raw_ok && g.raw != nullptr && (g.N & 3) == 0 && (g.ldo & 3) == 0;
   }
   for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; maps.b2[i] = maps.b2[0]; }
   grp.tile_start[n] = tiles;
+  const int m_tiles = (M + mt * GBM - 1) / (mt * GBM);
+  grp.split = 1;
+  if (narrow && raw_ok) {
+    const int want = (2 * 148 + tiles * m_tiles - 1) / (tiles * m_tiles);    // about two CTAs per SM in total
+    grp.split = std::max(1, std::min(std::min(want, GEMM_SPLIT_MAX), min_k1 / 4));   // at least 4 K slices per CTA
+  }
   if (mt == 1)
     for (int i = 0; i < n; ++i) grp.dual |= probs[i].A2 != nullptr;
-  grp.stage_bytes = (uint32_t)(grp.dual ? 2 : 1) * mt * G_A_BYTES + G_B_BYTES;
+  grp.stage_bytes = (uint32_t)(grp.dual ? 2 : 1) * mt * G_A_BYTES + (uint32_t)bn * GBK * 2;
   grp.stages = (int)std::min<size_t>(4, (192u << 10) / grp.stage_bytes);
-  const size_t smem = 1024 + (size_t)grp.stages * grp.stage_bytes + 1024;
-  dim3 grid(tiles, (probs[0].M + mt * GBM - 1) / (mt * GBM));
-  cudaError_t e;
-  if (mt == 1) {
-    e = cudaFuncSetAttribute(gemm_f16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    gemm_f16_kernel<1><<<grid, G_THREADS, smem, st>>>(maps, grp);
-  } else {
-    e = cudaFuncSetAttribute(gemm_f16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    gemm_f16_kernel<2><<<grid, G_THREADS, smem, st>>>(maps, grp);
+  if (narrow) {
+    if (const char *e = getenv("FR_B200_NARROW_STAGES")) grp.stages = std::max(2, std::min(grp.stages, atoi(e)));
   }
+  const size_t smem = 1024 + (size_t)grp.stages * grp.stage_bytes + 1024;
+  dim3 grid(tiles, m_tiles, grp.split);
+  cudaError_t e;
+  if (narrow) e = mt == 1 ? launch_gemm_t<1, 64>(maps, grp, grid, smem, st) : launch_gemm_t<2, 64>(maps, grp, grid, smem, st);
+  else e = mt == 1 ? launch_gemm_t<1, 256>(maps, grp, grid, smem, st) : launch_gemm_t<2, 256>(maps, grp, grid, smem, st);
+  if (e != cudaSuccess) return e;
+  if (grp.split > 1)
+    for (int i = 0; i < n; ++i) {
+      const int threads = M * (probs[i].N / 4);
+      gemm_finish_kernel<<<(threads + 255) / 256, 256, 0, st>>>(probs[i], grp.split);
+    }
   return cudaGetLastError();
 }
 
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st) {
-  return launch_gemm_group(&g, 1, g.M > GBM ? 2 : 1, st);
+  return launch_gemm_group(&g, 1, g.M > GBM ? 2 : 1, st);   // no raw scratch: no split-K
 }
 
 }  // namespace frb
