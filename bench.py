@@ -29,8 +29,8 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
 WORKLOADS = {  # name -> (shape key, description)
-    "c1": ("c1", "RWKV-4 1.5B-shaped (L24 C2048 F8192 V65536), batch-1 decode"),
-    "c0": ("c0", "RWKV-4 0.1B-shaped (L12 C768 F3072 V65536), batch-1 decode"),
+    "c1": ("c1", "RWKV-4 1.5B-shaped (L24 C2048 F8192 V65536), decode"),
+    "c0": ("c0", "RWKV-4 0.1B-shaped (L12 C768 F3072 V65536), decode"),
     "tiny": ("tiny4b", "tiny RWKV-4 (L7 C192 F448 V211)"),
 }
 FILE_DTYPE = {"fp16": "fp16", "int8": "fp32", "int4": "fp32"}
@@ -412,7 +412,9 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     achieved = algo * K / (ms_max * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": MEASURED_TRAFFIC.get((args.workload, args.weights, B)), "peak_source": peak_kind, "kernel": "decode_kernel (persistent, one launch per token)",
+                "traffic": MEASURED_TRAFFIC.get((args.workload, args.weights, B)), "peak_source": peak_kind,
+                "kernel": "decode_kernel (persistent, one launch per token)" if B <= 8 else
+                          "gemm_f16_kernel + row kernels (one row per stream; two steps replayed as a CUDA graph)",
                 "algorithmic_bytes_per_launch": algo}
 
     variants = {}
