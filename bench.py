@@ -31,6 +31,8 @@ import __graft_entry__ as entry  # noqa: E402
 WORKLOADS = {  # name -> (shape key, description)
     "c1": ("c1", "RWKV-4 1.5B-shaped (L24 C2048 F8192 V65536), decode"),
     "c0": ("c0", "RWKV-4 0.1B-shaped (L12 C768 F3072 V65536), decode"),
+    "c3": ("c3", "RWKV-5.2 3B-shaped (L32 C2560 F8960 H40 V65536), decode"),
+    "c4": ("c4", "RWKV-4 14B-shaped (L40 C5120 F20480 V50277), decode"),
     "tiny": ("tiny4b", "tiny RWKV-4 (L7 C192 F448 V211)"),
 }
 FILE_DTYPE = {"fp16": "fp16", "int8": "fp32", "int4": "fp32"}
