@@ -807,6 +807,7 @@ namespace {
 // ids: host or device.  The residual stream stays fp32 between the layers; GEMM inputs are fp16.
 int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids, int R, cudaStream_t st) {
   const int C = m->C, F = m->F, H = m->H, af = m->cfg.act_fp16, T = R;
+  if (C > 8192) return fail(FR_B200_E_UNSUPPORTED, "the row kernels of the GEMM path hold at most n_embd = 8192");
   const size_t TC = (size_t)T * C, TF = (size_t)T * F;
   // activation buffers: one blob, 256-byte aligned pieces
   size_t off = 0;
@@ -914,7 +915,8 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     {
       GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
       give_raw(&go, 1);
-      CU(launch_gemm_group(&go, 1, 1, st));   // few tiles: 128-row tiles fill the SMs better (measured)
+      // prompts: few tiles, 128-row tiles fill the SMs better (measured); streams: one pass over the weights for all rows
+      CU(launch_gemm_group(&go, 1, batch_mode ? mt : 1, st));
     }
     // ---- channel mix ----
     memset(&la, 0, sizeof(la));
@@ -936,7 +938,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f, kk_lo);
       gv.aux1_lo = rr_lo;
       give_raw(&gv, 1);
-      CU(launch_gemm_group(&gv, 1, 1, st));
+      CU(launch_gemm_group(&gv, 1, batch_mode ? mt : 1, st));
     }
     m->launches += m->v5 ? 9 : 7;
   }

@@ -480,41 +480,103 @@ __global__ void gather_emb_kernel(const void *emb, int emb_f32, const int32_t *i
 // row before it, so no CTA waits for another.
 // Batch mode (rows = independent streams, one token each): prev of row b is stream b's stored shift state and every
 // row writes its new one.  nvec == 0: plain LayerNorm into op[0] (ln_out before the head).
+// Each thread keeps its float4 pieces of the row (and of the row before) in registers: x is read once.
+constexpr int LN_MAX4 = 8;   // float4 per thread: n_embd <= 8192
+__device__ __forceinline__ float2 stats_from_regs(const float4 *v, int n4, float piv, int C, float *red) {
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < LN_MAX4; ++j) {
+    if ((int)threadIdx.x + j * 256 < n4) {
+      const float d0 = v[j].x - piv, d1 = v[j].y - piv, d2 = v[j].z - piv, d3 = v[j].w - piv;
+      s1 += (d0 + d1) + (d2 + d3);
+      s2 += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+  const float2 s = block_sum2(s1, s2, red);
+  const float m = s.x / (float)C;
+  float var = s.y / (float)C - m * m;
+  var = var > 0.f ? var : 0.f;
+  return make_float2(piv + m, rsqrtf(var + 1e-5f));
+}
+__device__ __forceinline__ void store_hl4(__half *hi, __half *lo, size_t o, const float4 &v) {
+  const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t *>(&h0); u.y = *reinterpret_cast<const uint32_t *>(&h1);
+  *reinterpret_cast<uint2 *>(hi + o) = u;
+  if (lo) {
+    const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+    const __half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+    u.x = *reinterpret_cast<const uint32_t *>(&l0); u.y = *reinterpret_cast<const uint32_t *>(&l1);
+    *reinterpret_cast<uint2 *>(lo + o) = u;
+  }
+}
+__device__ __forceinline__ float4 load_act_f4(const void *p, int i4, int act_fp16) {
+  if (act_fp16) {
+    const uint2 u = reinterpret_cast<const uint2 *>(p)[i4];
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  return reinterpret_cast<const float4 *>(p)[i4];
+}
+__device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }
+
 __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
   __shared__ float red[16];
-  const int t = blockIdx.x, C = a.C;
-  const float *xr = a.x + (size_t)t * C;
-  const float2 st = row_stats(xr, C, red);
-  const bool from_row = !a.batch_mode && t > 0;
+  const int t = blockIdx.x, C = a.C, n4 = C >> 2;
+  const float4 *xr = reinterpret_cast<const float4 *>(a.x + (size_t)t * C);
+  const bool from_row = !a.batch_mode && t > 0 && a.nvec > 0;
+  float4 xv[LN_MAX4], pv[LN_MAX4];
+#pragma unroll
+  for (int j = 0; j < LN_MAX4; ++j) {
+    const int i4 = threadIdx.x + j * 256;
+    if (i4 < n4) {
+      xv[j] = xr[i4];
+      if (from_row) pv[j] = xr[i4 - n4];
+    }
+  }
+  const float2 st = stats_from_regs(xv, n4, a.x[(size_t)t * C], C, red);
   float2 sp = make_float2(0.f, 0.f);
-  if (from_row && a.nvec > 0) sp = row_stats(xr - C, C, red);
+  if (from_row) sp = stats_from_regs(pv, n4, a.x[(size_t)(t - 1) * C], C, red);
   const uint8_t *srd = reinterpret_cast<const uint8_t *>(a.sx_rd) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
   uint8_t *swr = reinterpret_cast<uint8_t *>(a.sx_wr) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
-  for (int i = threadIdx.x; i < C; i += blockDim.x) {
-    const float w = a.ln_w[i], b = a.ln_b[i];
-    const float xx = (xr[i] - st.x) * st.y * w + b;
+#pragma unroll
+  for (int j = 0; j < LN_MAX4; ++j) {
+    const int i4 = threadIdx.x + j * 256;
+    if (i4 >= n4) continue;
+    const float4 w = reinterpret_cast<const float4 *>(a.ln_w)[i4], b = reinterpret_cast<const float4 *>(a.ln_b)[i4];
+    const float4 xx = make_float4((xv[j].x - st.x) * st.y * w.x + b.x, (xv[j].y - st.x) * st.y * w.y + b.y,
+                                  (xv[j].z - st.x) * st.y * w.z + b.z, (xv[j].w - st.x) * st.y * w.w + b.w);
+    const size_t o = (size_t)t * C + (size_t)i4 * 4;
     if (a.nvec == 0) {
-      const __half hi = __float2half_rn(xx);
-      a.op[0][(size_t)t * C + i] = hi;
-      if (a.op_lo[0]) a.op_lo[0][(size_t)t * C + i] = __float2half_rn(xx - __half2float(hi));
+      store_hl4(a.op[0], a.op_lo[0], o, xx);
       continue;
     }
-    float prev;
-    if (from_row) prev = (xr[i - C] - sp.x) * sp.y * w + b;
-    else prev = a.act_fp16 ? __half2float(reinterpret_cast<const __half *>(srd)[i]) : reinterpret_cast<const float *>(srd)[i];
-    if (a.act_fp16 && from_row) prev = __half2float(__float2half_rn(prev));   // what the token loop would have stored as shift state
+    float4 prev;
+    if (from_row) {
+      prev = make_float4((pv[j].x - sp.x) * sp.y * w.x + b.x, (pv[j].y - sp.x) * sp.y * w.y + b.y,
+                         (pv[j].z - sp.x) * sp.y * w.z + b.z, (pv[j].w - sp.x) * sp.y * w.w + b.w);
+      // what the token loop would have stored as shift state
+      if (a.act_fp16) prev = make_float4(round_h(prev.x), round_h(prev.y), round_h(prev.z), round_h(prev.w));
+    } else {
+      prev = load_act_f4(srd, i4, a.act_fp16);
+    }
 #pragma unroll
     for (int v = 0; v < 4; ++v)
       if (v < a.nvec) {
-        const float m = a.mix[v][i];
-        const float val = xx * m + prev * (1.f - m);
-        const __half hi = __float2half_rn(val);
-        a.op[v][(size_t)t * C + i] = hi;
-        if (a.op_lo[v]) a.op_lo[v][(size_t)t * C + i] = __float2half_rn(val - __half2float(hi));
+        const float4 m = reinterpret_cast<const float4 *>(a.mix[v])[i4];
+        store_hl4(a.op[v], a.op_lo[v], o,
+                  make_float4(xx.x * m.x + prev.x * (1.f - m.x), xx.y * m.y + prev.y * (1.f - m.y),
+                              xx.z * m.z + prev.z * (1.f - m.z), xx.w * m.w + prev.w * (1.f - m.w)));
       }
     if (a.batch_mode || t == a.T - 1) {
-      if (a.act_fp16) reinterpret_cast<__half *>(swr)[i] = __float2half_rn(xx);
-      else reinterpret_cast<float *>(swr)[i] = xx;
+      if (a.act_fp16) {
+        const __half2 h0 = __floats2half2_rn(xx.x, xx.y), h1 = __floats2half2_rn(xx.z, xx.w);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t *>(&h0); u.y = *reinterpret_cast<const uint32_t *>(&h1);
+        reinterpret_cast<uint2 *>(swr)[i4] = u;
+      } else {
+        reinterpret_cast<float4 *>(swr)[i4] = xx;
+      }
     }
   }
 }
