@@ -58,6 +58,7 @@ SIGNATURES = {
     "fr_b200_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "fr_b200_decode_greedy": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "fr_b200_logits_device": (_i, [_vp, ctypes.POINTER(_vp)]),
+    "fr_b200_sample": (_i, [_vp, _i, ctypes.c_float, _i, ctypes.c_float, _vp, _vp, _vp]),
     "fr_b200_vocab_padded": (_i, [_vp]),
     "fr_b200_run_seq": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "fr_b200_state_reset": (_i, [_vp, _i]),
@@ -196,6 +197,15 @@ class Model:
         out = np.empty((n_tokens, len(ids)), np.int32)
         check(lib().fr_b200_decode_greedy(self._h, _np_ptr(ids), len(ids), n_tokens, _np_ptr(out), None),
               "fr_b200_decode_greedy")
+        return out
+
+    def sample(self, batch: int, temperature: float, top_k: int, top_p: float, uniform) -> np.ndarray:
+        """Sampler::Sample (sampler.cpp:38-101) on the device over the logits of the last decode; uniform = the
+        draws in [0, 1], one per stream."""
+        u = np.ascontiguousarray(uniform, np.float32)
+        out = np.empty(batch, np.int32)
+        check(lib().fr_b200_sample(self._h, batch, temperature, top_k, top_p, _np_ptr(u), _np_ptr(out), None),
+              "fr_b200_sample")
         return out
 
     def decode_profile(self, ids: Sequence[int]) -> np.ndarray:

@@ -79,6 +79,7 @@ struct fr_b200_model {
   PhaseDev *d_head_phase = nullptr;   // the head as a stand-alone matvec phase
   // greedy runs of many streams: two decode steps captured as a CUDA graph and replayed (the step is ~170 launches)
   GreedyCtl *d_ctl = nullptr;
+  uint8_t *d_sample = nullptr; size_t sample_bytes = 0;   // scratch of fr_b200_sample
   cudaStream_t gstream = nullptr;
   cudaEvent_t gev = nullptr;
   cudaGraphExec_t gexec = nullptr;
@@ -420,6 +421,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   if (m->gev) cudaEventDestroy(m->gev);
   if (m->gstream) cudaStreamDestroy(m->gstream);
   if (m->d_ctl) cudaFree(m->d_ctl);
+  if (m->d_sample) cudaFree(m->d_sample);
   if (m->d_hist) cudaFree(m->d_hist);
   delete m;
 }
@@ -788,6 +790,33 @@ int fr_b200_decode_profile(fr_b200_model *m, const int32_t *ids, int batch, uint
   int status = 0;
   CU(cudaMemcpy(&status, m->out_status(), 4, cudaMemcpyDeviceToHost));
   return check_status(m, status);
+}
+
+int fr_b200_sample(fr_b200_model *m, int batch, float temperature, int top_k, float top_p, const float *uniform,
+                   int32_t *ids, void *stream) {
+  if (!m || !uniform || !ids) return fail(FR_B200_E_ARG, "null argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  if (batch < 1 || batch > m->cfg.max_batch) return fail(FR_B200_E_ARG, "batch must be 1..max_batch");
+  CU(cudaSetDevice(m->device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t need = sample_scratch_bytes(batch, m->V) + align256((size_t)batch * 4) * 2;
+  if (m->sample_bytes < need) {
+    CU(cudaStreamSynchronize(st));
+    if (m->d_sample) cudaFree(m->d_sample);
+    m->d_sample = nullptr; m->sample_bytes = 0;
+    CU(cudaMalloc((void **)&m->d_sample, need));
+    m->sample_bytes = need;
+  }
+  float *d_u = reinterpret_cast<float *>(m->d_sample);
+  int32_t *d_ids = reinterpret_cast<int32_t *>(m->d_sample + align256((size_t)batch * 4));
+  uint8_t *scratch = m->d_sample + 2 * align256((size_t)batch * 4);
+  CU(cudaMemcpyAsync(d_u, uniform, (size_t)batch * 4, cudaMemcpyDefault, st));
+  CU(launch_sample_rows(m->d_out, batch, m->V, m->Vpad, temperature, top_k, top_p, d_u, d_ids, scratch,
+                        need - 2 * align256((size_t)batch * 4), st));
+  m->launches += 4;
+  CU(cudaMemcpyAsync(ids, d_ids, (size_t)batch * 4, cudaMemcpyDefault, st));
+  if (is_host_ptr(ids)) CU(cudaStreamSynchronize(st));
+  return FR_B200_OK;
 }
 
 int fr_b200_logits_device(fr_b200_model *m, float **ptr) {

@@ -175,6 +175,10 @@ cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st);
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
                                int H, __half *out, __half *out_lo, cudaStream_t st);
 cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st);
+// device-side Sampler::Sample over the rows of a logits matrix (sample.cu)
+size_t sample_scratch_bytes(int rows, int V);
+cudaError_t launch_sample_rows(const float *logits, int rows, int V, int ld, float temperature, int top_k, float top_p,
+                               const float *u, int32_t *out, void *scratch, size_t scratch_bytes, cudaStream_t st);
 struct GreedyCtl {           // device-side cursor of a greedy run through the GEMM path
   int32_t *hist;             // [n_tokens][rows] sampled ids
   int step;                  // next row of hist

@@ -98,6 +98,14 @@ int fr_b200_decode(fr_b200_model *m, const int32_t *ids, int batch, float *logit
 int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch, int n_tokens, int32_t *out_ids,
                           void *stream);
 
+/* Sampler::Sample (sampler.cpp:38-101) on the device, over the logits the last decode of `batch` streams left there:
+ * softmax, descending sort, top_p prefix, top_k cut, probs^(1/temperature) with temperature clamped to [0.1, 5],
+ * inverse-CDF draw.  uniform: host [batch], the draw in [0, 1] of each stream -- the reference computes it as
+ * (g() - g.min()) / (g.max() - g.min()) from a std::minstd_rand0 (sampler.cpp:20-22); a host that does the same gets
+ * the reference's choice.  ids: host or device [batch].  No [V] logits cross to the host, no host sort. */
+int fr_b200_sample(fr_b200_model *m, int batch, float temperature, int top_k, float top_p, const float *uniform,
+                   int32_t *ids, void *stream);
+
 /* Device pointer of the [max_batch, vocab_padded] fp32 logits of the last decode (row stride =
  * fr_b200_vocab_padded()); valid until the next decode. */
 int fr_b200_logits_device(fr_b200_model *m, float **ptr);
