@@ -183,6 +183,36 @@ def prefill_leg(pkg, device_index: int, wl: str = "c3", T: int = 4096, reps: int
         m.close()
         del m
         torch.cuda.empty_cache()
+        # 16 streams: one prompt each (slot by slot: a 4096-token prompt already fills the tensor cores), then 64
+        # greedy steps of all 16 together through the GEMM path
+        try:
+            B = 16
+            m = build_model(pkg, shape, "fp16", B, device_index, seed=0)
+            prompts = [[int(t) for t in pkg.synth.token_ids(shape, T, seed=10 + b)] for b in range(B)]
+            m.run(prompts[0], slot=0)
+            m.reset_states()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            firsts = [int(np.argmax(m.run(prompts[b], slot=b))) for b in range(B)]
+            e1.record()
+            torch.cuda.synchronize()
+            ms16 = e0.elapsed_time(e1)
+            m.decode_greedy(firsts, 4)
+            torch.cuda.synchronize()
+            e0.record()
+            m.decode_greedy(firsts, 64)
+            e1.record()
+            torch.cuda.synchronize()
+            msd = e0.elapsed_time(e1)
+            out["batch16"] = {"prefill_ms": ms16, "prefill_tok_s": B * T / (ms16 * 1e-3),
+                              "prefill_tflops": B * flops / (ms16 * 1e-3) / 1e12,
+                              "decode_64_steps_ms_per_step": msd / 64, "decode_tok_s": B * 64 / (msd * 1e-3)}
+            m.close()
+            del m
+            torch.cuda.empty_cache()
+        except Exception as ex:
+            out["batch16"] = {"error": str(ex)[:200]}
         return out
     except Exception as ex:
         return {"error": str(ex)[:200]}

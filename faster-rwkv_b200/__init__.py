@@ -170,13 +170,14 @@ class Model:
         check(lib().fr_b200_set_tensor(self._h, name.encode(), ptr, dt, sh, len(shp)), f"fr_b200_set_tensor({name})")
 
     # -- forward -----------------------------------------------------------------------------
-    def run(self, ids: Union[int, Sequence[int]]) -> np.ndarray:
-        """Model::Run (model.cpp:188-208): one id, or a list processed in order; logits of the last token."""
+    def run(self, ids: Union[int, Sequence[int]], slot: int = 0) -> np.ndarray:
+        """Model::Run (model.cpp:188-208): one id, or a list processed in order; logits of the last token.
+        slot: the stream whose state the prompt advances (prompts on slots > 0 need the seq / GEMM path)."""
         if isinstance(ids, (int, np.integer)):
             ids = [int(ids)]
         ids = np.ascontiguousarray(ids, np.int32)
         out = np.empty(self.vocab, np.float32)
-        check(lib().fr_b200_run_seq(self._h, 0, _np_ptr(ids), len(ids), _np_ptr(out), None), "fr_b200_run_seq")
+        check(lib().fr_b200_run_seq(self._h, slot, _np_ptr(ids), len(ids), _np_ptr(out), None), "fr_b200_run_seq")
         return out
 
     def decode(self, ids: Sequence[int], want_logits: bool = True, want_argmax: bool = False):
