@@ -44,9 +44,15 @@ def test_reference_model_class_on_b200_backend(orc, synth, tmp_path, name, strat
         want = ref.run(int(t))
         assert np.abs(got[i] - want).max() < 1e-2
         assert np.linalg.norm(got[i] - want) / np.linalg.norm(want) < 1e-3
-    # Model::Run(vector) == the token loop (kernels/default/model_forward_seq.cpp:34-46)
+    # Model::Run(vector): RWKV-4 and quantised models run the token loop (kernels/default/model_forward_seq.cpp:34-46)
+    # and must repeat it bit for bit; RWKV-5.x fp16 prompts run the seq kernels (GEMM projections + chunked state
+    # scan), whose sums are ordered differently, so they are held to the same tolerance against the oracle.
     last = _run(DROPIN, fr, strategy, ids, str(tmp_path), seq=True)
-    assert np.array_equal(last, got[-1])
+    if shape.version.startswith("5") and fmt == "fp16":
+        assert np.abs(last - want).max() < 1e-2
+        assert np.linalg.norm(last - want) / np.linalg.norm(want) < 1e-3
+    else:
+        assert np.array_equal(last, got[-1])
 
 
 @pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built")
