@@ -20,6 +20,14 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 
 // ---- mbarrier -------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic stream-serialisation attribute may become
+// resident while its predecessor in the stream is still running; pdl_wait() returns once that predecessor has
+// completed and its writes are visible, so everything before it may only touch shared memory, TMEM and kernel
+// parameters.  pdl_trigger() lets the successor's CTAs be scheduled as soon as every CTA of this grid has called it.
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void mbar_init(uint64_t *b, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
 }

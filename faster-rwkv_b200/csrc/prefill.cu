@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
+#include <utility>
 
 #include "common.cuh"
 #include "internal.h"
@@ -20,6 +21,27 @@
 namespace frb {
 
 namespace {
+
+// Every kernel of the seq / batch chain goes through here.  With FR_B200_PDL != 0 (the default) the launch carries
+// the programmatic stream-serialisation attribute: the kernel's CTAs may be scheduled, and run their set-up, while the
+// kernel before it in the stream drains; each kernel calls pdl_wait() before it touches global memory, so the data
+// dependences are those of plain stream order.
+bool pdl_enabled() {
+  static const int on = [] { const char *v = getenv("FR_B200_PDL"); return !(v && v[0] == '0'); }();
+  return on != 0;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
 
 // ------------------------------------------------------------------------------------------------
 // tcgen05 GEMM: out[M, N] = epilogue((A + A2)[M, K] . (Bt + Bt2)[N, K]^T), fp16 operands (both K-major), fp32
@@ -236,6 +258,8 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();   // operands and epilogue inputs come from the kernels before this one
 
   if (warp == 0) {
     if (lane == 0) {
@@ -332,9 +356,161 @@ gemm_f16_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Few rows (batched decode: one row per stream, or a short prompt): the same product with the operands' roles
+// swapped, out^T[N, M] = W^T[N, K] . X[M, K]^T.  The 128 MMA rows are 128 output channels of the weight matrix, the
+// MMA columns are the BN rows of X (32 .. 256), so a ring slot is 16 KB of weights plus a small X tile instead of a
+// 128-row X tile that is mostly zero fill plus 8 KB of weights: several times the weight bytes in flight per SM,
+// which is what a step that streams every weight once is bound by.  The low halves of X (A2) and of the weights
+// (Bt2) sit in the same slot and multiply into the same accumulator; (lo W) x (lo X) is below fp32 resolution.
+// The accumulator holds out^T: TMEM lane = output channel, column = row of X; the epilogue warps write with the
+// lanes along the channels (coalesced), either the finished values or the split-K slabs gemm_finish_kernel sums.
+constexpr int WT_MAX_STAGES = 8;
+
+__device__ __forceinline__ void epi_store_one(const GemmArgs &g, int row, int col, float a) {
+  const size_t o = (size_t)row * g.ldo + col;
+  if (g.epi == GEMM_EPI_F32) {
+    reinterpret_cast<float *>(g.out)[o] = a;
+  } else if (g.epi == GEMM_EPI_ADD_F32) {
+    reinterpret_cast<float *>(g.out)[o] = (reinterpret_cast<const float *>(g.aux0)[o] + a) * g.scale;
+  } else if (g.epi == GEMM_EPI_MULADD_F32) {
+    float r = __half2float(reinterpret_cast<const __half *>(g.aux1)[o]);
+    if (g.aux1_lo) r += __half2float(reinterpret_cast<const __half *>(g.aux1_lo)[o]);
+    reinterpret_cast<float *>(g.out)[o] = (reinterpret_cast<const float *>(g.aux0)[o] + r * a) * g.scale;
+  } else {
+    const float e = epi_half_op(g.epi, a);
+    const __half h = __float2half_rn(e);
+    reinterpret_cast<__half *>(g.out)[o] = h;
+    if (g.out_lo) reinterpret_cast<__half *>(g.out_lo)[o] = __float2half_rn(e - __half2float(h));
+  }
+}
+
+// grp.dual here: bit 0 = some problem has A2 (slot holds an X lo tile), bit 1 = some problem has Bt2 (W lo tile)
+template <int BN>
+__global__ void __launch_bounds__(G_THREADS, 2)
+gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
+  constexpr uint32_t X_BYTES = BN * GBK * 2;
+  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  const int STAGES = grp.stages;
+  const uint32_t STAGE_BYTES = grp.stage_bytes;
+  const uint32_t X_OFF = ((grp.dual & 2) ? 2u : 1u) * G_A_BYTES, XLO_OFF = X_OFF + X_BYTES;
+  extern __shared__ uint8_t gsm_raw[];
+  uint8_t *gsm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *full = reinterpret_cast<uint64_t *>(gsm);
+  uint64_t *empty = full + WT_MAX_STAGES;
+  uint64_t *acc_full = empty + WT_MAX_STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t tiles = smem_u32(gsm + 1024);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int pi = 0;
+  while (pi + 1 < grp.n && (int)blockIdx.x >= grp.tile_start[pi + 1]) ++pi;
+  const GemmArgs &g = grp.p[pi];
+  const int tile_n = blockIdx.x - grp.tile_start[pi], m0 = blockIdx.y * BN;
+  const int num_k1 = g.K / GBK;
+  const int kz0 = (int)((long long)blockIdx.z * num_k1 / grp.split), nkz = (int)((long long)(blockIdx.z + 1) * num_k1 / grp.split) - kz0;
+  const bool x_lo = g.A2 != nullptr, w_lo = g.Bt2 != nullptr;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();   // operands and epilogue inputs come from the kernels before this one
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkz; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        mbar_expect_tx(&full[s], (w_lo ? 2u : 1u) * G_A_BYTES + (x_lo ? 2u : 1u) * X_BYTES);
+        const uint32_t dst = tiles + (uint32_t)s * STAGE_BYTES;
+        const int kx = (kz0 + kb) * GBK;
+        tma_load_2d(dst, &maps.b[pi], kx, tile_n * GBM, &full[s]);
+        if (w_lo) tma_load_2d(dst + G_A_BYTES, &maps.b2[pi], kx, tile_n * GBM, &full[s]);
+        tma_load_2d(dst + X_OFF, &maps.a[pi], kx, m0, &full[s]);
+        if (x_lo) tma_load_2d(dst + XLO_OFF, &maps.a2[pi], kx, m0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkz; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        tc_fence_after();
+        const uint32_t base = tiles + (uint32_t)s * STAGE_BYTES;
+        const uint64_t wd = umma_desc_k128(base), xd = umma_desc_k128(base + X_OFF);
+#pragma unroll
+        for (int k4 = 0; k4 < GBK / 16; ++k4)
+          umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, (kb | k4) != 0);
+        if (x_lo) {
+          const uint64_t xl = umma_desc_k128(base + XLO_OFF);
+#pragma unroll
+          for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xl + (uint64_t)(k4 * 2), IDESC, 1u);
+        }
+        if (w_lo) {
+          const uint64_t wl = umma_desc_k128(base + G_A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wl + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, 1u);
+        }
+        umma_commit(&empty[s]);
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int ch = tile_n * GBM + quad * 32 + lane;
+    const bool ok = mbar_wait(acc_full, 0, abort_flag, g.status, ST_GEMM_TIMEOUT);
+    tc_fence_after();
+    if (ok) {
+      const float sc = (g.col_scale && ch < g.N && grp.split == 1) ? __half2float(g.col_scale[ch]) : 1.f;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (m0 + c0 >= g.M) break;   // warp-uniform
+        uint32_t acc[32];
+        __syncwarp();
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
+        if (ch < g.N) {
+          if (grp.split > 1) {
+            float *dst = g.raw + ((size_t)blockIdx.z * g.M + m0 + c0) * g.N + ch;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m0 + c0 + i < g.M) dst[(size_t)i * g.N] = __uint_as_float(acc[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m0 + c0 + i < g.M) epi_store_one(g, m0 + c0 + i, ch, __uint_as_float(acc[i]) * sc);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // split-K: sum the slabs in a fixed order, then the same epilogue.  One thread per 4 consecutive columns of a row
 // (coalesced 16-byte reads of every slab); N is a multiple of 4 for every projection (the head never splits).
-__global__ void __launch_bounds__(256) gemm_finish_kernel(const GemmArgs g, int split) {
+// blockIdx.y picks the problem of the group (grid.x covers the largest one).
+__global__ void __launch_bounds__(256) gemm_finish_kernel(const __grid_constant__ GemmGroup grp) {
+  pdl_trigger();
+  pdl_wait();
+  const GemmArgs &g = grp.p[blockIdx.y];
+  const int split = grp.split;
   const int n4 = g.N >> 2;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= g.M * n4) return;
@@ -467,6 +643,8 @@ __device__ __forceinline__ float2 row_stats(const float *x, int C, float *red) {
 
 // x[t, :] = embedding row of ids[t]
 __global__ void gather_emb_kernel(const void *emb, int emb_f32, const int32_t *ids, int C, float *x) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const size_t row = (size_t)ids[t] * C;
   for (int i = threadIdx.x; i < C; i += blockDim.x)
@@ -521,6 +699,8 @@ __device__ __forceinline__ float4 load_act_f4(const void *p, int i4, int act_fp1
 __device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }
 
 __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[16];
   const int t = blockIdx.x, C = a.C, n4 = C >> 2;
   const float4 *xr = reinterpret_cast<const float4 *>(a.x + (size_t)t * C);
@@ -585,6 +765,8 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
 // (stream, channel).  Seq mode: one stream, T rows in order; batch mode: row b is the one token of stream b.
 //   out[row, c] = sigmoid(r) * wkv (fp16, the operand of the output projection); aa, bb, pp updated in place.
 __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
+  pdl_trigger();
+  pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (c >= a.C) return;
@@ -616,6 +798,8 @@ __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
 // greedy sample of every row: index of the largest logit (lowest index on ties).  ctl (optional): the id also goes
 // to row ctl->step of the history ctl->hist -- fixed kernel arguments, so that a captured graph can be replayed.
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, int V, int ld, int32_t *out, const GreedyCtl *ctl) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ unsigned long long best[8];
   const float *row = logits + (size_t)blockIdx.x * ld;
   unsigned long long m = 0;
@@ -639,7 +823,7 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, i
     if (ctl) ctl->hist[(size_t)ctl->step * gridDim.x + blockIdx.x] = id;
   }
 }
-__global__ void greedy_bump_kernel(GreedyCtl *ctl) { ctl->step += 1; }
+__global__ void greedy_bump_kernel(GreedyCtl *ctl) { pdl_trigger(); pdl_wait(); ctl->step += 1; }
 
 
 // RWKV-5 state scan over the tokens of one head (rwkv5_2_kernel_forward, att_seq.cu:258-322; per-head decay for 5.0):
@@ -670,6 +854,8 @@ __device__ __forceinline__ void wkv_stage(float (*sr)[64], float (*sk)[64], floa
 constexpr int WKV_THREADS = 64;
 template <int MODE>
 __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ __align__(16) float sr[2][WKV_TT][64], sk[2][WKV_TT][64], sv[2][WKV_TT][64];
   const int h = blockIdx.x, c = blockIdx.y, C = a.C;
   const int jg = threadIdx.x >> 2, iq = threadIdx.x & 3;
@@ -744,6 +930,8 @@ __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
 // mode 1: chain the chunk states; one thread per state entry (grid = H * 16 CTAs of 256 threads), the chunk end
 // states are fetched eight at a time ahead of the dependent multiply-adds
 __global__ void __launch_bounds__(256) wkv5_combine_kernel(SeqWkvArgs a) {
+  pdl_trigger();
+  pdl_wait();
   const int h = blockIdx.x >> 4, e = (blockIdx.x & 15) * 256 + threadIdx.x;
   const int i = e >> 6;
   const float w = a.per_head ? a.decay[h] : a.decay[h * 64 + i];
@@ -773,6 +961,8 @@ __global__ void __launch_bounds__(256) wkv5_combine_kernel(SeqWkvArgs a) {
 // (att_seq.cu:406-415): one warp per (token, head)
 __global__ void __launch_bounds__(256) gn_gate_seq_kernel(const float *y, const float *lnx_w, const float *lnx_b, const __half *g,
                                                           const __half *g_lo, int T, int H, __half *out, __half *out_lo) {
+  pdl_trigger();
+  pdl_wait();
   const int unit = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (unit >= T * H) return;
   const int t = unit / H, h = unit - t * H;
@@ -807,6 +997,8 @@ __global__ void __launch_bounds__(256) gn_gate_seq_kernel(const float *y, const 
 
 // plain LayerNorm of one row -> fp32 vector (ln_out before the head, model_forward_seq.cpp:171-175)
 __global__ void __launch_bounds__(256) ln_row_kernel(const float *x, const float *w, const float *b, int C, float *out) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[16];
   const float2 st = row_stats(x, C, red);
   for (int i = threadIdx.x; i < C; i += blockDim.x) out[i] = (x[i] - st.x) * st.y * w[i] + b[i];
@@ -815,44 +1007,44 @@ __global__ void __launch_bounds__(256) ln_row_kernel(const float *x, const float
 }  // namespace
 
 cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st) {
-  gather_emb_kernel<<<T, 256, 0, st>>>(emb, emb_f32, ids, C, x);
+  launch_k(gather_emb_kernel, dim3(T), dim3(256), 0, st, emb, emb_f32, ids, C, x);
   return cudaGetLastError();
 }
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
-  ln_mix_seq_kernel<<<a.T, 256, 0, st>>>(a);
+  launch_k(ln_mix_seq_kernel, dim3(a.T), dim3(256), 0, st, a);
   return cudaGetLastError();
 }
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
   if (a.batch_mode) {
-    wkv5_seq_kernel<2><<<dim3(H, a.T), WKV_THREADS, 0, st>>>(a);   // n_chunks == 1: every stream reads and writes its own state
+    launch_k(wkv5_seq_kernel<2>, dim3(dim3(H, a.T)), dim3(WKV_THREADS), 0, st, a);   // n_chunks == 1: every stream reads and writes its own state
     return cudaGetLastError();
   }
   if (a.n_chunks <= 1) {
-    wkv5_seq_kernel<2><<<dim3(H, 1), WKV_THREADS, 0, st>>>(a);
+    launch_k(wkv5_seq_kernel<2>, dim3(dim3(H, 1)), dim3(WKV_THREADS), 0, st, a);
     return cudaGetLastError();
   }
-  wkv5_seq_kernel<0><<<dim3(H, a.n_chunks), WKV_THREADS, 0, st>>>(a);
-  wkv5_combine_kernel<<<H * 16, 256, 0, st>>>(a);
-  wkv5_seq_kernel<2><<<dim3(H, a.n_chunks), WKV_THREADS, 0, st>>>(a);
+  launch_k(wkv5_seq_kernel<0>, dim3(dim3(H, a.n_chunks)), dim3(WKV_THREADS), 0, st, a);
+  launch_k(wkv5_combine_kernel, dim3(H * 16), dim3(256), 0, st, a);
+  launch_k(wkv5_seq_kernel<2>, dim3(dim3(H, a.n_chunks)), dim3(WKV_THREADS), 0, st, a);
   return cudaGetLastError();
 }
 cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st) {
   dim3 grid((a.C + 255) / 256, a.batch_mode ? a.T : 1);
-  wkv4_rows_kernel<<<grid, 256, 0, st>>>(a);
+  launch_k(wkv4_rows_kernel, dim3(grid), dim3(256), 0, st, a);
   return cudaGetLastError();
 }
 cudaError_t launch_argmax_rows(const float *logits, int rows, int V, int ld, int32_t *out, GreedyCtl *ctl, cudaStream_t st) {
-  argmax_rows_kernel<<<rows, 256, 0, st>>>(logits, V, ld, out, ctl);
-  if (ctl) greedy_bump_kernel<<<1, 1, 0, st>>>(ctl);
+  launch_k(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, logits, V, ld, out, ctl);
+  if (ctl) launch_k(greedy_bump_kernel, dim3(1), dim3(1), 0, st, ctl);
   return cudaGetLastError();
 }
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
                                int H, __half *out, __half *out_lo, cudaStream_t st) {
-  gn_gate_seq_kernel<<<(T * H + 7) / 8, 256, 0, st>>>(y, lnx_w, lnx_b, g, g_lo, T, H, out, out_lo);
+  launch_k(gn_gate_seq_kernel, dim3((T * H + 7) / 8), dim3(256), 0, st, y, lnx_w, lnx_b, g, g_lo, T, H, out, out_lo);
   return cudaGetLastError();
 }
 cudaError_t launch_ln_row(const float *x, const float *w, const float *b, int C, float *out, cudaStream_t st) {
-  ln_row_kernel<<<1, 256, 0, st>>>(x, w, b, C, out);
+  launch_k(ln_row_kernel, dim3(1), dim3(256), 0, st, x, w, b, C, out);
   return cudaGetLastError();
 }
 
@@ -861,7 +1053,77 @@ template <int MT, int BN>
 cudaError_t launch_gemm_t(const GemmMaps &maps, const GemmGroup &grp, dim3 grid, size_t smem, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(gemm_f16_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  gemm_f16_kernel<MT, BN><<<grid, G_THREADS, smem, st>>>(maps, grp);
+  launch_k(gemm_f16_kernel<MT, BN>, dim3(grid), dim3(G_THREADS), smem, st, maps, grp);
+  return cudaGetLastError();
+}
+}  // namespace
+
+namespace {
+template <int BN>
+cudaError_t launch_gemm_wt_t(const GemmMaps &maps, const GemmGroup &grp, dim3 grid, size_t smem, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(gemm_wt_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  launch_k(gemm_wt_kernel<BN>, dim3(grid), dim3(G_THREADS), smem, st, maps, grp);
+  return cudaGetLastError();
+}
+
+// FR_B200_GEMM_WT=0 sends few-row GEMMs through the 64-column tiles of gemm_f16_kernel instead (for comparison)
+bool wt_enabled() {
+  static const int on = [] { const char *v = getenv("FR_B200_GEMM_WT"); return !(v && v[0] == '0'); }();
+  return on != 0;
+}
+
+// up to GEMM_SMALL_M rows: weights along the MMA rows (gemm_wt_kernel), split-K into slabs when scratch was given
+cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
+  const int M = probs[0].M;
+  const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  GemmMaps maps;
+  GemmGroup grp;
+  memset(&grp, 0, sizeof(grp));
+  grp.n = n;
+  int tiles = 0, min_k1 = 1 << 30;
+  bool raw_ok = true;
+  for (int i = 0; i < n; ++i) {
+    const GemmArgs &g = probs[i];
+    if (g.K % GBK != 0 || g.M < 1 || g.N < 1 || g.M != M) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Bt) & 15) || (reinterpret_cast<uintptr_t>(g.A2) & 15) ||
+        (reinterpret_cast<uintptr_t>(g.Bt2) & 15))
+      return cudaErrorInvalidValue;
+    if (!make_map(&maps.a[i], g.A, g.M, g.K, bn) || !make_map(&maps.b[i], g.Bt, g.N, g.K, GBM)) return cudaErrorNotSupported;
+    if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, bn)) return cudaErrorNotSupported;
+    if (!make_map(&maps.b2[i], g.Bt2 ? g.Bt2 : g.Bt, g.N, g.K, GBM)) return cudaErrorNotSupported;
+    grp.p[i] = g;
+    grp.tile_start[i] = tiles;
+    tiles += (g.N + GBM - 1) / GBM;
+    min_k1 = std::min(min_k1, g.K / GBK);
+    raw_ok = raw_ok && g.raw != nullptr && (g.N & 3) == 0 && (g.ldo & 3) == 0;
+    if (g.A2) grp.dual |= 1;
+    if (g.Bt2) grp.dual |= 2;
+  }
+  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; maps.b2[i] = maps.b2[0]; }
+  grp.tile_start[n] = tiles;
+  const int m_tiles = (M + bn - 1) / bn;
+  // one CTA per SM, none waiting for a second wave: split K until the tiles about cover the SMs
+  grp.split = 1;
+  if (raw_ok) grp.split = std::max(1, std::min(std::min(148 / (tiles * m_tiles), GEMM_SPLIT_MAX), min_k1 / 4));
+  grp.stage_bytes = ((grp.dual & 2) ? 2u : 1u) * G_A_BYTES + ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
+  // two CTAs per SM with rings of >= 3 slots where they fit (shorter tail when there are more tiles than SMs),
+  // else one CTA with as deep a ring as fits
+  int stages = (int)((100u << 10) / grp.stage_bytes);
+  if (stages < 3) stages = (int)((200u << 10) / grp.stage_bytes);
+  grp.stages = std::max(2, std::min(stages, WT_MAX_STAGES));
+  const size_t smem = 1024 + (size_t)grp.stages * grp.stage_bytes + 1024;
+  dim3 grid(tiles, m_tiles, grp.split);
+  cudaError_t e = bn == 32    ? launch_gemm_wt_t<32>(maps, grp, grid, smem, st)
+                  : bn == 64  ? launch_gemm_wt_t<64>(maps, grp, grid, smem, st)
+                  : bn == 128 ? launch_gemm_wt_t<128>(maps, grp, grid, smem, st)
+                              : launch_gemm_wt_t<256>(maps, grp, grid, smem, st);
+  if (e != cudaSuccess) return e;
+  if (grp.split > 1) {
+    int max_n = 0;
+    for (int i = 0; i < n; ++i) max_n = std::max(max_n, probs[i].N);
+    launch_k(gemm_finish_kernel, dim3(dim3((M * (max_n / 4) + 255) / 256, n)), dim3(256), 0, st, grp);
+  }
   return cudaGetLastError();
 }
 }  // namespace
@@ -869,6 +1131,7 @@ cudaError_t launch_gemm_t(const GemmMaps &maps, const GemmGroup &grp, dim3 grid,
 cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st) {
   if (n < 1 || n > GEMM_GROUP_MAX || (mt != 1 && mt != 2)) return cudaErrorInvalidValue;
   const int M = probs[0].M;
+  if (M <= GEMM_SMALL_M && wt_enabled()) return launch_gemm_wt(probs, n, st);
   // few rows (batched decode): narrow N tiles and split-K, so that a few hundred CTAs stream the weights
   const bool narrow = M <= GEMM_SMALL_M;
   const int bn = narrow ? 64 : 256;
@@ -911,11 +1174,11 @@ cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t
   if (narrow) e = mt == 1 ? launch_gemm_t<1, 64>(maps, grp, grid, smem, st) : launch_gemm_t<2, 64>(maps, grp, grid, smem, st);
   else e = mt == 1 ? launch_gemm_t<1, 256>(maps, grp, grid, smem, st) : launch_gemm_t<2, 256>(maps, grp, grid, smem, st);
   if (e != cudaSuccess) return e;
-  if (grp.split > 1)
-    for (int i = 0; i < n; ++i) {
-      const int threads = M * (probs[i].N / 4);
-      gemm_finish_kernel<<<(threads + 255) / 256, 256, 0, st>>>(probs[i], grp.split);
-    }
+  if (grp.split > 1) {
+    int max_n = 0;
+    for (int i = 0; i < n; ++i) max_n = std::max(max_n, probs[i].N);
+    launch_k(gemm_finish_kernel, dim3(dim3((M * (max_n / 4) + 255) / 256, n)), dim3(256), 0, st, grp);
+  }
   return cudaGetLastError();
 }
 
