@@ -803,12 +803,20 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float *logits, i
   __shared__ unsigned long long best[8];
   const float *row = logits + (size_t)blockIdx.x * ld;
   unsigned long long m = 0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    unsigned u = __float_as_uint(row[i]);
+  auto take = [&](float f, int i) {
+    unsigned u = __float_as_uint(f);
     u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
     const unsigned long long w = ((unsigned long long)u << 32) | (0xffffffffu - (unsigned)i);
     m = w > m ? w : m;
+  };
+  const int V4 = ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) ? (V & ~3) : 0;
+  // 16-byte loads, eight in flight per thread: a row is read by one CTA, so the loads in flight set its speed
+#pragma unroll 8
+  for (int i = threadIdx.x * 4; i < V4; i += blockDim.x * 4) {
+    const float4 f = *reinterpret_cast<const float4 *>(row + i);
+    take(f.x, i); take(f.y, i + 1); take(f.z, i + 2); take(f.w, i + 3);
   }
+  for (int i = V4 + threadIdx.x; i < V; i += blockDim.x) take(row[i], i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const unsigned long long other = __shfl_xor_sync(0xffffffffu, m, o);
@@ -1104,8 +1112,20 @@ cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
   grp.tile_start[n] = tiles;
   const int m_tiles = (M + bn - 1) / bn;
   // one CTA per SM, none waiting for a second wave: split K until the tiles about cover the SMs
+  // (up to 64 rows the slabs are small next to the weights and two CTAs fit an SM: twice the slots, so that every SM
+  // streams even when the group has few tiles)
   grp.split = 1;
-  if (raw_ok) grp.split = std::max(1, std::min(std::min(148 / (tiles * m_tiles), GEMM_SPLIT_MAX), min_k1 / 4));
+  const int slots = bn <= 64 ? 2 * 148 : 148;
+  if (raw_ok) {
+    // cost of a split, in K slices of one CTA: waves x (slices per CTA + fill and drain) + the slabs it adds
+    const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 4));
+    float best = 0.f;
+    for (int sp = 1; sp <= max_split; ++sp) {
+      const int waves = (ctas * sp + slots - 1) / slots;
+      const float cost = (float)waves * (float)((min_k1 + sp - 1) / sp + 2) + 0.5f * (float)sp;
+      if (sp == 1 || cost < best) { best = cost; grp.split = sp; }
+    }
+  }
   grp.stage_bytes = ((grp.dual & 2) ? 2u : 1u) * G_A_BYTES + ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
   // two CTAs per SM with rings of >= 3 slots where they fit (shorter tail when there are more tiles than SMs),
   // else one CTA with as deep a ring as fits
