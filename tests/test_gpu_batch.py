@@ -28,14 +28,16 @@ def _close(got, want, what):
 
 @pytest.mark.parametrize("name,fmt,B", [("tiny4", "fp16", 12), ("tiny4b", "int8", 20), ("tiny4", "int4", 16),
                                         ("tiny52", "fp16", 12), ("tiny50", "int8", 9), ("tiny51", "int4", 10),
-                                        ("mid4", "fp16", 40), ("mid52", "int4", 150)])
+                                        ("mid4", "fp16", 40), ("mid52", "int4", 150), ("mid4", "int8", 100),
+                                        ("mid4", "int4", 300), ("mid52", "fp16", 70)])
 def test_many_streams_match_oracle(pkg, orc, synth, name, fmt, B):
-    """Stream b of a B-stream decode == the oracle fed stream b's tokens; 150 streams use the 256-row GEMM tiles."""
+    """Stream b of a B-stream decode == the oracle fed stream b's tokens.  The stream counts walk the few-row GEMM's
+    tile widths: 32 (up to 32 streams), 64, 128, 256, and two 256-stream tiles (300 streams)."""
     shape, m, ref = _pair(pkg, orc, synth, name, fmt, B)
     steps = 4
     ids = synth.token_ids(shape, steps * B, seed=9).reshape(steps, B)
     got = [m.decode(ids[t]) for t in range(steps)]
-    for b in list(range(min(B, 6))) + [B - 1]:
+    for b in list(range(min(B, 6))) + ([B // 2 + 1] if B > 64 else []) + [B - 1]:
         ref.reset()
         for t in range(steps):
             _close(got[t][b], ref.run(int(ids[t, b])), f"{name} {fmt} stream {b} step {t}")
