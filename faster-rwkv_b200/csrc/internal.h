@@ -131,7 +131,7 @@ struct GemmArgs {
   float *raw;          // optional scratch [GEMM_SPLIT_MAX][M][N] f32: allows split-K when M <= GEMM_SMALL_M
 };
 constexpr int GEMM_GROUP_MAX = 4;
-constexpr int GEMM_SMALL_M = 1024;    // up to this many rows the GEMM uses 64-column tiles (and split-K, given scratch)
+constexpr int GEMM_SMALL_M = 1024;    // up to this many rows the GEMM puts the weights along the MMA rows (and splits K, given scratch)
 constexpr int GEMM_SPLIT_MAX = 8;
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);   // one GEMM; 256-row tiles when M > 128
 // n <= 4 GEMMs with equal M in one launch; mt = 128-row sub-tiles per CTA (1 or 2)

@@ -21,9 +21,10 @@ def _sig(v):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (200, 448, 448), (7, 128, 128), (333, 1024, 256),
-                                   (1, 64, 64), (129, 257, 192)])
+                                   (1, 64, 64), (129, 257, 192), (1100, 320, 128), (1500, 520, 192)])
 def test_gemm_plain_against_numpy(pkg, M, N, K):
-    """acc = fp16(A) @ fp16(W) with fp32 accumulation; ragged M and N tails are zero-filled by TMA and masked."""
+    """acc = fp16(A) @ fp16(W) with fp32 accumulation; ragged M and N tails are zero-filled by TMA and masked.
+    Up to 1024 rows run the few-row kernel (weights along the MMA rows), more rows the 256 x 256 prompt tiles."""
     rng = np.random.default_rng(M * 7 + N)
     A = rng.standard_normal((M, K), dtype=np.float32)
     W = rng.standard_normal((K, N), dtype=np.float32) / np.sqrt(K)
@@ -35,7 +36,11 @@ def test_gemm_plain_against_numpy(pkg, M, N, K):
 def test_gemm_epilogues_against_numpy(pkg):
     """The element-wise kernels the reference runs after each GEMM (att_seq.cu:368-423, ffn_seq.cu:65-87), fused."""
     rng = np.random.default_rng(5)
-    M, N, K = 200, 448, 192
+    _epilogues(pkg, rng, 200, 448, 192)      # few-row kernel
+    _epilogues(pkg, rng, 1300, 448, 192)     # prompt tiles
+
+
+def _epilogues(pkg, rng, M, N, K):
     A = rng.standard_normal((M, K), dtype=np.float32)
     W = rng.standard_normal((K, N), dtype=np.float32) / np.sqrt(K)
     x = rng.standard_normal((M, N), dtype=np.float32)
