@@ -446,7 +446,7 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": MEASURED_TRAFFIC.get((args.workload, args.weights, B)), "peak_source": peak_kind,
                 "kernel": "decode_kernel (persistent, one launch per token)" if B <= 8 else
-                          "gemm_f16_kernel + row kernels (one row per stream; two steps replayed as a CUDA graph)",
+                          "gemm_wt_kernel + row kernels (one row per stream; two steps replayed as a CUDA graph)",
                 "algorithmic_bytes_per_launch": algo}
 
     variants = {}
