@@ -15,6 +15,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Union
 
 import numpy as np
 
+from . import shard  # noqa: F401  (re-exported: stream partitioning across ranks)
 from . import synth  # noqa: F401  (re-exported: synthetic `.fr` generator)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -79,6 +80,7 @@ SIGNATURES = {
     "fr_b200_noalloc_last_error": (ctypes.c_char_p, []),
     "fr_b200_get_info": (_i, [_vp, ctypes.POINTER(Info)]),
     "fr_b200_decode_profile": (_i, [_vp, _vp, _i, _vp, _i]),
+    "fr_b200_wait_selftest": (_i, [_i, ctypes.c_uint]),
     "fr_b200_strerror": (ctypes.c_char_p, [_i]),
     "fr_b200_last_error": (ctypes.c_char_p, []),
 }

@@ -3,7 +3,7 @@
 
   backend/build/fr_b200_run <model.fr> "cuda fp16|int8|int4" <out.bin> [--seq] ids...
 
-The reference sources are compiled where they lie (FR_REFERENCE_DIR, default /root/reference) with
+The reference sources are compiled where they lie (FR_REFERENCE_DIR, else a checkout named "reference" beside this repository) with
 -DFR_ENABLE_CUDA; kernels/cuda/* is left out (this backend replaces it).  registry_backend.o is linked last so
 that its registrations for Device::kCUDA win over def::init_model / def::ModelForward (kernels/registry.h:17-19).
 msgpack-c is not available offline; backend/compat/msgpack.hpp stands in for it in this container.
@@ -15,7 +15,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("FR_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("FR_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 OUT = os.path.join(HERE, "build")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 

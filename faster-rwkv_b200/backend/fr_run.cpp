@@ -4,6 +4,9 @@
 // Model::Run(vector) once (model.cpp:188-203) and only the last logits are written.
 // --bench N: after the ids, N greedy tokens through Model::Run(int) (host argmax, as bench_model.cpp:5-10 times
 // Run + the copy to the host) are timed with the wall clock; prints "ms_per_token <x>".
+// --time-seq N (with --seq): the prompt is run N more times from reset states, each Run(vector) (which ends with the
+// copy of the logits to the host) timed with the wall clock; prints "ms_per_prompt <fastest>".
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -23,11 +26,12 @@ int main(int argc, char **argv) {
     rwkv::Model model(argv[1], argv[2]);
     std::ofstream out(argv[3], std::ios::binary);
     bool seq = false;
-    int bench = 0;
+    int bench = 0, time_seq = 0;
     std::vector<int> ids;
     for (int i = 4; i < argc; ++i) {
       if (!std::strcmp(argv[i], "--seq")) seq = true;
       else if (!std::strcmp(argv[i], "--bench") && i + 1 < argc) bench = std::atoi(argv[++i]);
+      else if (!std::strcmp(argv[i], "--time-seq") && i + 1 < argc) time_seq = std::atoi(argv[++i]);
       else ids.push_back(std::atoi(argv[i]));
     }
     auto dump = [&](const rwkv::Tensor &t) {
@@ -35,6 +39,17 @@ int main(int argc, char **argv) {
     };
     if (seq) dump(model.Run(ids));
     else for (int id : ids) dump(model.Run(id));
+    if (seq && time_seq > 0) {
+      double best = 1e30;
+      for (int i = 0; i < time_seq; ++i) {
+        model.ResetStates();
+        auto t0 = std::chrono::steady_clock::now();
+        rwkv::Tensor t = model.Run(ids);
+        auto t1 = std::chrono::steady_clock::now();
+        best = std::min(best, std::chrono::duration<double, std::milli>(t1 - t0).count());
+      }
+      std::printf("ms_per_prompt %.6f\n", best);
+    }
     if (bench > 0) {
       auto greedy = [&](int id) {
         rwkv::Tensor t = model.Run(id);

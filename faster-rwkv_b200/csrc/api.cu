@@ -153,7 +153,7 @@ void plan(fr_b200_model *m) {
     p.w = reinterpret_cast<const uint8_t *>(w_off);        // patched to a pointer in finalize
     p.rscale = reinterpret_cast<const __half *>(rs_off);   // element offset, patched in finalize
     p.kind = kind; p.layer = layer; p.K = K; p.n_items = n_items; p.n_sub = n_sub;
-    p.rot = (pi * 37) % 148;
+    p.rot = 0;   // set in finalize, once the grid size is known
     ++pi;
     m->phases.push_back(p);
   };
@@ -557,16 +557,32 @@ int fr_b200_finalize(fr_b200_model *m) {
 }
 
 namespace {
+// Streams that are decoded together read the same copy of their token-shift states (the kernels take one parity per
+// launch).  A stream that was reset, imported or prefilled on its own may be one token out of step with stream 0:
+// its current copy is duplicated into the other one and its parity flipped, which changes nothing it will read.
+int align_parity(fr_b200_model *m, int batch, cudaStream_t st) {
+  const size_t ab = act_bytes(m->cfg.act_fp16), row = (size_t)m->C * ab;
+  for (int b = 1; b < batch; ++b) {
+    if (m->par[b] == m->par[0]) continue;
+    const int par = (int)m->par[b];
+    uint8_t *base = m->d_state + (size_t)b * m->state_stride;
+    CU(cudaMemcpy2DAsync(base + off_sx(m->C, m->cfg.act_fp16, par ^ 1), m->layer_stride, base + off_sx(m->C, m->cfg.act_fp16, par),
+                         m->layer_stride, row, m->L, cudaMemcpyDeviceToDevice, st));
+    CU(cudaMemcpy2DAsync(base + off_ffn_sx(m->C, m->H, m->v5, m->cfg.act_fp16, par ^ 1), m->layer_stride,
+                         base + off_ffn_sx(m->C, m->H, m->v5, m->cfg.act_fp16, par), m->layer_stride, row, m->L,
+                         cudaMemcpyDeviceToDevice, st));
+    m->par[b] ^= 1u;
+  }
+  return 0;
+}
 int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids, int R, cudaStream_t st);
 // more streams than the persistent kernel carries (or a model too wide for that many): the GEMM path decodes them
 bool decode_by_rows(const fr_b200_model *m, int batch) { return batch > MAX_B || m->n_stages[decode_mode(batch)] == 0; }
-int rows_decode_check(fr_b200_model *m, const int32_t *ids_host, int batch) {
+int rows_decode_check(fr_b200_model *m, const int32_t *ids_host, int batch, cudaStream_t st) {
   if (!m->d_plain) return fail(FR_B200_E_UNSUPPORTED, "this batch size needs a model created with max_batch > 8");
-  for (int b = 0; b < batch; ++b) {
+  for (int b = 0; b < batch; ++b)
     if (ids_host && (ids_host[b] < 0 || ids_host[b] >= m->V)) return fail(FR_B200_E_ARG, "token id out of range");
-    if (m->par[b] != m->par[0]) return fail(FR_B200_E_STATE, "streams decoded together must have seen the same number of tokens since their last reset");
-  }
-  return 0;
+  return align_parity(m, batch, st);
 }
 }  // namespace
 
@@ -606,11 +622,12 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned
     m->exch_batch = batch;
   }
   p.seq_base = 255u + m->seq;
-  p.par_mask = 0;
-  for (int b = 0; b < batch; ++b) {
-    if (m->par[b] != m->par[0]) return fail(FR_B200_E_STATE, "streams decoded together must have seen the same number of tokens since their last reset");
-    p.par_mask |= m->par[b] << b;
+  {
+    int rc = align_parity(m, batch, st);
+    if (rc) return rc;
   }
+  p.par_mask = 0;
+  for (int b = 0; b < batch; ++b) p.par_mask |= m->par[b] << b;
   const size_t bc = (size_t)m->cfg.max_batch * m->C;
   p.k5 = m->d_v5buf; p.v5 = p.k5 + bc; p.r5 = p.v5 + bc; p.g5 = p.r5 + bc; p.o5 = p.g5 + bc;
   p.state = m->d_state; p.state_stride = m->state_stride; p.layer_stride = m->layer_stride;
@@ -619,7 +636,8 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned
   p.l2_prefetch_bytes = m->l2_prefetch;
   CU(launch_decode(p, mode, m->grid, smem, st));
   m->launches++;
-  m->seq = (m->seq + (unsigned)m->phases.size()) % 255u;
+  // a phase count that is a multiple of 255 would give consecutive tokens identical tags: skip one tag per token then
+  m->seq = (m->seq + (unsigned)m->phases.size() + (m->phases.size() % 255u == 0 ? 1u : 0u)) % 255u;
   for (int b = 0; b < batch; ++b) m->par[b] ^= 1u;
   return 0;
 }
@@ -632,7 +650,7 @@ int fr_b200_decode(fr_b200_model *m, const int32_t *ids, int batch, float *logit
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   if (decode_by_rows(m, batch)) {
-    if ((rc = rows_decode_check(m, ids, batch))) return rc;
+    if ((rc = rows_decode_check(m, ids, batch, st))) return rc;
     if ((rc = rows_forward(m, true, 0, ids, batch, st))) return rc;
     if (argmax) {
       CU(launch_argmax_rows(m->d_out, batch, m->V, m->Vpad, m->out_argmax(), nullptr, st));
@@ -685,7 +703,7 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
   }
   if (decode_by_rows(m, batch)) {
     // GEMM path: ids stay on the device, row t of the history feeds step t + 1
-    int rc = rows_decode_check(m, first_ids, batch);
+    int rc = rows_decode_check(m, first_ids, batch, st);
     if (rc) return rc;
     int32_t *hist32 = reinterpret_cast<int32_t *>(m->d_hist + need);
     GreedyCtl ctl;
@@ -850,7 +868,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
   int n_chunks = 1, chunk_len = T;
   if (!batch_mode && m->v5) {
-    n_chunks = std::max(1, std::min(T / 32, (8 * 148 + H - 1) / H));
+    n_chunks = std::max(1, std::min(T / 32, (8 * device_sm_count() + H - 1) / H));
     chunk_len = (T + n_chunks - 1) / n_chunks;
     n_chunks = (T + chunk_len - 1) / chunk_len;
   }
@@ -1299,6 +1317,20 @@ int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float 
   CU(cudaMemcpy(&status, p.status, 4, cudaMemcpyDeviceToHost));
   if (status) return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(status) + ")");
   CU(cudaMemcpy2D(y, (size_t)N * 4, dy.p, (size_t)Npad * 4, (size_t)N * 4, batch, cudaMemcpyDefault));
+  return FR_B200_OK;
+}
+
+int fr_b200_wait_selftest(int device, unsigned limit_us) {
+  if (limit_us < 1 || limit_us > 1000000) return fail(FR_B200_E_ARG, "limit must be 1 .. 1,000,000 microseconds");
+  CU(cudaSetDevice(device));
+  DevBuf st;
+  CU(st.alloc(4));
+  CU(cudaMemset(st.p, 0, 4));
+  CU(launch_wait_selftest((int *)st.p, (unsigned long long)limit_us * 1000ull, 0));
+  CU(cudaDeviceSynchronize());
+  int status = 0;
+  CU(cudaMemcpy(&status, st.p, 4, cudaMemcpyDeviceToHost));
+  if (status) return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(status) + ")");
   return FR_B200_OK;
 }
 

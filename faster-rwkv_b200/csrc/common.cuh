@@ -65,7 +65,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t *b, uint32_t parity) {
 // Bounded wait.  abort_flag lives in shared memory; once any thread of the CTA sets it every
 // later wait returns at once, so the CTA drains to its end instead of hanging.
 __device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, volatile int *abort_flag, int *status,
-                                          int code) {
+                                          int code, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try(b, parity)) return true;
   if (*abort_flag) return false;
   const unsigned long long t0 = globaltimer_ns();
@@ -73,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, volatile
   while (!mbar_try(b, parity)) {
     if ((++it & 63) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

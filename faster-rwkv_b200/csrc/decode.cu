@@ -14,9 +14,9 @@
 //     are added: the operand keeps ~22 mantissa bits at no extra MMA for one stream (7 of the 8
 //     columns are idle anyway) and 4 streams share one MMA.
 //
-// Phases are not separated by barriers.  Every value one phase hands to the next across CTAs is a
-// 64-bit word {fp32 value, sequence number of the writing phase}; a reader polls the words it needs
-// until they carry the expected number.  Because each phase needs all outputs of the one before it,
+// Phases are not separated by barriers.  Every value one phase hands to the next across CTAs is one
+// 32-bit word: the fp32 value rounded to 16 significant bits, its low 8 mantissa bits replaced by an
+// 8-bit tag of the writing phase; a reader polls the words it needs until they carry the expected tag.  Because each phase needs all outputs of the one before it,
 // a CTA can only overwrite a vector after every reader of its previous contents has moved on; a CTA
 // that owns no row block in a phase skips the phase.  The token-shift states are double-buffered for
 // the same reason.  Every wait is bounded: after WAIT_LIMIT_NS the CTA records a status and drains.
@@ -1254,6 +1254,27 @@ cudaError_t launch_decode(const DecodeParams &p, int mode, int grid, size_t smem
 
 cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *grid) {
   FRB_DISPATCH(max_grid_t, smem, device, grid)
+}
+
+namespace {
+// One thread waits on an mbarrier that nobody ever arrives at, through the same bounded-wait helper every kernel
+// here uses, with the given limit: the wait must give up, record ST_TIMEOUT_FULL and let the kernel end normally.
+__global__ void wait_selftest_kernel(int *status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, status, ST_TIMEOUT_FULL, limit_ns);
+}
+}  // namespace
+
+cudaError_t launch_wait_selftest(int *status, unsigned long long limit_ns, cudaStream_t st) {
+  wait_selftest_kernel<<<1, 32, 0, st>>>(status, limit_ns);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_unpack_ids(const unsigned long long *packed, int n, int32_t *out, cudaStream_t st) {

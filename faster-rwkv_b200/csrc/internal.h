@@ -53,9 +53,9 @@ struct LayerDev {
 };
 
 // One element of an exchange vector (a vector one phase writes and the next phases read across CTAs):
-// the fp32 value in the low word and, in the high word, the sequence number of the phase that wrote it.
+// the fp32 value rounded to 16 significant bits with an 8-bit tag of the writing phase in its low mantissa bits.
 // A reader knows which phase must have produced the value and polls until the tag matches, so the data
-// is its own synchronisation: no grid-wide barrier, no fence, one 64-bit store per value.
+// is its own synchronisation: no grid-wide barrier, no fence, one 32-bit store per value.
 typedef uint32_t exch_t;   // fp32 value, low 8 mantissa bits = tag of the phase that wrote it
 
 struct DecodeParams {
@@ -133,6 +133,7 @@ struct GemmArgs {
 constexpr int GEMM_GROUP_MAX = 4;
 constexpr int GEMM_SMALL_M = 1024;    // up to this many rows the GEMM puts the weights along the MMA rows (and splits K, given scratch)
 constexpr int GEMM_SPLIT_MAX = 8;
+int device_sm_count();   // SMs of the current device
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);   // one GEMM; 256-row tiles when M > 128
 // n <= 4 GEMMs with equal M in one launch; mt = 128-row sub-tiles per CTA (1 or 2)
 cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st);
@@ -196,6 +197,7 @@ cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *gri
 // packed arg-max word = {order-preserving image of the fp32 logit, 0xFFFFFFFF - index}: a 64-bit max picks the
 // largest logit and, among equals, the smallest index
 cudaError_t launch_unpack_ids(const unsigned long long *packed, int n, int32_t *out, cudaStream_t st);
+cudaError_t launch_wait_selftest(int *status, unsigned long long limit_ns, cudaStream_t st);
 
 // quantise / pack (pack.cu); all pointers device
 cudaError_t launch_f16_to_f32(const __half *src, float *dst, size_t n, cudaStream_t st);

@@ -13,6 +13,7 @@
 // In host code the array's name is only a handle for the runtime, not a device address; the address is looked up
 // with cudaGetSymbolAddress once per device, with that device current, the first time the entry point runs on
 // it.  Make that first call outside any stream capture.
+#include <atomic>
 #include <cstring>
 #include <string>
 
@@ -36,7 +37,9 @@ constexpr size_t SCRATCH_BYTES = OFF_PHASE + 256;
 static __device__ __align__(256) unsigned char g_scratch[SCRATCH_BYTES];
 
 constexpr int MAX_DEVICES = 64;
-unsigned char *g_scratch_addr[MAX_DEVICES];       // device address of g_scratch on each device, once looked up
+// device address of g_scratch on each device, once looked up.  The address belongs to the device's primary context:
+// after a cudaDeviceReset the entry point must not be used again in this process.
+std::atomic<unsigned char *> g_scratch_addr[MAX_DEVICES];
 
 thread_local std::string g_noalloc_err;
 
@@ -58,19 +61,29 @@ extern "C" int fr_b200_matvec_noalloc(const float *W, int K, int N, int weight_f
   if (weight_format < 0 || weight_format > 2) NA_FAIL(FR_B200_E_ARG, "bad weight_format");
   if (batch < 1 || batch > MAX_B) NA_FAIL(FR_B200_E_ARG, "batch must be 1..8");
   if (device < 0 || device >= MAX_DEVICES) NA_FAIL(FR_B200_E_ARG, "device ordinal out of range");
+  // the kernel reads x with 16-byte loads straight from the caller's buffer (fr_b200_matvec copies it first)
+  if (reinterpret_cast<uintptr_t>(x) & 15) NA_FAIL(FR_B200_E_ARG, "x must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(W) & 3) || (reinterpret_cast<uintptr_t>(y) & 3)) NA_FAIL(FR_B200_E_ARG, "W and y must be 4-byte aligned");
   const int Npad = (N + ROWS - 1) / ROWS * ROWS, nb = Npad / ROWS;
   if (K > MAX_K || Npad > MAX_ROWS || (size_t)Npad * K > MAX_WEIGHTS)
     NA_FAIL(FR_B200_E_UNSUPPORTED, "matrix exceeds the built-in scratch: at most 1,048,576 weights after padding the "
                                    "rows to a multiple of 16, K <= 8192, N <= 16384");
   NA_CU(cudaSetDevice(device));
-  if (!g_scratch_addr[device]) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  {
+    // the call copies a status word back and synchronises the stream: neither is legal while the stream is capturing
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    NA_CU(cudaStreamIsCapturing(st, &cap));
+    if (cap != cudaStreamCaptureStatusNone) NA_FAIL(FR_B200_E_STATE, "the stream is capturing: this entry point synchronises it");
+  }
+  unsigned char *S = g_scratch_addr[device].load(std::memory_order_acquire);
+  if (!S) {
     // first call on this device: resolve the device address of the array (the host-side name is not one)
     unsigned char *ptr = nullptr;
     NA_CU(cudaGetSymbolAddress((void **)&ptr, g_scratch));
-    g_scratch_addr[device] = ptr;
+    g_scratch_addr[device].store(ptr, std::memory_order_release);
+    S = ptr;
   }
-  unsigned char *S = g_scratch_addr[device];
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int fmt = weight_format;
   const size_t n = (size_t)K * N, rb = rowblock_bytes(fmt, K);
   uint8_t *tiles = S + OFF_TILES;

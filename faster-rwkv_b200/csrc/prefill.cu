@@ -20,6 +20,19 @@
 
 namespace frb {
 
+// SMs of the current device (asked once per device): grids and split-K factors are sized from it
+int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 namespace {
 
 // Every kernel of the seq / batch chain goes through here.  With FR_B200_PDL != 0 (the default) the launch carries
@@ -1116,7 +1129,8 @@ cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
   // (up to 64 rows the slabs are small next to the weights and two CTAs fit an SM: twice the slots, so that every SM
   // streams even when the group has few tiles)
   grp.split = 1;
-  const int slots = bn <= 64 ? 2 * 148 : 148;
+  const int sms = device_sm_count();
+  const int slots = bn <= 64 ? 2 * sms : sms;
   if (raw_ok) {
     // cost of a split, in K slices of one CTA: waves x (slices per CTA + fill and drain) + the slabs it adds
     const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 4));
@@ -1181,7 +1195,7 @@ cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t
   const int m_tiles = (M + mt * GBM - 1) / (mt * GBM);
   grp.split = 1;
   if (narrow && raw_ok) {
-    const int want = (2 * 148 + tiles * m_tiles - 1) / (tiles * m_tiles);    // about two CTAs per SM in total
+    const int want = (2 * device_sm_count() + tiles * m_tiles - 1) / (tiles * m_tiles);    // about two CTAs per SM in total
     grp.split = std::max(1, std::min(std::min(want, GEMM_SPLIT_MAX), min_k1 / 4));   // at least 4 K slices per CTA
   }
   if (mt == 1)

@@ -220,3 +220,66 @@ def read_fr(path: str):
 def token_ids(shape: Shape, n: int, seed: int = 0) -> np.ndarray:
     """n token ids ~ U[0, vocab) from `seed`."""
     return np.random.default_rng(seed + 12345).integers(0, shape.vocab, n).astype(np.int32)
+
+
+def device_tensors(shape: Shape, seed: int, device, file_dtype: str = "fp32"):
+    """Yield (name, CUDA tensor) for a model of `shape` with the distributions of generate(), drawn on the GPU (the
+    1.5B- to 14B-shaped models take minutes to draw with numpy).  The stream of values differs from generate()'s.
+    file_dtype "fp16" applies what a "cuda fp16" `.fr` file holds: fp16 everywhere except time_decay, time_first and
+    ln_x, att.output / ffn.value pre-divided by 2**(layer // 6) (kernels/default/model_forward.cpp:173-175)."""
+    import math
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    C, F, V, L, H = shape.n_embd, shape.n_ffn, shape.vocab, shape.n_layer, shape.n_head
+    v5 = shape.version.startswith("5")
+    gate = shape.version in ("5.1", "5.2")
+
+    def mat(k, n):
+        return torch.randn(k, n, generator=g, device=device, dtype=torch.float32) / math.sqrt(k)
+
+    def uni(n, lo, hi):
+        return torch.rand(n, generator=g, device=device, dtype=torch.float32) * (hi - lo) + lo
+
+    def raw():
+        yield "emb.weight", torch.randn(V, C, generator=g, device=device, dtype=torch.float32)
+        for i in range(L):
+            b, a, f = f"blocks.{i}.", f"blocks.{i}.att.", f"blocks.{i}.ffn."
+            for ln in (b + "ln1", b + "ln2"):
+                yield ln + ".weight", torch.ones(C, device=device)
+                yield ln + ".bias", torch.zeros(C, device=device)
+            if v5:
+                yield a + "ln_x.weight", torch.ones(C, device=device)
+                yield a + "ln_x.bias", torch.zeros(C, device=device)
+            for m in ("k", "v", "r") + (("g",) if gate else ()):
+                yield a + "time_mix_" + m, uni(C, 0, 1)
+            if not v5:
+                yield a + "time_decay", -torch.exp(uni(C, -6, 1))
+                yield a + "time_first", uni(C, -1, 1)
+            elif shape.version == "5":
+                yield a + "time_decay", torch.exp(-torch.exp(uni(H, -6, 1))).reshape(H, 1, 1)
+                yield a + "time_first", uni(H, -1, 1).reshape(H, 1, 1)
+            else:
+                yield a + "time_decay", torch.exp(-torch.exp(uni(C, -6, 1))).reshape(H, C // H, 1)
+                yield a + "time_first", uni(C, -1, 1).reshape(H, C // H, 1)
+            yield a + "key.weight", mat(C, C)
+            yield a + "value.weight", mat(C, C)
+            yield a + "receptance.weight", mat(C, C)
+            if gate:
+                yield a + "gate.weight", mat(C, C)
+            yield a + "output.weight", mat(C, C)
+            yield f + "time_mix_k", uni(C, 0, 1)
+            yield f + "time_mix_r", uni(C, 0, 1)
+            yield f + "key.weight", mat(C, F)
+            yield f + "value.weight", mat(F, C)
+            yield f + "receptance.weight", mat(C, C)
+        yield "ln_out.weight", torch.ones(C, device=device)
+        yield "ln_out.bias", torch.zeros(C, device=device)
+        yield "head.weight", mat(C, V)
+
+    for name, t in raw():
+        if file_dtype == "fp16" and not name.endswith(_FP32_ONLY):
+            if name.endswith(("att.output.weight", "ffn.value.weight")):
+                t = t / float(2 ** (int(name.split(".")[1]) // 6))
+            t = t.half()
+        yield name, t

@@ -156,12 +156,14 @@ int fr_b200_matvec(const float *W, int K, int N, int weight_format, const float 
  * whole device and may fail once a framework pool owns the memory, or a latency-bound loop.  All scratch (the
  * converted matrix, the packed tiles, scales, padded output, descriptor) sits in a fixed 4.7 MiB array inside the
  * library image, present on every GPU that loads the library until the process ends.
- *   - W [K,N], x [batch,K], y [batch,N]: fp32 DEVICE pointers on `device`; nothing is allocated, no
+ *   - W [K,N], x [batch,K], y [batch,N]: fp32 DEVICE pointers on `device`; x must be 16-byte aligned (the kernel
+ *     reads it in place with 16-byte loads; FR_B200_E_ARG otherwise); nothing is allocated, no
  *     cudaMalloc / cudaFree / pool routine is called.
  *   - limits: K a multiple of 64, K <= 8192, N <= 16384, ceil16(N) * K <= 1,048,576, batch <= 8; larger inputs
  *     return FR_B200_E_UNSUPPORTED with the reason in fr_b200_noalloc_last_error().
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make it before any
- *     stream capture begins.
+ *     stream capture begins.  Every call copies a status word back and synchronises `stream`, so it must never be
+ *     made on a capturing stream (FR_B200_E_STATE), and not again after the device's context was reset.
  *   - every call reuses the one array: calls whose GPU work can overlap race; serialise them.
  * Synchronises `stream` before returning. */
 int fr_b200_matvec_noalloc(const float *W, int K, int N, int weight_format, const float *x, int batch, float *y,
@@ -192,6 +194,13 @@ int fr_b200_get_info(const fr_b200_model *m, fr_b200_info *info);
  * A tracing aid (the reference has only wall-clock FR_SHOW_SPEED prints, chat.cpp:98-111).
  * stamps: host, n_ctas * n_phases * 8 entries (fr_b200_get_info gives both counts). */
 int fr_b200_decode_profile(fr_b200_model *m, const int32_t *ids, int batch, uint64_t *stamps, int n_stamps);
+
+/* Runs out one bounded device-side wait on purpose, without hanging anything: a one-CTA kernel waits, through the
+ * helper every kernel of this library waits with, on a barrier that nothing arrives at, with a limit of limit_us
+ * microseconds (1 .. 1,000,000) instead of the built-in 2 s.  The wait gives up, records its status word and the
+ * kernel ends normally; the call returns FR_B200_E_TIMEOUT (the expected result) and the context stays usable.
+ * The reference has no device-side waits and reports failures as exceptions from CUDA_CHECK (check.h:40-48). */
+int fr_b200_wait_selftest(int device, unsigned limit_us);
 
 const char *fr_b200_strerror(int status);
 const char *fr_b200_last_error(void);   /* thread-local detail of the last failure */

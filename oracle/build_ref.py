@@ -1,6 +1,6 @@
 """Build the reference's own CPU path from its sources where they lie (never copied into this tree).
 
-Outputs go to oracle/_ref/ only (git-ignored, shipped to the GPU box as built files):
+Outputs go to oracle/_ref/ only (the whole folder is git-ignored; the built files still travel to a GPU box):
   fr_ref_run   rwkv::Model driver: reference model.cpp, tensor.cpp, utils.cpp, kernels/cpu/*,
                kernels/default/*, kernels/shape/*, kernels/export-ncnn/kernels.cpp  +  oracle/ref/cpu_prims.cpp
                (the fp32 CPU primitives the reference lacks)  +  faster-rwkv_b200/backend/fr_run.cpp
@@ -14,7 +14,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 BACKEND = os.path.join(os.path.dirname(HERE), "faster-rwkv_b200", "backend")   # msgpack stand-in + the shared driver
-REF = os.environ.get("FR_REFERENCE_DIR", "/root/reference")
+# the reference tree: FR_REFERENCE_DIR, else a checkout named "reference" beside this repository
+REF = os.environ.get("FR_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 OUT = os.path.join(HERE, "_ref")
 
 

@@ -159,12 +159,19 @@ class OracleModel:
             raise ValueError(f"token id {token_id} out of range")
         return logits
 
+    def advance(self, token_id: int) -> None:
+        """One token without the head: only the state moves (what a prompt token before the last one needs)."""
+        rc = lib().orc_forward(ctypes.byref(self.cfg), self._params, _ptr(self.emb), _ptr(self.state),
+                               int(token_id), None)
+        if rc != 0:
+            raise ValueError(f"token id {token_id} out of range")
+
     def run_seq(self, ids) -> np.ndarray:
         """Seq mode = token loop (kernels/default/model_forward_seq.cpp:34-46); returns the last logits."""
-        out = None
-        for t in ids:
-            out = self.run(int(t))
-        return out
+        ids = list(ids)
+        for t in ids[:-1]:
+            self.advance(int(t))
+        return self.run(int(ids[-1]))
 
     # state accessors in the reference's layout (model.cpp:145-177)
     def state_v4(self) -> np.ndarray:

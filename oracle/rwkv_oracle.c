@@ -246,9 +246,11 @@ int orc_forward(const orc_cfg *c, const float *const *params, const float *emb, 
     if (c->rescale_every > 0 && (l + 1) % c->rescale_every == 0)
       for (int i = 0; i < C; ++i) x[i] *= 0.5f;
   }
-  const float *const *p = params + (size_t)L * ppl;
-  layernorm(x, p[0], p[1], C, tmp);
-  matvec(tmp, p[2], C, c->vocab, logits);
+  if (logits) {   /* a caller that walks a prompt only wants the last token's logits (model_forward_seq.cpp:170-179) */
+    const float *const *p = params + (size_t)L * ppl;
+    layernorm(x, p[0], p[1], C, tmp);
+    matvec(tmp, p[2], C, c->vocab, logits);
+  }
   free(x);
   free(tmp);
   return 0;

@@ -7,6 +7,8 @@ import subprocess
 import numpy as np
 import pytest
 
+import __graft_entry__ as entry  # noqa: E402  (tests/conftest.py puts the repository root on sys.path)
+
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLDEN = os.path.join(HERE, "golden")
 CASES = ["tiny4", "tiny4b", "tiny50", "tiny51", "tiny52"]
@@ -45,7 +47,7 @@ def test_cuda_gate_convention_differs_only_for_gated_versions(orc, synth):
         assert (not np.array_equal(la, lb)) == differs
 
 
-@pytest.mark.skipif(not (os.path.isdir("/root/reference") and
+@pytest.mark.skipif(not (os.path.isdir(entry.reference_dir()) and
                          os.path.exists(os.path.join(os.path.dirname(HERE), "oracle", "_ref", "fr_ref_run"))),
                     reason="needs the reference tree and oracle/_ref/fr_ref_run")
 def test_oracle_against_live_reference_cpu(orc, synth, tmp_path):

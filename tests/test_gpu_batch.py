@@ -45,20 +45,40 @@ def test_many_streams_match_oracle(pkg, orc, synth, name, fmt, B):
 
 
 def test_small_and_large_batches_share_state(pkg, orc, synth):
-    """The persistent kernel (<= 8 streams) and the GEMM path (> 8) read and write the same state slots."""
-    shape, m, ref = _pair(pkg, orc, synth, "tiny4", "fp16", 12)
-    ids = synth.token_ids(shape, 36, seed=3).reshape(3, 12)
-    m.decode(ids[0])                 # 12 streams: GEMM path
-    m.decode(ids[1][:4])             # streams 0..3 one token further: persistent kernel
-    with pytest.raises(pkg.FrB200Error):
-        m.decode(ids[2])             # streams 0..3 are now a token ahead of 4..11
-    got = m.decode(ids[2][:4])
-    for b in range(4):
-        ref.reset()
-        for t in range(3):
-            want = ref.run(int(ids[t, b]))
-        _close(got[b], want, f"stream {b}")
-    m.close()
+    """The persistent kernel (<= 8 streams) and the GEMM path (> 8) read and write the same state slots, and streams
+    that are decoded together need not have seen the same number of tokens (continuous batching: a stream joins a
+    running batch after a reset, a prompt of its own or a few extra steps)."""
+    for name in ("tiny4", "tiny52"):
+        shape, m, ref = _pair(pkg, orc, synth, name, "fp16", 12)
+        ids = synth.token_ids(shape, 48, seed=3).reshape(4, 12)
+        fed = [[] for _ in range(12)]
+
+        def step(row, streams):
+            got = m.decode(ids[row][:streams])
+            for b in range(streams):
+                fed[b].append(int(ids[row, b]))
+            return got
+        step(0, 12)                      # 12 streams: GEMM path
+        step(1, 4)                       # streams 0..3 one token further: persistent kernel
+        got = step(2, 12)                # all together again, 0..3 a token ahead of 4..11
+        m.reset_states(5)                # stream 5 starts over while the others are an odd number of tokens in
+        fed[5] = []
+        got = step(3, 12)
+        for b in (0, 3, 4, 5, 11):
+            ref.reset()
+            for t in fed[b]:
+                want = ref.run(t)
+            _close(got[b], want, f"{name} stream {b} after {len(fed[b])} tokens")
+        # the same through the persistent kernel: streams 0..5, stream 5 one reset behind
+        m.reset_states(2)
+        fed[2] = []
+        got = step(0, 6)
+        for b in (1, 2, 5):
+            ref.reset()
+            for t in fed[b]:
+                want = ref.run(t)
+            _close(got[b], want, f"{name} stream {b} (persistent kernel) after {len(fed[b])} tokens")
+        m.close()
 
 
 def test_greedy_many_streams_on_device(pkg, orc, synth):

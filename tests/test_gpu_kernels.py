@@ -79,3 +79,19 @@ def test_matvec_argument_errors(pkg):
     W = np.zeros((64, 8), np.float32)
     with pytest.raises(pkg.FrB200Error):
         pkg.matvec(W, np.zeros((9, 64), np.float32), 0)      # batch > 8
+
+
+def test_a_bounded_wait_runs_out_and_leaves_the_context_usable(pkg):
+    """Every device-side wait gives up after a limit and reports through a status word.  Here the limit is 1 ms and
+    the barrier is one nothing arrives at: the call must come back with FR_B200_E_TIMEOUT (-6), not hang, and the
+    next kernel on the same context must run as if nothing had happened."""
+    L = pkg.lib()
+    assert L.fr_b200_wait_selftest(0, 1000) == -6
+    assert b"timed out" in L.fr_b200_last_error()
+    assert L.fr_b200_wait_selftest(0, 0) == -1
+    rng = np.random.default_rng(3)
+    W = (rng.standard_normal((256, 48)) / 16).astype(np.float32)
+    x = rng.standard_normal((1, 256)).astype(np.float32)
+    y = pkg.matvec(W, x, 0)
+    want = x.astype(np.float64) @ W.astype(np.float16).astype(np.float64)
+    assert np.abs(y - want).max() < 1e-4

@@ -39,6 +39,17 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(pkg, fmt):
         # same kernels on the same packed data: the tolerance of tests/test_gpu_kernels.py, in practice equality
         assert np.abs(got - want).max() < 2e-6 * np.sqrt(K)
         assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-6
+        # and on its own feet: the float64 product with the weights as the format stores them
+        if fmt == 0:
+            Wq = W.astype(np.float16).astype(np.float64)
+        elif fmt == 1:
+            q, s = pkg.quantize_int8(W)
+            Wq = pkg.dequantize_int8(q, s).astype(np.float64)
+        else:
+            p4, s = pkg.quantize_int4(W)
+            Wq = pkg.dequantize_int4(p4, s).astype(np.float64)
+        exact = x.astype(np.float64) @ Wq
+        assert np.abs(got - exact).max() < 2e-6 * np.sqrt(K) * max(1.0, np.abs(exact).max())
 
 
 def test_sizes_beyond_the_built_in_scratch_are_refused(pkg):
@@ -51,3 +62,7 @@ def test_sizes_beyond_the_built_in_scratch_are_refused(pkg):
         assert b"scratch" in L.fr_b200_noalloc_last_error()
     assert L.fr_b200_matvec_noalloc(d.data_ptr(), 100, 8, 0, d.data_ptr(), 1, d.data_ptr(), 0, None) == -1
     assert L.fr_b200_matvec_noalloc(None, 64, 8, 0, d.data_ptr(), 1, d.data_ptr(), 0, None) == -1
+    # x is read in place with 16-byte loads: a view that starts 4 bytes in is refused on the host, before any launch
+    big = torch.zeros(64 * 8 + 64 + 4, device="cuda")
+    assert L.fr_b200_matvec_noalloc(big.data_ptr(), 64, 8, 0, big.data_ptr() + 4, 1, big.data_ptr(), 0, None) == -1
+    assert b"aligned" in L.fr_b200_noalloc_last_error()
