@@ -58,6 +58,7 @@ struct fr_b200_model {
   uint8_t *d_weights = nullptr;  size_t weights_bytes = 0;
   __half *d_rscale = nullptr;    size_t rscale_n = 0;
   float *d_vecs = nullptr;       size_t vecs_n = 0;
+  __half *d_vecs16 = nullptr;    // fp16 image of d_vecs, kept when LayerNorm / mix vectors are all exact in fp16
   uint8_t *d_emb = nullptr;      int emb_dtype = -1;   // rows kept in the dtype they arrive in
   uint8_t *d_state = nullptr;    size_t state_stride = 0, layer_stride = 0;
   exch_t *d_x = nullptr, *d_xa = nullptr, *d_rwkv = nullptr, *d_kk = nullptr, *d_rr = nullptr;   // tagged exchange vectors
@@ -140,7 +141,7 @@ void plan(fr_b200_model *m) {
     m->mats[name] = s;
   };
   auto vec = [&](const std::string &name, int n) {
-    VecSlot s; s.off = voff; s.n = n; voff += (size_t)(n + 3) / 4 * 4;
+    VecSlot s; s.off = voff; s.n = n; voff += (size_t)(n + 7) / 8 * 8;   // 16-byte aligned in the fp16 image too
     m->vecs[name] = s;
   };
   const size_t rbC = rowblock_bytes(fmt, C), rbF = rowblock_bytes(fmt, F);
@@ -412,7 +413,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   if (!m) return;
   cudaSetDevice(m->device);
   free_scratch(m);
-  void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
+  void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_vecs16, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
                   m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_plain2, m->d_pscale, m->d_seq, m->d_head_phase, m->d_lnvec};
   for (void *p : ptrs)
     if (p) cudaFree(p);
@@ -509,6 +510,30 @@ int fr_b200_finalize(fr_b200_model *m) {
     if (m->v5) { d.lnx_w = vp(a + "ln_x.weight"); d.lnx_b = vp(a + "ln_x.bias"); }
   }
   CU(cudaMemcpy(m->d_layers, layers.data(), sizeof(LayerDev) * m->L, cudaMemcpyHostToDevice));
+  // LayerNorm weights / biases and the mix vectors as fp16, when that loses nothing (files of the fp16 strategy):
+  // the one-stream kernel stages them in half the shared memory
+  bool par16 = m->cfg.act_fp16 != 0;
+  if (const char *e = getenv("FR_B200_PAR16")) par16 = par16 && atoi(e) != 0;
+  if (par16) {
+    std::vector<float> hv(m->vecs_n);
+    CU(cudaMemcpy(hv.data(), m->d_vecs, m->vecs_n * 4, cudaMemcpyDeviceToHost));
+    std::vector<__half> h16(m->vecs_n);
+    for (auto &kv : m->vecs) {
+      const std::string &n = kv.first;
+      const bool staged = n.find("ln1.") != std::string::npos || n.find("ln2.") != std::string::npos ||
+                          n.find("time_mix_") != std::string::npos || n.rfind("ln_out.", 0) == 0;
+      for (int i = 0; i < kv.second.n; ++i) {
+        const float f = hv[kv.second.off + i];
+        const __half h = __float2half_rn(f);
+        h16[kv.second.off + i] = h;
+        if (staged && __half2float(h) != f) par16 = false;
+      }
+    }
+    if (par16) {
+      CU(cudaMalloc((void **)&m->d_vecs16, m->vecs_n * 2));
+      CU(cudaMemcpy(m->d_vecs16, h16.data(), m->vecs_n * 2, cudaMemcpyHostToDevice));
+    }
+  }
   // kernel geometry: as many ring stages as shared memory allows (capped), one CTA per SM
   int optin = 0;
   CU(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device));
@@ -522,14 +547,14 @@ int fr_b200_finalize(fr_b200_model *m) {
   for (int mode = 0; mode <= max_mode; ++mode) {
     int st = 0;
     for (int s = want; s >= 2; --s)
-      if (decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, s) <= (size_t)optin) { st = s; break; }
+      if (decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, s, m->d_vecs16 != nullptr) <= (size_t)optin) { st = s; break; }
     if (st == 0) {
       if (m->cfg.max_batch > MAX_B && mode > 0) { m->n_stages[mode] = 0; continue; }   // such batches take the GEMM path
       return fail(FR_B200_E_UNSUPPORTED, "model too wide for shared memory at this batch size (max_batch " +
                                              std::to_string(m->cfg.max_batch) + ")");
     }
     m->n_stages[mode] = st;
-    m->smem[mode] = decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, st);
+    m->smem[mode] = decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, st, m->d_vecs16 != nullptr);
     int g = 0;
     CU(decode_max_grid(m->fmt, mode, m->smem[mode], m->device, &g));
     if (g == 0) return fail(FR_B200_E_UNSUPPORTED, "decode kernel does not fit on an SM");
@@ -608,6 +633,7 @@ static int decode_impl(fr_b200_model *m, const int32_t *ids_host, const unsigned
   p.emb = m->d_emb; p.emb_f32 = m->emb_dtype == FR_B200_T_F32; p.layers = m->d_layers; p.phases = m->d_phases;
   p.lnout_w = m->d_vecs + m->vecs["ln_out.weight"].off;
   p.lnout_b = m->d_vecs + m->vecs["ln_out.bias"].off;
+  p.vecs16 = m->d_vecs16; p.vecs32 = m->d_vecs;
   p.x = m->d_x; p.xa = m->d_xa; p.rwkv = m->d_rwkv; p.kk = m->d_kk; p.rr = m->d_rr; p.logits = m->d_out;
   // Exchange words carry 8-bit tags: unambiguous only against the write just before them in the same slot.  Slots of
   // streams the previous launch did not write, or words a failed launch left half written, could alias: start clean.

@@ -55,18 +55,20 @@ __host__ __device__ inline size_t xs_halfs_needed(int C, int F, int version, int
   size_t b = F;
   return (a > b ? a : b) * NB * NT;
 }
-// one stream and a model narrow enough for the register-resident LayerNorm: parameters are staged in shared memory
-template <int NB, int NT> __host__ __device__ inline size_t par_bytes(int C) {
-  return (NB == 2 && (C >> 2) <= XR * NCONS) ? (size_t)PAR_VECS * C * 4 : 0;
+// one stream and a model narrow enough for the register-resident LayerNorm: parameters are staged in shared memory,
+// as fp16 when every LayerNorm / mix vector of the model is exact in fp16 (a "cuda fp16" file): half the space, which
+// buys another ring slot for the weight stream
+template <int NB, int NT> __host__ __device__ inline size_t par_bytes(int C, int par16) {
+  return (NB == 2 && (C >> 2) <= XR * NCONS) ? (size_t)PAR_VECS * C * (par16 ? 2 : 4) : 0;
 }
 
 template <int NB, int NT>
-__host__ __device__ inline size_t smem_layout(int fmt, int C, int F, int version, int n_stages, size_t *off_red,
+__host__ __device__ inline size_t smem_layout(int fmt, int C, int F, int version, int n_stages, int par16, size_t *off_red,
                                               size_t *off_par, size_t *off_xs, size_t *off_ring) {
   size_t o = 1024;  // barriers + flags + LN scratch
   *off_red = o;   o += sizeof(float) * 3 * NW * red_n<NB, NT>() * (NB == 2 ? 2 : 1);
   o = align_up(o, 128);
-  *off_par = o;   o += par_bytes<NB, NT>(C);
+  *off_par = o;   o += par_bytes<NB, NT>(C, par16);
   *off_xs = o;    o += xs_halfs_needed(C, F, version, NB, NT) * 2;
   o = align_up(o, 1024);
   *off_ring = o;  o += (size_t)n_stages * slot_bytes(fmt);
@@ -436,14 +438,18 @@ __device__ __forceinline__ LnArgs ln_args(const DecodeParams &p, const PhaseDev 
 // ahead of the consumers; the LayerNorm prologue waits on the barrier.
 __device__ __forceinline__ void ln_stage_params(Ctx &cx, const LnArgs &a) {
   const DecodeParams &p = *cx.p;
-  float *par = cx.sm.par;
-  const uint32_t vb = (uint32_t)p.C * 4u;
+  uint8_t *par = reinterpret_cast<uint8_t *>(cx.sm.par);
+  const uint32_t vb = (uint32_t)p.C * (p.vecs16 ? 2u : 4u);   // bytes per staged vector
   const uint32_t sxb = a.nvec > 0 ? (uint32_t)p.C * (p.act_fp16 ? 2u : 4u) : 0u;
+  // the fp16 image of a vector sits at the same element offset in the fp16 copy of the vector blob
+  auto src = [&](const float *v) -> const void * {
+    return p.vecs16 ? static_cast<const void *>(p.vecs16 + (v - p.vecs32)) : static_cast<const void *>(v);
+  };
   mbar_expect_tx(cx.sm.par_bar, vb * (2u + (uint32_t)a.nvec) + sxb);
-  bulk_g2s(par, a.ln_w, vb, cx.sm.par_bar);
-  bulk_g2s(par + p.C, a.ln_b, vb, cx.sm.par_bar);
-  for (int v = 0; v < a.nvec; ++v) bulk_g2s(par + (2 + v) * p.C, a.mix[v], vb, cx.sm.par_bar);
-  if (a.nvec > 0) bulk_g2s(par + 6 * p.C, a.sx_rd, sxb, cx.sm.par_bar);
+  bulk_g2s(par, src(a.ln_w), vb, cx.sm.par_bar);
+  bulk_g2s(par + vb, src(a.ln_b), vb, cx.sm.par_bar);
+  for (int v = 0; v < a.nvec; ++v) bulk_g2s(par + (2 + v) * vb, src(a.mix[v]), vb, cx.sm.par_bar);
+  if (a.nvec > 0) bulk_g2s(par + 6 * vb, a.sx_rd, sxb, cx.sm.par_bar);
 }
 
 // LayerNorm + token-shift mix for ONE stream of a model with n_embd <= 4 * XR * NCONS: the latency-critical
@@ -497,28 +503,30 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   var = var > 0.f ? var : 0.f;
   const float mean = piv + m, rstd = rsqrtf(var + 1e-5f);
   if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // trace
-  const float *par = cx.sm.par;
+  const uint8_t *par = reinterpret_cast<const uint8_t *>(cx.sm.par);
+  const bool par16 = p.vecs16 != nullptr;
+  const uint32_t vb = (uint32_t)p.C * (par16 ? 2u : 4u);
+  auto half4 = [](const uint8_t *base, int i4) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(base + (size_t)i4 * 8);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  };
+  auto par4 = [&](int v, int i4) {
+    return par16 ? half4(par + v * vb, i4) : *reinterpret_cast<const float4 *>(par + v * vb + (size_t)i4 * 16);
+  };
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
     const bool valid = cx.tid + r * NCONS < n4;
     const int i4 = valid ? cx.tid + r * NCONS : cx.lane & 7;   // lanes without data still make the (warp-wide) call
     if (r * NCONS + (cx.tid & ~31) < n4) {                      // warp-uniform
-      const float4 gw = *reinterpret_cast<const float4 *>(par + 0 * p.C + i4 * 4);
-      const float4 gb = *reinterpret_cast<const float4 *>(par + 1 * p.C + i4 * 4);
+      const float4 gw = par4(0, i4);
+      const float4 gb = par4(1, i4);
       float4 mx4[4], sx = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int v = 0; v < 4; ++v)
-        if (v < a.nvec) mx4[v] = *reinterpret_cast<const float4 *>(par + (2 + v) * p.C + i4 * 4);
-      if (a.nvec > 0) {
-        if (p.act_fp16) {
-          const uint2 u = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(par + 6 * p.C) + i4 * 4);
-          const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
-          const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
-          sx = make_float4(lo.x, lo.y, hi.x, hi.y);
-        } else {
-          sx = *reinterpret_cast<const float4 *>(par + 6 * p.C + i4 * 4);
-        }
-      }
+        if (v < a.nvec) mx4[v] = par4(2 + v, i4);
+      if (a.nvec > 0) sx = p.act_fp16 ? half4(par + 6 * vb, i4) : *reinterpret_cast<const float4 *>(par + 6 * vb + (size_t)i4 * 16);
       ln_emit<NB, NT>(cx, ph, a.nvec, a.sx_wr, a.item0, i4, 0, xv[r], mean, rstd, gw, gb, mx4, sx, valid);
     }
   }
@@ -871,19 +879,32 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, int pi, i
   const uint32_t vstride_b = plane_b * NT;
   const unsigned tag = phase_tag(p, pi);
   const int g = cx.lane >> 2, q = cx.lane & 3;
-  const int erow = cx.tid / SB, eb = cx.tid % SB;
-  const bool epi_thread = cx.tid < ROWS * SB && eb < p.B;
+  // Phases with one matrix per row block (everything but the fused K,V,R of RWKV-4) take up to three row blocks per
+  // barrier: their partial sums go to the three slots the fused phase uses for its three matrices, and thread
+  // (slot, row, stream) runs the epilogue of row block `slot` of the batch.  The barrier, the cross-warp sum and the
+  // epilogue's global stores are paid once per batch instead of once per 16 rows.
+  constexpr int SLOT_THREADS = ROWS * SB;
+  constexpr int MAX_GROUP = NCONS / SLOT_THREADS < 3 ? NCONS / SLOT_THREADS : 3;
+  const int group = ph.n_sub == 1 ? MAX_GROUP : 1;
+  const int eslot = cx.tid / SLOT_THREADS, etid = cx.tid - eslot * SLOT_THREADS;
+  const int erow = etid / SB, eb = etid % SB;
   const bool prof = p.prof != nullptr && cx.tid == 0;
   const uint32_t xs_a = smem_u32(cx.sm.xs), ring_a = smem_u32(cx.sm.ring), red_a = smem_u32(cx.sm.red);
   const int last_kt = ph.K - (nst - 1) * KT;
   unsigned long long best = 0;   // head phase: packed arg-max over this thread's logits
-  for (int it = first; it < ph.n_items; it += cx.G) {
+  for (int it0 = first; it0 < ph.n_items; it0 += cx.G * group) {
+    int n_in = 1;
+    while (n_in < group && it0 + n_in * cx.G < ph.n_items) ++n_in;
+    const int eit = it0 + eslot * cx.G;                       // row block this thread finishes
+    const bool epi_thread = eslot < n_in && eb < p.B;
     EpiIn epi_in;
-    if (epi_thread) epilogue_prefetch<FMT>(cx, ph, pi, it, erow, eb, epi_in);
+    if (epi_thread) epilogue_prefetch<FMT>(cx, ph, pi, eit, erow, eb, epi_in);
     const uint32_t red_it = red_a + (NB == 2 ? cx.red_buf * RED_BUF : 0u);
-    for (int u = 0; u < ph.n_sub; ++u) {
+    const int n_mat = ph.n_sub == 1 ? n_in : ph.n_sub;        // matrices multiplied before the barrier
+    for (int u = 0; u < n_mat; ++u) {
+      const int it = ph.n_sub == 1 ? it0 + u * cx.G : it0;
       // which operand vector feeds this matrix
-      int vec = u;
+      int vec = ph.n_sub == 1 ? 0 : u;
       if (ph.kind == PH_FFN_KR) vec = it < ph.split[0] ? 0 : 1;
       else if (ph.kind == PH5_KVRG) vec = it / (p.C / ROWS);
       const uint32_t xv = xs_a + (uint32_t)vec * vstride_b;
@@ -940,25 +961,27 @@ __device__ __forceinline__ void run_items(Ctx &cx, const PhaseDev &ph, int pi, i
 #pragma unroll
       for (int u = 0; u < 3; ++u) {
         if (u < ph.n_sub) {
+          const int slot = ph.n_sub == 1 ? eslot : u;
           float s = 0.f;
 #pragma unroll
-          for (int w = 0; w < NW; ++w) s += lds_f32(red_it + (uint32_t)((u * NW + w) * RN + cx.tid) * 4u);
+          for (int w = 0; w < NW; ++w) s += lds_f32(red_it + (uint32_t)((slot * NW + w) * RN + etid) * 4u);
           if (FMT == FMT_INT8) s *= epi_in.rscale[u];
           val[u] = s;
         }
       }
-      epilogue(cx, ph, pi, tag, it, erow, eb, val, epi_in);
-      if (ph.kind == PH_HEAD && p.amax && it * ROWS + erow < p.V) {
+      epilogue(cx, ph, pi, tag, eit, erow, eb, val, epi_in);
+      if (ph.kind == PH_HEAD && p.amax && eit * ROWS + erow < p.V) {
         unsigned u = __float_as_uint(val[0]);
         u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-        const unsigned long long w = ((unsigned long long)u << 32) | (0xffffffffu - (unsigned)(it * ROWS + erow));
+        const unsigned long long w = ((unsigned long long)u << 32) | (0xffffffffu - (unsigned)(eit * ROWS + erow));
         best = w > best ? w : best;
       }
     }
     if (NB == 2) cx.red_buf ^= 1u;
     else bar_sync(BAR_CONS, NCONS);   // the partial sums are read: the next row block may overwrite them
   }
-  if (ph.kind == PH_HEAD && p.amax && epi_thread && best) atomicMax(p.amax + eb, best);
+  // (the head phase has one matrix per row block: every thread with eslot < 3 may hold a candidate)
+  if (ph.kind == PH_HEAD && p.amax && eslot < MAX_GROUP && eb < p.B && best) atomicMax(p.amax + eb, best);
 }
 
 // ---- v5 state update + readout: units of (stream, head, 16 value columns) ----------------------------
@@ -1158,8 +1181,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
   cx.slot = 0; cx.parity = 0; cx.wait_ns = 0; cx.prof_phase = 0; cx.red_buf = 0; cx.ready = false;
   cx.slot_b = slot_bytes(FMT);
   size_t o_red, o_par, o_xs, o_ring;
-  smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, &o_red, &o_par, &o_xs, &o_ring);
-  cx.sm.par = par_bytes<NB, NT>(p.C) ? reinterpret_cast<float *>(smem + o_par) : nullptr;
+  smem_layout<NB, NT>(FMT, p.C, p.F, p.version, p.n_stages, p.vecs16 != nullptr, &o_red, &o_par, &o_xs, &o_ring);
+  cx.sm.par = par_bytes<NB, NT>(p.C, p.vecs16 != nullptr) ? reinterpret_cast<float *>(smem + o_par) : nullptr;
   cx.par_parity = 0;
   cx.sm.par_bar = reinterpret_cast<uint64_t *>(smem + 200);
   cx.sm.par_free = reinterpret_cast<uint64_t *>(smem + 208);
@@ -1224,12 +1247,12 @@ cudaError_t max_grid_t(size_t smem, int device, int *grid) {
 }  // namespace
 
 // mode: 0 = one stream, 1 = up to 4 streams, 2 = up to 8 streams
-size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages) {
+size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages, int par16) {
   size_t a, b, c, d;
   switch (mode) {
-    case 0: return smem_layout<2, 1>(fmt, C, F, version, n_stages, &a, &b, &c, &d);
-    case 1: return smem_layout<8, 1>(fmt, C, F, version, n_stages, &a, &b, &c, &d);
-    default: return smem_layout<8, 2>(fmt, C, F, version, n_stages, &a, &b, &c, &d);
+    case 0: return smem_layout<2, 1>(fmt, C, F, version, n_stages, par16, &a, &b, &c, &d);
+    case 1: return smem_layout<8, 1>(fmt, C, F, version, n_stages, par16, &a, &b, &c, &d);
+    default: return smem_layout<8, 2>(fmt, C, F, version, n_stages, par16, &a, &b, &c, &d);
   }
 }
 

@@ -74,6 +74,11 @@ struct DecodeParams {
   int emb_f32;
   const LayerDev *layers;
   const float *lnout_w, *lnout_b;
+  // optional: fp16 image of the whole per-layer vector blob (vecs32 = its fp32 original, same element offsets), given
+  // when every LayerNorm weight / bias and token-shift mix vector is exact in fp16; the one-stream kernel then stages
+  // these vectors in shared memory as fp16
+  const __half *vecs16;
+  const float *vecs32;
   const PhaseDev *phases;
   // Residual stream, two copies: x as the ffn value phase (or nothing yet, at layer 0) left it, xa as the attention
   // output phase left it.  A phase never overwrites the copy that CTAs of the phase before it may still be reading.
@@ -191,7 +196,8 @@ cudaError_t launch_transpose_f16(const __half *src, int K, int N, __half *dst, c
 // ---- launchers implemented in the .cu files ------------------------------------------------------
 // mode = how many streams one launch carries: 0 -> 1, 1 -> up to 4, 2 -> up to 8
 inline int decode_mode(int batch) { return batch == 1 ? 0 : batch <= 4 ? 1 : 2; }
-size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages);
+// par16: the launch will carry DecodeParams::vecs16 (LayerNorm parameters staged as fp16)
+size_t decode_smem_bytes(int fmt, int mode, int C, int F, int version, int n_stages, int par16 = 0);
 cudaError_t launch_decode(const DecodeParams &p, int mode, int grid, size_t smem, cudaStream_t st);
 cudaError_t decode_max_grid(int fmt, int mode, size_t smem, int device, int *grid);
 // packed arg-max word = {order-preserving image of the fp32 logit, 0xFFFFFFFF - index}: a 64-bit max picks the

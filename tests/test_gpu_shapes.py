@@ -72,7 +72,8 @@ def _build(pkg, orc, shape, fmt, max_batch=1, seed=0):
 
 
 def _state_check(m, ref, shape, what, slot=0):
-    """Recurrent state of one stream against the oracle's; returns the worst distances."""
+    """Recurrent state of one stream against the oracle's; returns the worst distances (max-abs relative to the
+    largest entry for the two running sums aa and bb)."""
     st = m.states(slot)
     C, worst = shape.n_embd, (0.0, 0.0)
     if str(shape.version) == "4":
@@ -83,6 +84,13 @@ def _state_check(m, ref, shape, what, slot=0):
                     # pp starts at -1e30 and follows max(pp + w, k): compare where it has left the initial value
                     live = want[l, j] > -1e29
                     d = _close(st[l][j][live], want[l, j][live], f"{what} pp[{l}]")
+                elif j in (1, 2):
+                    # aa and bb are running sums of exp-weighted values: they grow with the number of tokens, so the
+                    # max-abs bound scales with their largest entry (the relative L2 bound does not)
+                    e, r = _dist(st[l][j], want[l, j])
+                    big = max(1.0, float(np.abs(want[l, j]).max()))
+                    assert r < REL_TOL and e < ABS_TOL * big, f"{what} state[{l}][{j}]: max-abs {e:.3e} (largest entry {big:.1f}), rel-L2 {r:.3e}"
+                    d = (e / big, r)
                 else:
                     d = _close(st[l][j].astype(np.float32), want[l, j], f"{what} state[{l}][{j}]")
                 worst = (max(worst[0], d[0]), max(worst[1], d[1]))
