@@ -39,6 +39,8 @@ struct MatrixSlot {       // where a projection matrix lives inside the packed w
   bool has_plain = false; // seq mode keeps the matrix a second time as W^T [N, K] fp16 row-major
   size_t plain_off = 0;   // offset of that copy in halfs
   size_t pscale_off = 0;  // int8: offset of the [N] output-row scales that go with the copy (the copy holds the codes)
+  size_t q_off = 0;       // int8 / int4: byte offset of the row-major packed copy ([N, K] codes or [N, K/2] nibbles)
+  size_t qs_off = 0;      // int4: offset (halfs) of its [N, K/32] group scales
 };
 
 struct VecSlot {
@@ -76,6 +78,11 @@ struct fr_b200_model {
   __half *d_plain = nullptr;     size_t plain_halfs = 0;   // fp16: W^T; int8: the integer codes as fp16; int4: hi(q * scale)
   __half *d_plain2 = nullptr;    // int4: lo(q * scale), what fp16 rounding of the dequantised weight lost
   __half *d_pscale = nullptr;    size_t pscale_halfs = 0;  // int8: per output row scales, per matrix
+  // int8 / int4: every projection a second time in its packed interchange form, row-major (one row per output
+  // channel): what the few-row GEMM streams for prompts and for decode of more than 8 streams
+  uint8_t *d_qcopy = nullptr;    size_t qcopy_bytes = 0;
+  __half *d_qscale = nullptr;    size_t qscale_halfs = 0;
+  bool row_copies = true;        // keep the copies the GEMM path needs (FR_B200_ROW_COPIES=0: decode-only model)
   uint8_t *d_seq = nullptr;      size_t seq_bytes = 0; int seq_T = 0;
   PhaseDev *d_head_phase = nullptr;   // the head as a stand-alone matvec phase
   // greedy runs of many streams: two decode steps captured as a CUDA graph and replayed (the step is ~170 launches)
@@ -203,19 +210,29 @@ void plan(fr_b200_model *m) {
   phase(PH_HEAD, 0, C, nbV, 1, woff, roff);
   woff += (size_t)nbV * rbC; roff += (size_t)nbV * ROWS;
   m->weights_bytes = woff; m->rscale_n = roff; m->vecs_n = voff;
-  m->plain_halfs = 0; m->pscale_halfs = 0;
-  // the GEMM path needs every projection again as W^T fp16 (dequantised for int8 / int4): seq mode of RWKV-5.x fp16
-  // models, and decode of more than 8 streams at once for every model (then the head too: all rows want logits)
+  m->plain_halfs = 0; m->pscale_halfs = 0; m->qcopy_bytes = 0; m->qscale_halfs = 0;
+  // The GEMM path (prompts, and decode of more than 8 streams at once) reads the projections row by output channel:
+  // fp16 models keep W^T fp16 [N, K] (with the head when more than 8 streams can be decoded: all rows want logits;
+  // a prompt's head is a matvec over the last token), made at load for RWKV-5.x and for max_batch > 8, else on the
+  // first long prompt; int8 / int4 models keep the packed codes row-major [N, K] / [N, K/2] (+ scales), the same
+  // bytes as the streaming tiles, which the GEMM expands in shared memory.
   const bool big = m->cfg.max_batch > MAX_B;
-  if ((m->v5 && fmt == FMT_FP16) || big)
-    for (auto &kv : m->mats) {
-      if (kv.first == "head.weight" && !big) continue;   // seq mode: the head is a matvec over the last token
-      kv.second.has_plain = true;
-      kv.second.plain_off = m->plain_halfs;
-      m->plain_halfs += ((size_t)kv.second.K * kv.second.N + 127) / 128 * 128;
-      kv.second.pscale_off = m->pscale_halfs;
-      if (fmt == FMT_INT8) m->pscale_halfs += ((size_t)kv.second.N + 7) / 8 * 8;
+  for (auto &kv : m->mats) {
+    MatrixSlot &ms = kv.second;
+    if (fmt == FMT_FP16) {
+      if (kv.first == "head.weight" && !big) continue;
+      ms.has_plain = true;
+      ms.plain_off = m->plain_halfs;
+      m->plain_halfs += ((size_t)ms.K * ms.N + 127) / 128 * 128;
+    } else if (m->row_copies) {
+      ms.q_off = m->qcopy_bytes;
+      m->qcopy_bytes += ((size_t)ms.N * (fmt == FMT_INT8 ? ms.K : ms.K / 2) + 255) / 256 * 256;
+      ms.pscale_off = m->pscale_halfs;
+      if (fmt == FMT_INT8) m->pscale_halfs += ((size_t)ms.N + 7) / 8 * 8;
+      ms.qs_off = m->qscale_halfs;
+      if (fmt == FMT_INT4) m->qscale_halfs += ((size_t)ms.N * (ms.K / 32) + 7) / 8 * 8;
     }
+  }
   m->stream_bytes = (long long)woff + (fmt == FMT_INT8 ? (long long)roff * 2 : 0);
 }
 
@@ -254,9 +271,9 @@ int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int d
       CU(launch_quant_int8(w32, s.K, s.N, reinterpret_cast<int8_t *>(m->d_scratch[2]), reinterpret_cast<__half *>(m->d_scratch[3]), 0));
       CU(launch_pack(FMT_INT8, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
                      s.item_stride, m->d_rscale + s.rscale_off, s.rscale_stride, 0));
-      if (s.has_plain && m->d_plain) {
-        // the codes are [N, K] already and exact in fp16; the row scale is applied to the accumulator
-        CU(launch_i8_to_f16(reinterpret_cast<const int8_t *>(m->d_scratch[2]), m->d_plain + s.plain_off, n, 0));
+      if (m->d_qcopy) {
+        // the codes are [N, K] already; the row scale is applied to the GEMM's accumulator
+        CU(cudaMemcpy(m->d_qcopy + s.q_off, m->d_scratch[2], n, cudaMemcpyDeviceToDevice));
         CU(cudaMemcpy(m->d_pscale + s.pscale_off, m->d_scratch[3], (size_t)s.N * 2, cudaMemcpyDeviceToDevice));
       }
     } else {
@@ -265,17 +282,9 @@ int upload_matrix(fr_b200_model *m, const MatrixSlot &s, const void *data, int d
       CU(launch_quant_int4(w32, s.K, s.N, reinterpret_cast<uint8_t *>(m->d_scratch[2]), reinterpret_cast<__half *>(m->d_scratch[3]), 0));
       CU(launch_pack(FMT_INT4, m->d_scratch[2], reinterpret_cast<const __half *>(m->d_scratch[3]), s.K, s.N, dst,
                      s.item_stride, nullptr, 0, 0));
-      if (s.has_plain && m->d_plain) {
-        // q * scale needs up to 14 significant bits: kept as an fp16 pair (hi, lo), exact
-        if ((rc = ensure_scratch(m, 0, n * 4))) return rc;   // the input is packed: its buffer takes the dequantised matrix
-        CU(launch_dequant_int4(reinterpret_cast<const uint8_t *>(m->d_scratch[2]), reinterpret_cast<const __half *>(m->d_scratch[3]),
-                               s.K, s.N, reinterpret_cast<float *>(m->d_scratch[0]), 0));
-        if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
-        if ((rc = ensure_scratch(m, 2, n * 2))) return rc;
-        CU(launch_f32_split_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]),
-                                reinterpret_cast<__half *>(m->d_scratch[2]), n, 0));
-        CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[1]), s.K, s.N, m->d_plain + s.plain_off, 0));
-        CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[2]), s.K, s.N, m->d_plain2 + s.plain_off, 0));
+      if (m->d_qcopy) {
+        CU(cudaMemcpy(m->d_qcopy + s.q_off, m->d_scratch[2], n / 2, cudaMemcpyDeviceToDevice));
+        CU(cudaMemcpy(m->d_qscale + s.qs_off, m->d_scratch[3], (size_t)s.N * (s.K / 32) * 2, cudaMemcpyDeviceToDevice));
       }
     }
   }
@@ -362,6 +371,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   m->gate = v == FR_B200_V5_1 || v == FR_B200_V5_2;
   m->device = cfg->device;
   m->par.assign(cfg->max_batch, 0u);
+  if (const char *e = getenv("FR_B200_ROW_COPIES")) m->row_copies = atoi(e) != 0;
   if ((m->C + prop.multiProcessorCount - 1) / prop.multiProcessorCount > 128) {
     delete m;
     return fail(FR_B200_E_UNSUPPORTED, "n_embd too large for the shift-state stash");
@@ -389,8 +399,10 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_v5buf, (size_t)5 * B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
   if (!rc) rc = alloc((void **)&m->d_amax, (size_t)B * 8);
-  if (!rc && m->plain_halfs) rc = alloc((void **)&m->d_plain, m->plain_halfs * 2);
-  if (!rc && m->plain_halfs && m->fmt == FMT_INT4) rc = alloc((void **)&m->d_plain2, m->plain_halfs * 2);
+  // fp16 W^T copies now for RWKV-5.x (seq kernels) and for models that decode more than 8 streams; else on demand
+  if (!rc && m->plain_halfs && m->row_copies && (m->v5 || cfg->max_batch > MAX_B)) rc = alloc((void **)&m->d_plain, m->plain_halfs * 2);
+  if (!rc && m->qcopy_bytes) rc = alloc((void **)&m->d_qcopy, m->qcopy_bytes);
+  if (!rc && m->qscale_halfs) rc = alloc((void **)&m->d_qscale, m->qscale_halfs * 2);
   if (!rc && m->pscale_halfs) rc = alloc((void **)&m->d_pscale, m->pscale_halfs * 2);
   if (!rc) rc = alloc((void **)&m->d_head_phase, sizeof(PhaseDev));
   if (!rc) rc = alloc((void **)&m->d_ctl, sizeof(GreedyCtl));
@@ -414,7 +426,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   cudaSetDevice(m->device);
   free_scratch(m);
   void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_vecs16, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
-                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_plain2, m->d_pscale, m->d_seq, m->d_head_phase, m->d_lnvec};
+                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_plain2, m->d_pscale, m->d_qcopy, m->d_qscale, m->d_seq, m->d_head_phase, m->d_lnvec};
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);
@@ -603,8 +615,37 @@ int align_parity(fr_b200_model *m, int batch, cudaStream_t st) {
 int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids, int R, cudaStream_t st);
 // more streams than the persistent kernel carries (or a model too wide for that many): the GEMM path decodes them
 bool decode_by_rows(const fr_b200_model *m, int batch) { return batch > MAX_B || m->n_stages[decode_mode(batch)] == 0; }
+// fp16 models that were created without the W^T copies build them from the streaming tiles (exact: the tiles hold
+// the same fp16 values) the first time the GEMM path is asked for
+int ensure_row_copies(fr_b200_model *m) {
+  if (m->d_plain || m->d_qcopy) return 0;
+  if (m->fmt != FMT_FP16 || !m->row_copies || !m->plain_halfs) return fail(FR_B200_E_UNSUPPORTED, "the model keeps no row copies for the GEMM path");
+  CU(cudaDeviceSynchronize());
+  cudaError_t e = cudaMalloc((void **)&m->d_plain, m->plain_halfs * 2);
+  if (e != cudaSuccess) { m->d_plain = nullptr; return fail(FR_B200_E_NOMEM, std::string("cudaMalloc(row copies): ") + cudaGetErrorString(e)); }
+  for (auto &kv : m->mats) {
+    const MatrixSlot &s = kv.second;
+    if (!s.has_plain) continue;
+    const size_t n = (size_t)s.K * s.N;
+    int rc;
+    if ((rc = ensure_scratch(m, 0, n * 4))) return rc;
+    if ((rc = ensure_scratch(m, 1, n * 2))) return rc;
+    CU(launch_unpack(FMT_FP16, m->d_weights + s.tile_off, s.item_stride, nullptr, 0, s.K, s.N, reinterpret_cast<float *>(m->d_scratch[0]), 0));
+    CU(launch_f32_to_f16(reinterpret_cast<const float *>(m->d_scratch[0]), reinterpret_cast<__half *>(m->d_scratch[1]), n, 0));
+    CU(launch_transpose_f16(reinterpret_cast<const __half *>(m->d_scratch[1]), s.K, s.N, m->d_plain + s.plain_off, 0));
+  }
+  CU(cudaDeviceSynchronize());
+  free_scratch(m);
+  return 0;
+}
+bool rows_path_built(const fr_b200_model *m) { return m->d_plain || m->d_qcopy; }
 int rows_decode_check(fr_b200_model *m, const int32_t *ids_host, int batch, cudaStream_t st) {
-  if (!m->d_plain) return fail(FR_B200_E_UNSUPPORTED, "this batch size needs a model created with max_batch > 8");
+  if (m->fmt == FMT_FP16 && !m->mats["head.weight"].has_plain)
+    return fail(FR_B200_E_UNSUPPORTED, "this batch size needs a model created with max_batch > 8");
+  {
+    int rc = ensure_row_copies(m);
+    if (rc) return rc;
+  }
   for (int b = 0; b < batch; ++b)
     if (ids_host && (ids_host[b] < 0 || ids_host[b] >= m->V)) return fail(FR_B200_E_ARG, "token id out of range");
   return align_parity(m, batch, st);
@@ -920,14 +961,21 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   if (ids != d_ids) CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
   CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
   auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
-  auto wt = [&](const std::string &n) -> const __half * { return m->d_plain + m->mats[n].plain_off; };
+  const bool quant = m->fmt != FMT_FP16;
   auto mk = [&](const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
                 float scale, const __half *A2 = nullptr) -> GemmArgs {
     GemmArgs ga;
     memset(&ga, 0, sizeof(ga));
-    ga.A = A; ga.A2 = A2; ga.Bt = wt(w); ga.M = T;
-    if (m->d_plain2) ga.Bt2 = m->d_plain2 + m->mats[w].plain_off;
-    if (m->d_pscale) ga.col_scale = m->d_pscale + m->mats[w].pscale_off; ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
+    const MatrixSlot &ms = m->mats[w];
+    ga.A = A; ga.A2 = A2; ga.M = T;
+    if (quant) {
+      ga.Wq = m->d_qcopy + ms.q_off; ga.wfmt = m->fmt;
+      if (m->fmt == FMT_INT4) ga.wq_scale = m->d_qscale + ms.qs_off;
+      else ga.col_scale = m->d_pscale + ms.pscale_off;
+    } else {
+      ga.Bt = m->d_plain + ms.plain_off;
+    }
+    ga.N = N; ga.K = K; ga.epi = epi; ga.out = out; ga.ldo = N; ga.aux0 = aux0; ga.aux1 = aux1;
     ga.scale = scale; ga.status = m->out_status();
     return ga;
   };
@@ -1062,7 +1110,15 @@ int fr_b200_run_seq(fr_b200_model *m, int slot, const int32_t *ids, int n, float
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int seq_min = 2;   // shorter prompts take the token loop
   if (const char *e = getenv("FR_B200_SEQ_MIN")) seq_min = atoi(e);
-  if (m->d_plain && n >= seq_min) {
+  // fp16 RWKV-4 models build their row copies when the first prompt of 32 tokens or more arrives
+  bool by_rows = rows_path_built(m) && n >= seq_min;
+  if (!by_rows && m->fmt == FMT_FP16 && m->row_copies && m->plain_halfs && n >= std::max(seq_min, 32)) {
+    CU(cudaSetDevice(m->device));
+    int rc = ensure_row_copies(m);
+    if (rc) return rc;
+    by_rows = true;
+  }
+  if (by_rows) {
     CU(cudaSetDevice(m->device));
     for (int i = 0; i < n; ++i)
       if (ids[i] < 0 || ids[i] >= m->V) return fail(FR_B200_E_ARG, "token id out of range");

@@ -124,6 +124,10 @@ struct GemmArgs {
   const __half *Bt;    // [N, K] row-major (the weight matrix transposed: one row per output channel)
   const __half *Bt2;   // optional [N, K]: what rounding the weights to fp16 lost (int4: q * scale needs 14 bits); third pass
   const __half *col_scale;   // optional [N]: acc *= col_scale[n] before the epilogue (int8: Bt holds the integer codes)
+  // quantised weights in packed form instead of Bt (few-row GEMM that expands them in shared memory):
+  const uint8_t *Wq;         // wfmt FMT_INT8: codes [N, K] int8;  FMT_INT4: [N, K/2], nibble = q + 8, even k low
+  const __half *wq_scale;    // FMT_INT4: group scales [N, K/32] (int8 row scales go in col_scale)
+  int wfmt;
   int M, N, K;         // K a multiple of 64
   int epi;
   void *out;           // [M, ldo]

@@ -516,6 +516,225 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The few-row GEMM for quantised weights: the weight operand is read in its packed form (int8 codes [N, K], or int4
+// nibbles [N, K/2] with fp16 group scales [N, K/32]: the bytes a step has to stream) and expanded to the K-major fp16
+// tile the tensor core wants inside the kernel, by four warps that do nothing else.  Per K slice of 64 inputs:
+//   warp 0      TMA: the packed 128-row weight tile (8 KB int8 / 4 KB int4) + the X tile(s) into a ring slot
+//   warps 6..9  expanders: packed tile -> 128 x 64 fp16 in the 128-byte-swizzled layout of a TMA-loaded tile
+//               (int8: the integer code, exact in fp16, the row scale is applied to the accumulator;
+//                int4: hi = fp16(q * scale) and lo = q * scale - hi, an exact pair), double-buffered
+//   warp 1      MMA: acc += W_hi X_hi (+ W_hi X_lo) (+ W_lo X_hi)
+//   warps 2..5  epilogue, as in gemm_wt_kernel
+// A ring slot is free again when the expanders have read its weight bytes and the MMAs its X tiles; an expanded
+// buffer when the MMAs that read it have retired.  Shared-memory writes of the expanders are made visible to the
+// tensor core's (asynchronous) reads with fence.proxy.async before the barrier arrive.
+constexpr int WQ_THREADS = 320;
+constexpr int WQ_NE = 2;   // expanded buffers
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+template <int BN, int FMT>
+__global__ void __launch_bounds__(WQ_THREADS, 1)
+gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
+  constexpr uint32_t X_BYTES = BN * GBK * 2;
+  constexpr uint32_t WQ_BYTES = FMT == FMT_INT8 ? GBM * GBK : GBM * GBK / 2;   // packed weight tile
+  constexpr uint32_t ROW_B = WQ_BYTES / GBM;                                   // packed bytes per row: 64 / 32
+  constexpr uint32_t E_BYTES = (FMT == FMT_INT4 ? 2u : 1u) * G_A_BYTES;        // expanded buffer: hi (+ lo)
+  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  const int STAGES = grp.stages;
+  const uint32_t STAGE_BYTES = grp.stage_bytes;
+  const uint32_t X_OFF = 8192u, XLO_OFF = X_OFF + X_BYTES;   // the packed tile takes the first 8 KB of a slot
+  extern __shared__ uint8_t gsm_raw[];
+  uint8_t *gsm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *full = reinterpret_cast<uint64_t *>(gsm);
+  uint64_t *empty = full + WT_MAX_STAGES;
+  uint64_t *a_full = empty + WT_MAX_STAGES;
+  uint64_t *a_empty = a_full + WQ_NE;
+  uint64_t *acc_full = a_empty + WQ_NE;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  uint8_t *exp_base = gsm + 1024;                                   // WQ_NE expanded buffers, 1024-byte aligned
+  uint8_t *ring_base = exp_base + WQ_NE * E_BYTES;
+  const uint32_t tiles = smem_u32(ring_base), etiles = smem_u32(exp_base);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int pi = 0;
+  while (pi + 1 < grp.n && (int)blockIdx.x >= grp.tile_start[pi + 1]) ++pi;
+  const GemmArgs &g = grp.p[pi];
+  const int tile_n = blockIdx.x - grp.tile_start[pi], m0 = blockIdx.y * BN;
+  const int num_k1 = g.K / GBK;
+  const int kz0 = (int)((long long)blockIdx.z * num_k1 / grp.split), nkz = (int)((long long)(blockIdx.z + 1) * num_k1 / grp.split) - kz0;
+  const bool x_lo = g.A2 != nullptr;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }   // 4 expander warps + the MMA commit
+    for (int e = 0; e < WQ_NE; ++e) { mbar_init(&a_full[e], 4); mbar_init(&a_empty[e], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();   // operands and epilogue inputs come from the kernels before this one
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkz; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        mbar_expect_tx(&full[s], WQ_BYTES + (x_lo ? 2u : 1u) * X_BYTES);
+        const uint32_t dst = tiles + (uint32_t)s * STAGE_BYTES;
+        const int kx = (kz0 + kb) * GBK;
+        tma_load_2d(dst, &maps.b[pi], (kz0 + kb) * (int)ROW_B, tile_n * GBM, &full[s]);
+        tma_load_2d(dst + X_OFF, &maps.a[pi], kx, m0, &full[s]);
+        if (x_lo) tma_load_2d(dst + XLO_OFF, &maps.a2[pi], kx, m0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkz; ++kb) {
+        const int s = kb % STAGES, e = kb % WQ_NE;
+        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        if (!mbar_wait(&a_full[e], (kb / WQ_NE) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        tc_fence_after();
+        const uint32_t base = tiles + (uint32_t)s * STAGE_BYTES, eb = etiles + (uint32_t)e * E_BYTES;
+        const uint64_t wd = umma_desc_k128(eb), xd = umma_desc_k128(base + X_OFF);
+#pragma unroll
+        for (int k4 = 0; k4 < GBK / 16; ++k4)
+          umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, (kb | k4) != 0);
+        if (x_lo) {
+          const uint64_t xl = umma_desc_k128(base + XLO_OFF);
+#pragma unroll
+          for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xl + (uint64_t)(k4 * 2), IDESC, 1u);
+        }
+        if (FMT == FMT_INT4) {
+          const uint64_t wl = umma_desc_k128(eb + G_A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wl + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, 1u);
+        }
+        umma_commit(&empty[s]);
+        umma_commit(&a_empty[e]);
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp >= 6) {
+    // expanders: lane l of expander warp w owns row 32 w + l of the tile
+    const int row = (warp - 6) * 32 + lane;
+    const int ch = tile_n * GBM + row;                      // output channel of this row
+    const uint32_t swz = (uint32_t)(row & 7);
+    const uint32_t erow = (uint32_t)row * 128u;             // byte offset of the row inside an expanded tile
+    const __half *gs = nullptr;                             // int4: this row's group scales
+    if (FMT == FMT_INT4 && ch < g.N) gs = g.wq_scale + (size_t)ch * (g.K / 32);
+    uint32_t sc_next = 0x3c003c00u;
+    if (FMT == FMT_INT4 && gs && nkz > 0) sc_next = *reinterpret_cast<const uint32_t *>(gs + (size_t)kz0 * 2);
+    bool live = true;
+    for (int kb = 0; kb < nkz && live; ++kb) {
+      const int s = kb % STAGES, e = kb % WQ_NE;
+      const uint32_t sc = sc_next;                          // scales of the two 32-input groups of this slice
+      if (FMT == FMT_INT4 && gs && kb + 1 < nkz) sc_next = *reinterpret_cast<const uint32_t *>(gs + (size_t)(kz0 + kb + 1) * 2);
+      if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) { live = false; break; }
+      if (!mbar_wait(&a_empty[e], ((kb / WQ_NE) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) { live = false; break; }
+      const uint32_t src = tiles + (uint32_t)s * STAGE_BYTES + (uint32_t)row * ROW_B;
+      const uint32_t dst = etiles + (uint32_t)e * E_BYTES + erow;
+      if (FMT == FMT_INT8) {
+        // four 16-byte pieces of 16 codes; lanes start at different pieces so that a quarter warp touches 8 banks groups
+#pragma unroll
+        for (int pp = 0; pp < 4; ++pp) {
+          const uint32_t piece = (uint32_t)(pp + lane) & 3u;
+          const uint4 w = lds128(src + piece * 16u);
+          const uint32_t M = 0x64646464u, OFF = 0x64806480u;    // 1024 + (code + 128) - 1152 = code
+          const uint32_t wx = w.x ^ 0x80808080u, wy = w.y ^ 0x80808080u, wz = w.z ^ 0x80808080u, ww = w.w ^ 0x80808080u;
+          const uint4 o0 = make_uint4(hsub2_u32(prmt(wx, M, 0x4140), OFF), hsub2_u32(prmt(wx, M, 0x4342), OFF),
+                                      hsub2_u32(prmt(wy, M, 0x4140), OFF), hsub2_u32(prmt(wy, M, 0x4342), OFF));
+          const uint4 o1 = make_uint4(hsub2_u32(prmt(wz, M, 0x4140), OFF), hsub2_u32(prmt(wz, M, 0x4342), OFF),
+                                      hsub2_u32(prmt(ww, M, 0x4140), OFF), hsub2_u32(prmt(ww, M, 0x4342), OFF));
+          sts128(dst + (((piece * 2u) ^ swz) << 4), o0);        // inputs 16 piece .. +7: 16-byte chunk 2 piece
+          sts128(dst + (((piece * 2u + 1u) ^ swz) << 4), o1);
+        }
+      } else {
+        // two 16-byte pieces of 32 nibbles = the two scale groups of the slice
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {
+          const uint32_t piece = (uint32_t)(pp + lane) & 1u;
+          const uint4 w = lds128(src + piece * 16u);
+          const uint32_t s16 = piece ? (sc >> 16) : (sc & 0xffffu);
+          const uint32_t s2 = s16 | (s16 << 16);
+          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            // 8 nibbles = inputs 8 wi .. 8 wi + 7 of the group -> one 16-byte chunk of hi and one of lo
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // byte j -> {1024 + low nibble, 64 + high nibble} - {1032, 72} = {q_even, q_odd}
+              const uint32_t x = prmt(words[wi], 0u, 0x4040u + (uint32_t)j * 0x0101u);   // bytes [b_j, 0, b_j, 0]
+              const uint32_t qv = hsub2_u32(lop3_and_or(x, 0x00f0000fu, 0x54006400u), 0x54806408u);
+              hi[j] = hmul2_u32(qv, s2);
+              lo[j] = hfma2_u32(qv, s2, hi[j] ^ 0x80008000u);
+            }
+            const uint32_t chunk = (piece * 4u + (uint32_t)wi) ^ swz;
+            sts128(dst + (chunk << 4), make_uint4(hi[0], hi[1], hi[2], hi[3]));
+            sts128(dst + G_A_BYTES + (chunk << 4), make_uint4(lo[0], lo[1], lo[2], lo[3]));
+          }
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&a_full[e]); mbar_arrive(&empty[s]); }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int ch = tile_n * GBM + quad * 32 + lane;
+    const bool ok = mbar_wait(acc_full, 0, abort_flag, g.status, ST_GEMM_TIMEOUT);
+    tc_fence_after();
+    if (ok) {
+      const float sc = (g.col_scale && ch < g.N && grp.split == 1) ? __half2float(g.col_scale[ch]) : 1.f;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (m0 + c0 >= g.M) break;   // warp-uniform
+        uint32_t acc[32];
+        __syncwarp();
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
+        if (ch < g.N) {
+          if (grp.split > 1) {
+            float *dst = g.raw + ((size_t)blockIdx.z * g.M + m0 + c0) * g.N + ch;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m0 + c0 + i < g.M) dst[(size_t)i * g.N] = __uint_as_float(acc[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (m0 + c0 + i < g.M) epi_store_one(g, m0 + c0 + i, ch, __uint_as_float(acc[i]) * sc);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // split-K: sum the slabs in a fixed order, then the same epilogue.  One thread per 4 consecutive columns of a row
 // (coalesced 16-byte reads of every slab); N is a multiple of 4 for every projection (the head never splits).
 // blockIdx.y picks the problem of the group (grid.x covers the largest one).
@@ -592,6 +811,19 @@ bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows)
   const cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// [rows, row_bytes] bytes row-major -> tensor map with a (box_bytes x 128 rows) box, no swizzle, zero fill outside
+bool make_map_bytes(CUtensorMap *map, const void *base, int rows, int row_bytes, int box_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)GBM};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -1161,11 +1393,84 @@ cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
   }
   return cudaGetLastError();
 }
+template <int BN, int FMT>
+cudaError_t launch_gemm_wq_t(const GemmMaps &maps, const GemmGroup &grp, dim3 grid, size_t smem, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(gemm_wq_kernel<BN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  launch_k(gemm_wq_kernel<BN, FMT>, dim3(grid), dim3(WQ_THREADS), smem, st, maps, grp);
+  return cudaGetLastError();
+}
+
+// quantised weights in packed form (GemmArgs::Wq): any number of rows, walked in tiles of up to 256 along grid.y
+cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
+  const int M = probs[0].M, fmt = probs[0].wfmt;
+  if (fmt != FMT_INT8 && fmt != FMT_INT4) return cudaErrorInvalidValue;
+  const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  GemmMaps maps;
+  GemmGroup grp;
+  memset(&grp, 0, sizeof(grp));
+  grp.n = n;
+  int tiles = 0, min_k1 = 1 << 30;
+  bool raw_ok = M <= GEMM_SMALL_M;
+  for (int i = 0; i < n; ++i) {
+    const GemmArgs &g = probs[i];
+    if (g.K % GBK != 0 || g.M < 1 || g.N < 1 || g.M != M || !g.Wq || g.wfmt != fmt) return cudaErrorInvalidValue;
+    if (fmt == FMT_INT4 && !g.wq_scale) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Wq) & 15) || (reinterpret_cast<uintptr_t>(g.A2) & 15))
+      return cudaErrorInvalidValue;
+    const int row_bytes = fmt == FMT_INT8 ? g.K : g.K / 2;
+    if (!make_map(&maps.a[i], g.A, g.M, g.K, bn) || !make_map_bytes(&maps.b[i], g.Wq, g.N, row_bytes, fmt == FMT_INT8 ? GBK : GBK / 2))
+      return cudaErrorNotSupported;
+    if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, bn)) return cudaErrorNotSupported;
+    maps.b2[i] = maps.b[i];
+    grp.p[i] = g;
+    grp.tile_start[i] = tiles;
+    tiles += (g.N + GBM - 1) / GBM;
+    min_k1 = std::min(min_k1, g.K / GBK);
+    raw_ok = raw_ok && g.raw != nullptr && (g.N & 3) == 0 && (g.ldo & 3) == 0;
+    if (g.A2) grp.dual |= 1;
+  }
+  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; maps.b2[i] = maps.b2[0]; }
+  grp.tile_start[n] = tiles;
+  const int m_tiles = (M + bn - 1) / bn;
+  grp.split = 1;
+  const int sms = device_sm_count();
+  const int slots = bn <= 64 ? 2 * sms : sms;
+  if (raw_ok) {
+    const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 4));
+    float best = 0.f;
+    for (int sp = 1; sp <= max_split; ++sp) {
+      const int waves = (ctas * sp + slots - 1) / slots;
+      const float cost = (float)waves * (float)((min_k1 + sp - 1) / sp + 2) + 0.5f * (float)sp;
+      if (sp == 1 || cost < best) { best = cost; grp.split = sp; }
+    }
+  }
+  grp.stage_bytes = 8192u + ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
+  const uint32_t ebytes = WQ_NE * (fmt == FMT_INT4 ? 2u : 1u) * G_A_BYTES;
+  // two CTAs per SM with rings of >= 3 slots where they fit, else one CTA with as deep a ring as fits
+  int stages = (int)(((100u << 10) - ebytes) / grp.stage_bytes);
+  if (stages < 3) stages = (int)(((200u << 10) - ebytes) / grp.stage_bytes);
+  grp.stages = std::max(2, std::min(stages, WT_MAX_STAGES));
+  const size_t smem = 1024 + ebytes + (size_t)grp.stages * grp.stage_bytes + 1024;
+  dim3 grid(tiles, m_tiles, grp.split);
+  cudaError_t e = cudaErrorInvalidValue;
+#define FRB_WQ(BNV) (fmt == FMT_INT8 ? launch_gemm_wq_t<BNV, FMT_INT8>(maps, grp, grid, smem, st) : launch_gemm_wq_t<BNV, FMT_INT4>(maps, grp, grid, smem, st))
+  e = bn == 32 ? FRB_WQ(32) : bn == 64 ? FRB_WQ(64) : bn == 128 ? FRB_WQ(128) : FRB_WQ(256);
+#undef FRB_WQ
+  if (e != cudaSuccess) return e;
+  if (grp.split > 1) {
+    int max_n = 0;
+    for (int i = 0; i < n; ++i) max_n = std::max(max_n, probs[i].N);
+    launch_k(gemm_finish_kernel, dim3(dim3((M * (max_n / 4) + 255) / 256, n)), dim3(256), 0, st, grp);
+  }
+  return cudaGetLastError();
+}
 }  // namespace
 
 cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st) {
   if (n < 1 || n > GEMM_GROUP_MAX || (mt != 1 && mt != 2)) return cudaErrorInvalidValue;
   const int M = probs[0].M;
+  if (probs[0].Wq) return launch_gemm_wq(probs, n, st);
   if (M <= GEMM_SMALL_M && wt_enabled()) return launch_gemm_wt(probs, n, st);
   // few rows (batched decode): narrow N tiles and split-K, so that a few hundred CTAs stream the weights
   const bool narrow = M <= GEMM_SMALL_M;

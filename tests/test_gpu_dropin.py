@@ -44,15 +44,32 @@ def test_reference_model_class_on_b200_backend(orc, synth, tmp_path, name, strat
         want = ref.run(int(t))
         assert np.abs(got[i] - want).max() < 1e-2
         assert np.linalg.norm(got[i] - want) / np.linalg.norm(want) < 1e-3
-    # Model::Run(vector): RWKV-4 and quantised models run the token loop (kernels/default/model_forward_seq.cpp:34-46)
-    # and must repeat it bit for bit; RWKV-5.x fp16 prompts run the seq kernels (GEMM projections + chunked state
-    # scan), whose sums are ordered differently, so they are held to the same tolerance against the oracle.
+    # Model::Run(vector): short prompts of RWKV-4 fp16 models run the token loop (kernels/default/model_forward_seq.cpp:34-46)
+    # and must repeat it bit for bit; RWKV-5.x fp16 and every quantised model run the seq kernels (GEMM projections,
+    # state scan), whose sums are ordered differently, so they are held to the same tolerance against the oracle.
     last = _run(DROPIN, fr, strategy, ids, str(tmp_path), seq=True)
-    if shape.version.startswith("5") and fmt == "fp16":
+    if shape.version.startswith("5") or fmt != "fp16":
         assert np.abs(last - want).max() < 1e-2
         assert np.linalg.norm(last - want) / np.linalg.norm(want) < 1e-3
     else:
         assert np.array_equal(last, got[-1])
+
+
+@pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built (needs the reference tree at build time)")
+def test_rwkv4_prompt_behind_the_registry_runs_as_gemms(orc, synth, tmp_path):
+    """Upstream throws for RWKV-4 prompts on CUDA (kernels/default/model_forward_seq.cpp:111-112).  Here a prompt of 32
+    tokens or more makes an fp16 RWKV-4 model build its row copies and run the projections as GEMMs; result and the
+    next single token must match the oracle's token loop."""
+    shape, tensors, fr = _model_file(synth, str(tmp_path), "mid4", "fp16")
+    ids = synth.token_ids(shape, 70, seed=12)
+    last = _run(DROPIN, fr, "cuda fp16", ids, str(tmp_path), seq=True)
+    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6, state_fp16=True)
+    want = ref.run_seq([int(t) for t in ids])
+    assert np.abs(last - want).max() < 1e-2
+    assert np.linalg.norm(last - want) / np.linalg.norm(want) < 1e-3
+    loop = _run(DROPIN, fr, "cuda fp16", ids, str(tmp_path)).reshape(len(ids), shape.vocab)[-1]
+    assert not np.array_equal(last, loop)          # a different summation order: it really took the other path
+    assert np.linalg.norm(last - loop) / np.linalg.norm(loop) < 1e-3
 
 
 @pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built")
