@@ -81,6 +81,14 @@ SIGNATURES = {
     "fr_b200_get_info": (_i, [_vp, ctypes.POINTER(Info)]),
     "fr_b200_decode_profile": (_i, [_vp, _vp, _i, _vp, _i]),
     "fr_b200_wait_selftest": (_i, [_i, ctypes.c_uint]),
+    "fr_b200_ln_mix": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "fr_b200_wkv4_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "fr_b200_wkv5_step": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp]),
+    "fr_b200_wkv5_chunk_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]),
+    "fr_b200_groupnorm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
+    "fr_b200_elementwise": (_i, [_i, _vp, _i, _vp, _i, _vp, _i, ctypes.c_float, _vp, _i, _sz, _vp]),
+    "fr_b200_matmul": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp]),
+    "fr_b200_op_last_error": (ctypes.c_char_p, []),
     "fr_b200_strerror": (ctypes.c_char_p, [_i]),
     "fr_b200_last_error": (ctypes.c_char_p, []),
 }

@@ -15,9 +15,32 @@
 #include <iostream>
 #include <vector>
 
+#include <kernels/kernels.h>
 #include <model.h>
 
+// --ops-test: the body of the reference's tests/test_ops.cpp:9-16 on the registered CUDA operators: fill_(1) then
+// scalar_div_(2) must leave 0.5 in every element.  Prints "ops_test ok".
+static int ops_test() {
+  try {
+    for (rwkv::DType dt : {rwkv::DType::kFloat16, rwkv::DType::kFloat32}) {
+      rwkv::Tensor x = rwkv::Tensor::Empty({2, 3}, dt, rwkv::Device::kCUDA);
+      rwkv::fill_(x, 1.f);
+      rwkv::scalar_div_(x, 2.f);
+      rwkv::Tensor y = rwkv::cast_dtype(x, rwkv::DType::kFloat32);
+      rwkv::Tensor h = rwkv::Copy(y, rwkv::Device::kCPU);
+      for (int i = 0; i < 6; ++i)
+        if (h.data_ptr<float>()[i] != 0.5f) { std::fprintf(stderr, "ops_test: element %d is %g\n", i, h.data_ptr<float>()[i]); return 1; }
+    }
+  } catch (const std::exception &e) {
+    std::fprintf(stderr, "error: %s\n", e.what());
+    return 1;
+  }
+  std::printf("ops_test ok\n");
+  return 0;
+}
+
 int main(int argc, char **argv) {
+  if (argc >= 2 && !std::strcmp(argv[1], "--ops-test")) return ops_test();
   if (argc < 5) {
     std::fprintf(stderr, "usage: %s model.fr strategy out.bin [--seq] ids...\n", argv[0]);
     return 2;

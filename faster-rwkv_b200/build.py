@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(CSRC, "libfr_b200.so")
-SOURCES = ["pack.cu", "decode.cu", "prefill.cu", "sample.cu", "api.cu", "noalloc.cu"]
+SOURCES = ["pack.cu", "decode.cu", "prefill.cu", "sample.cu", "api.cu", "noalloc.cu", "ops.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

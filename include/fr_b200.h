@@ -170,6 +170,66 @@ int fr_b200_matvec_noalloc(const float *W, int K, int N, int weight_format, cons
                            int device, void *stream);
 const char *fr_b200_noalloc_last_error(void);
 
+/* ---- stand-alone operators over DEVICE pointers: the forward pass as the reference's operator API cuts it
+ * (kernels/kernels.h:15-257).  The decode kernel and the seq path fuse all of these; the entry points below exist so
+ * that every formula can be tested and registered on its own (backend/registry_backend.cpp registers the reference's
+ * op-level keys "att", "ffn", "layernorm", ... over them).  Tensor element types are FR_B200_T_F16 / FR_B200_T_F32;
+ * stream = cudaStream_t (0 = default); calls are asynchronous on that stream unless noted. */
+
+/* LayerNorm of `rows` rows of C elements (eps 1e-5, fp32 statistics: layer_norm_op, kernels/cuda/layer_norm.cu:101-130)
+ * and, with nvec > 0, the token-shift mix that follows it in the reference (Mix / MixWithG, kernels/cuda/att.cu:90-143;
+ * FfnOneMix, ffn.cu:15-32): out[v] = xx * mix[v] + sx * (1 - mix[v]).  x, sx, xx: act_dtype; ln_w, ln_b, mix[v]:
+ * param_dtype; out[v]: out_dtype.  xx may be NULL when only the mixed vectors are wanted; nvec = 0 is a plain LayerNorm. */
+int fr_b200_ln_mix(const void *x, const void *sx, const void *ln_w, const void *ln_b, const void *const *mix, int nvec, int rows,
+                   int C, int act_dtype, int param_dtype, int out_dtype, void *xx, void *const *out, void *stream);
+
+/* One RWKV-4 WKV step over C channels: WkvForwardOne with the sigmoid gate (kernels/cuda/att.cu:30-62, 154-159).
+ * k, v, r (r before the sigmoid), decay (= -exp(raw)), first, aa, bb, pp: fp32 [C].  out = sigmoid(r) * wkv in out_dtype;
+ * aa2, bb2, pp2: the new state (may alias the old one). */
+int fr_b200_wkv4_step(const float *k, const float *v, const float *r, const float *decay, const float *first, const float *aa,
+                      const float *bb, const float *pp, int C, int out_dtype, void *out, float *aa2, float *bb2, float *pp2,
+                      void *stream);
+
+/* One RWKV-5 state step over n_head heads of size 64: OneV5MulAdd and the readout around it (kernels/cuda/att.cu:64-81,
+ * 219-335).  r, k, v: fp32 [n_head * 64]; decay (= exp(-exp(raw))), first: fp32 [n_head] when per_head (RWKV-5.0) else
+ * [n_head * 64]; s, s2: fp32 [n_head, 64 key, 64 value] (s2 must not alias s); y: fp32 [n_head * 64] before GroupNorm. */
+int fr_b200_wkv5_step(const float *r, const float *k, const float *v, const float *decay, const float *first, int per_head,
+                      const float *s, int n_head, float *s2, float *y, void *stream);
+
+/* The RWKV-5 state recurrence over T tokens as a chunk-parallel scan: replaces rwkv5_2_kernel_forward
+ * (kernels/cuda/att_seq.cu:258-345), which walks T serially.  r, k, v, y: fp32 [T, n_head * 64]; state: fp32
+ * [n_head, 64, 64], updated in place; n_chunks = parallel pieces (1 = serial).  Synchronises the stream. */
+int fr_b200_wkv5_chunk_scan(const float *r, const float *k, const float *v, const float *decay, const float *first, int per_head,
+                            float *state, int n_head, int T, int n_chunks, float *y, void *stream);
+
+/* GroupNorm over the last dimension cut into num_groups pieces, eps 1e-5 (group_norm_op, kernels/cuda/group_norm.cu:322-357).
+ * x, out: [rows, C] in x_dtype; w, b: [C] in param_dtype. */
+int fr_b200_groupnorm(const void *x, const void *w, const void *b, int rows, int C, int num_groups, int x_dtype, int param_dtype,
+                      void *out, void *stream);
+
+/* Element-wise pieces (kernels/cuda/att.cu:145-175, ffn.cu:34-60, cast_dtype.cu:24-41, element_wise.cu:15-19, fill.cu:17-26):
+ * out[i] = f(x[i], y[i], z[i]) over n elements, each operand with its own element type. */
+enum {
+  FR_B200_EW_COPY = 0,     /* x (a dtype cast when the types differ) */
+  FR_B200_EW_FILL = 1,     /* alpha */
+  FR_B200_EW_SCALE = 2,    /* x * alpha (scalar_div_ with alpha = 1 / d) */
+  FR_B200_EW_ADD = 3,      /* x + y */
+  FR_B200_EW_MUL = 4,      /* x * y */
+  FR_B200_EW_SIGMOID = 5,
+  FR_B200_EW_RELU2 = 6,    /* max(x, 0)^2 */
+  FR_B200_EW_SILU = 7,
+  FR_B200_EW_FMA = 8       /* x * y + z */
+};
+int fr_b200_elementwise(int op, const void *x, int x_dtype, const void *y, int y_dtype, const void *z, int z_dtype, float alpha,
+                        void *out, int out_dtype, size_t n, void *stream);
+/* out[M,N] = a[M,K] @ w[K,N] over device tensors of either element type: gemm_cublas_tensor (kernels/cuda/matmul.cpp:105-146)
+ * for the operator API.  w is rounded to fp16 if it is not already; up to 8 rows run the streaming matvec (the rows
+ * travel as fp16 hi + lo pairs), more rows the tensor-core GEMM (rows rounded to fp16).  The matrix is repacked on
+ * every call, so this is the operator-level path, not the model's.  K a multiple of 64.  Synchronises the stream. */
+int fr_b200_matmul(const void *a, int a_dtype, int M, int K, const void *w, int w_dtype, int N, void *out, int out_dtype,
+                   int device, void *stream);
+const char *fr_b200_op_last_error(void);
+
 /* out[M,N] = epilogue(A[M,K] @ W[K,N]) on the tcgen05 tensor cores, fp16 operands, fp32 accumulate: the seq-mode
  * replacement of gemm_cublas_tensor (kernels/cuda/matmul.cpp:105-122) with the element-wise kernels that follow
  * it in the reference fused as the epilogue (att_seq.cu:368-423, ffn_seq.cu:65-87).  A: [M,K] fp32, rounded to

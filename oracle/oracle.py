@@ -49,6 +49,9 @@ def lib() -> ctypes.CDLL:
         L.orc_quant_int4.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
         L.orc_dequant_int8.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.orc_dequant_int4.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.orc_wkv4_step.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 9
+        L.orc_wkv5_step.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7
+        L.orc_layernorm.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         L.orc_f32_to_f16.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         L.orc_f16_to_f32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
         _lib = L
@@ -112,6 +115,41 @@ def fake_quant(W: np.ndarray, fmt: str) -> np.ndarray:
     if fmt == "int4":
         return dequant_int4(*quant_int4(W))
     return np.asarray(W, np.float32)
+
+
+# ------------------------------------------------------------------ single formulas (per-kernel tests)
+
+def _f32(a):
+    return np.ascontiguousarray(a, np.float32)
+
+
+def layernorm(x, g, b) -> np.ndarray:
+    """LayerNorm of every row of x [rows, n] (eps 1e-5)."""
+    x = _f32(np.atleast_2d(x))
+    g, b = _f32(g), _f32(b)
+    y = np.empty_like(x)
+    for i in range(x.shape[0]):
+        lib().orc_layernorm(_ptr(x[i]), _ptr(g), _ptr(b), x.shape[1], _ptr(y[i]))
+    return y
+
+
+def wkv4_step(k, v, r, decay, first, aa, bb, pp):
+    """One RWKV-4 WKV step; returns (sigmoid(r) * wkv, aa', bb', pp')."""
+    k, v, r, decay, first = map(_f32, (k, v, r, decay, first))
+    aa, bb, pp = _f32(aa).copy(), _f32(bb).copy(), _f32(pp).copy()
+    out = np.empty_like(k)
+    lib().orc_wkv4_step(len(k), _ptr(k), _ptr(v), _ptr(r), _ptr(decay), _ptr(first), _ptr(aa), _ptr(bb), _ptr(pp), _ptr(out))
+    return out, aa, bb, pp
+
+
+def wkv5_step(r, k, v, decay, first, s, per_head: bool):
+    """One RWKV-5 state step over s [H, S, S]; returns (readout before GroupNorm [H * S], s')."""
+    r, k, v, decay, first = map(_f32, (r, k, v, decay, first))
+    s = _f32(s).copy()
+    H, S = s.shape[0], s.shape[1]
+    out = np.empty(H * S, np.float32)
+    lib().orc_wkv5_step(H, S, int(per_head), _ptr(r), _ptr(k), _ptr(v), _ptr(decay), _ptr(first), _ptr(s), _ptr(out))
+    return out, s
 
 
 # ------------------------------------------------------------------ model

@@ -99,6 +99,51 @@ static void mix(const float *xx, const float *sx, const float *m, int n, float *
 
 /* ---------------------------------------------------------------- time mix */
 
+/* One WKV step over C channels, kernels/default/att.cpp:30-41 (WkvForwardOne, kernels/cuda/att.cu:30-62, with the
+ * sigmoid of att.cu:154-159): out = sigmoid(r) * wkv; aa, bb, pp updated in place.  Exported for per-kernel tests. */
+void orc_wkv4_step(int C, const float *k, const float *v, const float *r, const float *decay, const float *first,
+                   float *aa, float *bb, float *pp, float *out) {
+  for (int i = 0; i < C; ++i) {
+    float rr = sigmoidf_(r[i]);
+    float ww = first[i] + k[i];
+    float pm = pp[i] > ww ? pp[i] : ww;
+    float e1 = expf(pp[i] - pm), e2 = expf(ww - pm);
+    float wkv = (e1 * aa[i] + e2 * v[i]) / (e1 * bb[i] + e2);
+    ww = decay[i] + pp[i];
+    pm = ww > k[i] ? ww : k[i];
+    e1 = expf(ww - pm);
+    e2 = expf(k[i] - pm);
+    aa[i] = e1 * aa[i] + e2 * v[i];
+    bb[i] = e1 * bb[i] + e2;
+    pp[i] = pm;
+    out[i] = rr * wkv;
+  }
+}
+
+/* One RWKV-5 state step over H heads of size S, kernels/default/att.cpp:62-72 / 96-106 (OneV5MulAdd, kernels/cuda/att.cu:64-81):
+ * out[h,j] = sum_i r_i (u_i k_i v_j + s_ij), s_ij = k_i v_j + w_i s_ij; decay / first per head when per_head (v5.0).
+ * out is the readout before GroupNorm.  Exported for per-kernel tests. */
+void orc_wkv5_step(int H, int S, int per_head, const float *r, const float *k, const float *v, const float *decay,
+                   const float *first, float *s, float *out) {
+  for (int h = 0; h < H; ++h) {
+    float *sh = s + (size_t)h * S * S;
+    for (int j = 0; j < S; ++j) out[h * S + j] = 0.f;
+    for (int i = 0; i < S; ++i) {
+      const float u = per_head ? first[h] : first[h * S + i];
+      const float w = per_head ? decay[h] : decay[h * S + i];
+      const float ki = k[h * S + i], ri = r[h * S + i];
+      for (int j = 0; j < S; ++j) {
+        float a = ki * v[h * S + j];
+        out[h * S + j] += ri * (u * a + sh[i * S + j]);
+        sh[i * S + j] = a + w * sh[i * S + j];
+      }
+    }
+  }
+}
+
+/* LayerNorm of one row, exported for per-kernel tests (GroupNorm = this over each group). */
+void orc_layernorm(const float *x, const float *g, const float *b, int n, float *y) { layernorm(x, g, b, n, y); }
+
 /* RWKV-4 time mix, kernels/default/att.cpp:16-45 (same maths as WkvForwardOne,
  * kernels/cuda/att.cu:30-62).  state: sx, aa, bb, pp each [C], updated in place. */
 static void att_v4(int C, int sf16, float *x, float *sx, float *aa, float *bb, float *pp, const float *const *p,
@@ -114,21 +159,7 @@ static void att_v4(int C, int sf16, float *x, float *sx, float *aa, float *bb, f
   matvec(rx, rw, C, C, r);
   matvec(kx, kw, C, C, k);
   matvec(vx, vw, C, C, v);
-  for (int i = 0; i < C; ++i) {
-    float rr = sigmoidf_(r[i]);
-    float ww = first[i] + k[i];
-    float pm = pp[i] > ww ? pp[i] : ww;
-    float e1 = expf(pp[i] - pm), e2 = expf(ww - pm);
-    float wkv = (e1 * aa[i] + e2 * v[i]) / (e1 * bb[i] + e2);
-    ww = decay[i] + pp[i];
-    pm = ww > k[i] ? ww : k[i];
-    e1 = expf(ww - pm);
-    e2 = expf(k[i] - pm);
-    aa[i] = e1 * aa[i] + e2 * v[i];
-    bb[i] = e1 * bb[i] + e2;
-    pp[i] = pm;
-    r[i] = rr * wkv;
-  }
+  orc_wkv4_step(C, k, v, r, decay, first, aa, bb, pp, r);
   matvec(r, ow, C, C, out);
   for (int i = 0; i < C; ++i) { x[i] += out[i]; sx[i] = state_round(xx[i], sf16); }
 }
@@ -161,21 +192,8 @@ static void att_v5(int version, int C, int H, int sf16, int gate_xx, float *x, f
     matvec(gate_xx ? xx : gx, gw, C, C, g);
     for (int i = 0; i < C; ++i) g[i] = g[i] * sigmoidf_(g[i]); /* SiLU, att.cu:145-152 */
   }
-  for (int h = 0; h < H; ++h) {
-    float *sh = s + (size_t)h * S * S;
-    for (int j = 0; j < S; ++j) out[h * S + j] = 0.f;
-    for (int i = 0; i < S; ++i) {
-      const float u = version == 50 ? first[h] : first[h * S + i];
-      const float w = version == 50 ? decay[h] : decay[h * S + i];
-      const float ki = k[h * S + i], ri = r[h * S + i];
-      for (int j = 0; j < S; ++j) {
-        float a = ki * v[h * S + j];
-        out[h * S + j] += ri * (u * a + sh[i * S + j]);
-        sh[i * S + j] = a + w * sh[i * S + j];
-      }
-    }
-    layernorm(out + h * S, lx_w + h * S, lx_b + h * S, S, out + h * S);
-  }
+  orc_wkv5_step(H, S, version == 50, r, k, v, decay, first, s, out);
+  for (int h = 0; h < H; ++h) layernorm(out + h * S, lx_w + h * S, lx_b + h * S, S, out + h * S);
   if (gate) for (int i = 0; i < C; ++i) out[i] *= g[i];
   matvec(out, ow, C, C, k /* reuse */);
   for (int i = 0; i < C; ++i) { x[i] += k[i]; sx[i] = state_round(xx[i], sf16); }
