@@ -38,7 +38,7 @@ class FrB200Error(RuntimeError):
 class Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in
                 ("version", "n_layer", "n_embd", "n_ffn", "n_head", "vocab", "weight_format", "act_fp16",
-                 "max_batch", "device")]
+                 "max_batch", "device", "host_visible_state")]
 
 
 class Info(ctypes.Structure):
@@ -151,7 +151,7 @@ class Model:
         self.vocab = shape.vocab
         self._h = _vp()
         cfg = Config(_VERSIONS[str(shape.version)], shape.n_layer, shape.n_embd, shape.n_ffn, shape.n_head,
-                     shape.vocab, fmt, act_fp16, max_batch, device)
+                     shape.vocab, fmt, act_fp16, max_batch, device, 0)
         L = lib()
         check(L.fr_b200_create(ctypes.byref(cfg), ctypes.byref(self._h)), "fr_b200_create")
         try:

@@ -89,6 +89,15 @@ int main(int argc, char **argv) {
       std::printf("ms_per_token %.6f\n", std::chrono::duration<double, std::milli>(t1 - t0).count() / bench);
     }
     if (std::getenv("FR_REF_STATE")) model.SaveStateFile(std::getenv("FR_REF_STATE"));
+    if (const char *sf = std::getenv("FR_STATE_ROUNDTRIP")) {
+      // the sequence of the reference's tests/test_model.cpp:35-51: save the state, run a token, load the state back,
+      // run the same token again -- both logits are written after the ids' own
+      const int id = ids.empty() ? 0 : ids.front();
+      model.SaveStateFile(sf);
+      dump(model.Run(id));
+      model.LoadStateFile(sf);
+      dump(model.Run(id));
+    }
   } catch (const std::exception &e) {
     std::fprintf(stderr, "error: %s\n", e.what());
     return 1;

@@ -138,6 +138,8 @@ void init_model(Model *model, Device device, const std::string &path, const std:
   cfg.act_fp16 = model->_act_dtype == DType::kFloat16;
   cfg.max_batch = 1;
   cfg.device = 0;
+  // Model::SaveStateFile reads the state tensors with memcpy (model.cpp:110): hand out addresses the host can read
+  cfg.host_visible_state = 1;
 
   auto ex = std::make_shared<Extra>();
   FRB_CALL(fr_b200_create(&cfg, &ex->h));

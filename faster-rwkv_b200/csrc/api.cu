@@ -390,7 +390,18 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_weights, m->weights_bytes);
   if (!rc) rc = alloc((void **)&m->d_rscale, m->rscale_n * 2);
   if (!rc) rc = alloc((void **)&m->d_vecs, m->vecs_n * 4);
-  if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
+  if (!rc && cfg->host_visible_state) {
+    // managed memory, resident on the device: the host may read it between calls (a page then migrates and comes back
+    // with the next launch)
+    cudaError_t e = cudaMallocManaged((void **)&m->d_state, m->state_stride * B);
+    if (e != cudaSuccess) rc = fail(FR_B200_E_NOMEM, std::string("cudaMallocManaged(state): ") + cudaGetErrorString(e));
+    else {
+      cudaMemLocation loc;
+      loc.type = cudaMemLocationTypeDevice; loc.id = cfg->device;
+      cudaMemAdvise(m->d_state, m->state_stride * B, cudaMemAdviseSetPreferredLocation, loc);
+      cudaGetLastError();   // the advice is an optimisation: a platform that refuses it still works
+    }
+  } else if (!rc) rc = alloc((void **)&m->d_state, m->state_stride * B);
   if (!rc) rc = alloc((void **)&m->d_x, (size_t)B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_xa, (size_t)B * m->C * sizeof(exch_t));
   if (!rc) rc = alloc((void **)&m->d_rwkv, (size_t)B * m->C * sizeof(exch_t));

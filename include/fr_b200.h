@@ -59,6 +59,10 @@ typedef struct fr_b200_config {
                        * with max_batch > 8 also keeps every projection as fp16 W^T (dequantised for int8 / int4) and
                        * decodes larger batches through tensor-core GEMMs, one row per stream */
   int device;         /* CUDA device ordinal */
+  int host_visible_state; /* 1: the recurrent state lives in managed memory, so the device addresses fr_b200_state_tensor
+                           * hands out can also be read by the host between calls.  The reference's Model::SaveStateFile
+                           * copies the state tensors with a plain memcpy (model.cpp:110); the registry glue sets this so
+                           * that the unchanged class can save a CUDA model's state.  0: ordinary device memory. */
 } fr_b200_config;
 
 /* ---- model life cycle: replaces def::init_model (kernels/default/init_model.cpp:19-133) ---- */

@@ -105,3 +105,42 @@ def test_against_reference_cuda_fp16(orc, synth, tmp_path, name):
     assert d_ours < d_theirs
     assert d_pair < d_theirs + d_ours + 1e-4   # triangle: nothing but the reference's rounding separates the two
     assert np.abs(ours - theirs).max() < 3e-2
+
+
+@pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built (needs the reference tree at build time)")
+@pytest.mark.parametrize("name,strategy,dtype,fmt", [("tiny4", "cuda fp16", "fp16", "fp16"), ("tiny52", "cuda fp16", "fp16", "fp16"),
+                                                    ("tiny4b", "cuda int8", "fp32", "int8")])
+def test_state_file_roundtrip_through_the_reference_model_class(orc, synth, tmp_path, name, strategy, dtype, fmt):
+    """tests/test_model.cpp:35-51 of the reference: SaveStateFile, Run, LoadStateFile, Run again -> the same logits.
+    Model::SaveStateFile copies the state tensors with a plain memcpy (model.cpp:110), which reads a device pointer on
+    a CUDA model upstream; the glue asks the backend for host-visible (managed) state memory, so the unchanged class
+    works.  The file must hold the reference's shapes and dtypes and the oracle's values."""
+    import msgpack
+    shape, tensors, fr = _model_file(synth, str(tmp_path), name, dtype)
+    ids = [int(t) for t in synth.token_ids(shape, 5, seed=2)]
+    sf = str(tmp_path / "states.bin")
+    env = dict(os.environ, FR_STATE_ROUNDTRIP=sf)
+    got = _run(DROPIN, fr, strategy, ids, str(tmp_path), env=env).reshape(len(ids) + 2, shape.vocab)
+    assert np.array_equal(got[-1], got[-2])            # the reloaded state reproduces the step bit for bit
+    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6 if fmt == "fp16" else 0,
+                          weight_format=fmt, state_fp16=fmt == "fp16")
+    for t in ids:
+        ref.run(t)
+    with open(sf, "rb") as f:
+        layers = msgpack.unpack(f, raw=False)
+    assert len(layers) == shape.n_layer
+    C, H = shape.n_embd, shape.n_head
+    act = "torch.float16" if fmt == "fp16" else "torch.float32"
+    for l, st in enumerate(layers):
+        arrs = [np.frombuffer(t["data"], np.float16 if t["dtype"] == "torch.float16" else np.float32).astype(np.float32) for t in st]
+        if shape.version == "4":
+            assert [t["dtype"] for t in st] == [act, "torch.float32", "torch.float32", "torch.float32", act]
+            want = ref.state_v4()[l]
+            for j in range(5):
+                assert np.abs(arrs[j] - want[j]).max() < 1e-2 * max(1.0, np.abs(want[j][want[j] > -1e29]).max()), (l, j)
+        else:
+            assert [t["dtype"] for t in st] == [act, "torch.float32", act] and list(st[1]["shape"]) == [H, 64, 64]
+            per = 2 * C + H * 4096
+            blk = ref.state[l * per:(l + 1) * per]
+            for a, w in zip(arrs, (blk[:C], blk[C:C + H * 4096], blk[C + H * 4096:])):
+                assert np.abs(a - w).max() < 1e-2 * max(1.0, np.abs(w).max()), l
