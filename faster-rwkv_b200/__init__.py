@@ -56,6 +56,9 @@ SIGNATURES = {
     "fr_b200_set_tensor": (_i, [_vp, ctypes.c_char_p, _vp, _i, ctypes.POINTER(ctypes.c_int64), _i]),
     "fr_b200_finalize": (_i, [_vp]),
     "fr_b200_destroy": (None, [_vp]),
+    "fr_b200_save_packed": (_i, [_vp, ctypes.c_char_p]),
+    "fr_b200_load_packed": (_i, [ctypes.c_char_p, _i, _i, _i, ctypes.POINTER(_vp)]),
+    "fr_b200_get_config": (_i, [_vp, ctypes.POINTER(Config)]),
     "fr_b200_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "fr_b200_decode_greedy": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "fr_b200_logits_device": (_i, [_vp, ctypes.POINTER(_vp)]),
@@ -161,6 +164,20 @@ class Model:
         except Exception:
             self.close()
             raise
+
+    # -- packed model files ------------------------------------------------------------------
+    def save_packed(self, path: str) -> None:
+        """Write the finalized model's device blobs to `path` (fr_b200_save_packed)."""
+        check(lib().fr_b200_save_packed(self._h, os.fspath(path).encode()), "fr_b200_save_packed")
+
+    @classmethod
+    def load_packed(cls, path: str, shape, strategy: str, max_batch: int = 1, device: int = 0) -> "Model":
+        """A model from a packed file written by save_packed; shape and strategy must be the writer's."""
+        self = cls.__new__(cls)
+        self.shape, self.strategy, self.max_batch, self.vocab = shape, strategy, max_batch, shape.vocab
+        self._h = _vp()
+        check(lib().fr_b200_load_packed(os.fspath(path).encode(), max_batch, device, 0, ctypes.byref(self._h)), "fr_b200_load_packed")
+        return self
 
     # -- upload ------------------------------------------------------------------------------
     def set_tensor(self, name: str, arr) -> None:

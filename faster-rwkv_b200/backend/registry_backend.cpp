@@ -94,8 +94,44 @@ static void upload(fr_b200_model *h, const std::string &name, const msgpack::obj
 
 // replaces def::init_model (kernels/default/init_model.cpp:19-133): same file format, but the tensors go
 // straight into the backend's packed layout instead of Model::_params
+static const char *version_string(int code) {
+  return code == FR_B200_V4 ? "4" : code == FR_B200_V5_0 ? "5" : code == FR_B200_V5_1 ? "5.1" : "5.2";
+}
+
+// FR_B200_CACHE=1: a packed copy of the model (<file>.b200-<fp16|int8|int4>) is written after the first load and read
+// instead of the `.fr` file from then on: a few large reads in place of the msgpack parse, the upload per embedding
+// row and the re-quantisation.  Returns true when the model came from the cache.
+static bool load_from_cache(Model *model, const std::string &cache, int weight_format, int act_fp16) {
+  std::ifstream probe(cache, std::ios::binary);
+  if (!probe.good()) return false;
+  probe.close();
+  auto ex = std::make_shared<Extra>();
+  if (fr_b200_load_packed(cache.c_str(), 1, 0, 1, &ex->h) < 0) return false;   // stale or foreign file: load the `.fr`
+  fr_b200_config cfg;
+  FRB_CALL(fr_b200_get_config(ex->h, &cfg));
+  if (cfg.weight_format != weight_format || cfg.act_fp16 != act_fp16) return false;
+  model->_n_layer = cfg.n_layer;
+  model->_n_embd = cfg.n_embd;
+  model->_n_att = cfg.n_embd;
+  model->_n_ffn = cfg.n_ffn;
+  model->_head_size = cfg.n_head;   // the reference keeps n_head in _head_size (init_model.cpp:64)
+  model->_version = version_string(cfg.version);
+  ex->vocab = cfg.vocab;
+  model->_extra = ex;
+  return true;
+}
+
 void init_model(Model *model, Device device, const std::string &path, const std::string &strategy,
                 const std::any &extra) {
+  int wfmt;
+  if (model->_weight_dtype == DType::kFloat16) wfmt = FR_B200_W_FP16;
+  else if (model->_weight_dtype == DType::kInt8) wfmt = FR_B200_W_INT8;
+  else if (model->_weight_dtype == DType::kInt4) wfmt = FR_B200_W_INT4;
+  else RV_UNIMPLEMENTED() << "strategy " << strategy << ": this backend implements cuda fp16 / int8 / int4";
+  const char *cache_env = std::getenv("FR_B200_CACHE");
+  const bool use_cache = cache_env && cache_env[0] == '1';
+  const std::string cache = path + ".b200-" + (wfmt == FR_B200_W_FP16 ? "fp16" : wfmt == FR_B200_W_INT8 ? "int8" : "int4");
+  if (use_cache && load_from_cache(model, cache, wfmt, model->_act_dtype == DType::kFloat16)) return;
   std::ifstream in(path, std::ios::binary | std::ios::ate);
   RV_CHECK(in.good()) << "cannot open " << path;
   const std::streamsize len = in.tellg();
@@ -131,10 +167,7 @@ void init_model(Model *model, Device device, const std::string &path, const std:
   cfg.n_ffn = n_ffn;
   cfg.n_head = model->_head_size;
   cfg.vocab = (int)emb.size();
-  if (model->_weight_dtype == DType::kFloat16) cfg.weight_format = FR_B200_W_FP16;
-  else if (model->_weight_dtype == DType::kInt8) cfg.weight_format = FR_B200_W_INT8;
-  else if (model->_weight_dtype == DType::kInt4) cfg.weight_format = FR_B200_W_INT4;
-  else RV_UNIMPLEMENTED() << "strategy " << strategy << ": this backend implements cuda fp16 / int8 / int4";
+  cfg.weight_format = wfmt;
   cfg.act_fp16 = model->_act_dtype == DType::kFloat16;
   cfg.max_batch = 1;
   cfg.device = 0;
@@ -147,6 +180,7 @@ void init_model(Model *model, Device device, const std::string &path, const std:
   for (auto &kv : weights) upload(ex->h, kv.first, kv.second);
   for (size_t i = 0; i < emb.size(); ++i) upload(ex->h, "emb." + std::to_string(i), emb[i]);
   FRB_CALL(fr_b200_finalize(ex->h));
+  if (use_cache) fr_b200_save_packed(ex->h, cache.c_str());   // best effort: an unwritable directory just means no cache
   model->_extra = ex;
 }
 

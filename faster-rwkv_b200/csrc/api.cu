@@ -1,5 +1,6 @@
 // C-ABI implementation (include/fr_b200.h): model memory, tensor upload + repacking, the phase
 // table, decode launches, recurrent-state access.  No PyTorch types, no exceptions across the ABI.
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -1424,6 +1425,137 @@ int fr_b200_wait_selftest(int device, unsigned limit_us) {
   int status = 0;
   CU(cudaMemcpy(&status, st.p, 4, cudaMemcpyDeviceToHost));
   if (status) return fail(FR_B200_E_TIMEOUT, "device-side wait timed out (code " + std::to_string(status) + ")");
+  return FR_B200_OK;
+}
+
+// ---- packed model files ---------------------------------------------------------------------------------------------
+// A finalized model's device blobs, written back to back behind a small header: the streaming tiles (quantised
+// already), row scales, per-layer vectors, the embedding table and, for int8 / int4, the row-major packed copies.
+// Loading one is a handful of large reads and host-to-device copies: no msgpack parse, no per-row embedding uploads,
+// no re-quantisation (def::init_model, kernels/default/init_model.cpp:19-52,128-132, does all three on every start).
+namespace {
+struct PackedHeader {
+  char magic[8];             // "FRB200P2"
+  fr_b200_config cfg;        // max_batch / device / host_visible_state of the writer: replaced at load
+  int32_t emb_dtype, has_row_copies;
+  uint64_t weights_bytes, rscale_n, vecs_n, emb_bytes, qcopy_bytes, qscale_halfs, pscale_halfs;
+};
+constexpr size_t IO_CHUNK = 64u << 20;
+
+int write_blob(FILE *f, const void *dev, size_t bytes, void *pinned) {
+  for (size_t off = 0; off < bytes; off += IO_CHUNK) {
+    const size_t n = std::min(IO_CHUNK, bytes - off);
+    CU(cudaMemcpy(pinned, static_cast<const uint8_t *>(dev) + off, n, cudaMemcpyDeviceToHost));
+    if (fwrite(pinned, 1, n, f) != n) return fail(FR_B200_E_ARG, "short write to the packed model file");
+  }
+  return 0;
+}
+int read_blob(FILE *f, void *dev, size_t bytes, void *pinned) {
+  for (size_t off = 0; off < bytes; off += IO_CHUNK) {
+    const size_t n = std::min(IO_CHUNK, bytes - off);
+    if (fread(pinned, 1, n, f) != n) return fail(FR_B200_E_ARG, "packed model file is truncated");
+    CU(cudaMemcpy(static_cast<uint8_t *>(dev) + off, pinned, n, cudaMemcpyHostToDevice));
+  }
+  return 0;
+}
+struct PinnedBuf {
+  void *p = nullptr;
+  ~PinnedBuf() { if (p) cudaFreeHost(p); }
+};
+}  // namespace
+
+int fr_b200_save_packed(fr_b200_model *m, const char *path) {
+  if (!m || !path) return fail(FR_B200_E_ARG, "null argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  CU(cudaSetDevice(m->device));
+  CU(cudaDeviceSynchronize());
+  PackedHeader h;
+  memset(&h, 0, sizeof(h));
+  memcpy(h.magic, "FRB200P2", 8);
+  h.cfg = m->cfg;
+  h.emb_dtype = m->emb_dtype;
+  h.has_row_copies = m->d_qcopy != nullptr;
+  h.weights_bytes = m->weights_bytes; h.rscale_n = m->rscale_n; h.vecs_n = m->vecs_n;
+  h.emb_bytes = (uint64_t)m->V * m->C * (m->emb_dtype == FR_B200_T_F16 ? 2 : 4);
+  h.qcopy_bytes = m->d_qcopy ? m->qcopy_bytes : 0; h.qscale_halfs = m->d_qscale ? m->qscale_halfs : 0;
+  h.pscale_halfs = m->d_pscale ? m->pscale_halfs : 0;
+  PinnedBuf pin;
+  CU(cudaMallocHost(&pin.p, IO_CHUNK));
+  FILE *f = fopen(path, "wb");
+  if (!f) return fail(FR_B200_E_ARG, std::string("cannot open ") + path + " for writing");
+  int rc = fwrite(&h, sizeof(h), 1, f) == 1 ? 0 : fail(FR_B200_E_ARG, "short write to the packed model file");
+  if (!rc) rc = write_blob(f, m->d_weights, h.weights_bytes, pin.p);
+  if (!rc) rc = write_blob(f, m->d_rscale, h.rscale_n * 2, pin.p);
+  if (!rc) rc = write_blob(f, m->d_vecs, h.vecs_n * 4, pin.p);
+  if (!rc) rc = write_blob(f, m->d_emb, h.emb_bytes, pin.p);
+  if (!rc) rc = write_blob(f, m->d_qcopy, h.qcopy_bytes, pin.p);
+  if (!rc) rc = write_blob(f, m->d_qscale, h.qscale_halfs * 2, pin.p);
+  if (!rc) rc = write_blob(f, m->d_pscale, h.pscale_halfs * 2, pin.p);
+  if (fclose(f) != 0 && !rc) rc = fail(FR_B200_E_ARG, "closing the packed model file failed");
+  return rc;
+}
+
+int fr_b200_load_packed(const char *path, int max_batch, int device, int host_visible_state, fr_b200_model **out) {
+  if (!path || !out) return fail(FR_B200_E_ARG, "null argument");
+  *out = nullptr;
+  FILE *f = fopen(path, "rb");
+  if (!f) return fail(FR_B200_E_ARG, std::string("cannot open ") + path);
+  PackedHeader h;
+  if (fread(&h, sizeof(h), 1, f) != 1 || memcmp(h.magic, "FRB200P2", 8) != 0) {
+    fclose(f);
+    return fail(FR_B200_E_ARG, std::string(path) + " is not a packed model file of this library version");
+  }
+  fr_b200_config cfg = h.cfg;
+  cfg.max_batch = max_batch; cfg.device = device; cfg.host_visible_state = host_visible_state;
+  fr_b200_model *m = nullptr;
+  // the file decides whether the row copies exist, not this process's environment
+  const char *prev = getenv("FR_B200_ROW_COPIES");
+  const std::string prev_s = prev ? prev : "";
+  setenv("FR_B200_ROW_COPIES", h.has_row_copies || cfg.weight_format == FR_B200_W_FP16 ? "1" : "0", 1);
+  int rc = fr_b200_create(&cfg, &m);
+  if (prev) setenv("FR_B200_ROW_COPIES", prev_s.c_str(), 1); else unsetenv("FR_B200_ROW_COPIES");
+  if (rc) { fclose(f); return rc; }
+  const uint64_t emb_bytes = (uint64_t)m->V * m->C * (h.emb_dtype == FR_B200_T_F16 ? 2 : 4);
+  if (h.weights_bytes != m->weights_bytes || h.rscale_n != m->rscale_n || h.vecs_n != m->vecs_n || h.emb_bytes != emb_bytes ||
+      h.qcopy_bytes != m->qcopy_bytes || h.qscale_halfs != m->qscale_halfs || h.pscale_halfs != m->pscale_halfs ||
+      (h.emb_dtype != FR_B200_T_F16 && h.emb_dtype != FR_B200_T_F32)) {
+    fclose(f);
+    fr_b200_destroy(m);
+    return fail(FR_B200_E_ARG, "packed model file does not match this library's layout (written by another version?)");
+  }
+  PinnedBuf pin;
+  cudaError_t ce = cudaMallocHost(&pin.p, IO_CHUNK);
+  if (ce == cudaSuccess) ce = cudaMalloc((void **)&m->d_emb, emb_bytes);
+  if (ce != cudaSuccess) { fclose(f); fr_b200_destroy(m); return fail(FR_B200_E_NOMEM, cudaGetErrorString(ce)); }
+  m->emb_dtype = h.emb_dtype;
+  if (!rc) rc = read_blob(f, m->d_weights, h.weights_bytes, pin.p);
+  if (!rc) rc = read_blob(f, m->d_rscale, h.rscale_n * 2, pin.p);
+  if (!rc) rc = read_blob(f, m->d_vecs, h.vecs_n * 4, pin.p);
+  if (!rc) rc = read_blob(f, m->d_emb, h.emb_bytes, pin.p);
+  if (!rc) rc = read_blob(f, m->d_qcopy, h.qcopy_bytes, pin.p);
+  if (!rc) rc = read_blob(f, m->d_qscale, h.qscale_halfs * 2, pin.p);
+  if (!rc) rc = read_blob(f, m->d_pscale, h.pscale_halfs * 2, pin.p);
+  fclose(f);
+  if (!rc) {
+    for (auto &kv : m->mats) kv.second.set = true;
+    for (auto &kv : m->vecs) kv.second.set = true;
+    m->emb_rows_set.assign(m->V, 1);
+    // fp16 models created with their W^T copies (RWKV-5.x, or more than 8 streams) rebuild them from the tiles
+    if (m->d_plain) {
+      cudaFree(m->d_plain);
+      m->d_plain = nullptr;
+      rc = ensure_row_copies(m);
+    }
+  }
+  if (!rc) rc = fr_b200_finalize(m);
+  if (rc) { fr_b200_destroy(m); return rc; }
+  *out = m;
+  return FR_B200_OK;
+}
+
+int fr_b200_get_config(const fr_b200_model *m, fr_b200_config *cfg) {
+  if (!m || !cfg) return fail(FR_B200_E_ARG, "null argument");
+  *cfg = m->cfg;
   return FR_B200_OK;
 }
 

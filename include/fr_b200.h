@@ -82,6 +82,18 @@ int fr_b200_finalize(fr_b200_model *m);
 
 void fr_b200_destroy(fr_b200_model *m);
 
+/* Packed model files: everything fr_b200_finalize left on the device (the streaming tiles, already quantised for
+ * int8 / int4; row scales; per-layer vectors; the embedding table; the row-major packed copies) written back to back
+ * behind a header.  fr_b200_load_packed brings a model back with a few large reads and copies -- no msgpack parse, no
+ * upload per embedding row, no re-quantisation, which is what def::init_model does on every start
+ * (kernels/default/init_model.cpp:19-52, 128-132).  The weight format, version and shape come from the file;
+ * max_batch, device and host_visible_state are the caller's.  A file written by a library with another tile layout is
+ * refused (FR_B200_E_ARG).  The loaded model is finalized. */
+int fr_b200_save_packed(fr_b200_model *m, const char *path);
+int fr_b200_load_packed(const char *path, int max_batch, int device, int host_visible_state, fr_b200_model **out);
+/* The configuration a model was created with (for a model that came from a packed file: the file's). */
+int fr_b200_get_config(const fr_b200_model *m, fr_b200_config *cfg);
+
 /* ---- forward: replaces def::ModelForward (kernels/default/model_forward.cpp:22-193) and the
  * kernels it calls: layer_norm_op (kernels/cuda/layer_norm.cu:101-130), Mix / FfnOneMix
  * (kernels/cuda/att.cu:90-143, ffn.cu:15-32), gemm_cublas_tensor (kernels/cuda/matmul.cpp:105-122),

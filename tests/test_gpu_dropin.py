@@ -144,3 +144,20 @@ def test_state_file_roundtrip_through_the_reference_model_class(orc, synth, tmp_
             blk = ref.state[l * per:(l + 1) * per]
             for a, w in zip(arrs, (blk[:C], blk[C:C + H * 4096], blk[C + H * 4096:])):
                 assert np.abs(a - w).max() < 1e-2 * max(1.0, np.abs(w).max()), l
+
+
+@pytest.mark.skipif(not os.path.exists(DROPIN), reason="drop-in driver not built (needs the reference tree at build time)")
+@pytest.mark.parametrize("name,strategy,dtype", [("tiny4b", "cuda int4", "fp32"), ("tiny52", "cuda fp16", "fp16")])
+def test_packed_cache_behind_the_registry(synth, tmp_path, name, strategy, dtype):
+    """FR_B200_CACHE=1: the first rwkv::Model on a `.fr` file writes <file>.b200-<fmt>, the next one loads that instead of
+    parsing, uploading row by row and re-quantising; the logits are bit-identical."""
+    shape, tensors, fr = _model_file(synth, str(tmp_path), name, dtype)
+    ids = synth.token_ids(shape, 5, seed=8)
+    env = dict(os.environ, FR_B200_CACHE="1")
+    first = _run(DROPIN, fr, strategy, ids, str(tmp_path), env=env)
+    cache = fr + ".b200-" + strategy.split()[1]
+    assert os.path.exists(cache) and os.path.getsize(cache) > 1000
+    again = _run(DROPIN, fr, strategy, ids, str(tmp_path), env=env)
+    assert np.array_equal(first, again)
+    plain = _run(DROPIN, fr, strategy, ids, str(tmp_path))
+    assert np.array_equal(first, plain)

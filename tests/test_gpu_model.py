@@ -195,3 +195,31 @@ def test_cuda_path_against_reference_golden(pkg, synth, name):
         rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
         assert err < ABS_TOL and rel < REL_TOL, (name, err, rel)
     m.close()
+
+
+@pytest.mark.parametrize("strat", STRATS, ids=[s[0] for s in STRATS])
+@pytest.mark.parametrize("name,B", [("tiny4b", 1), ("tiny52", 12)])
+def test_packed_file_load_equals_fresh_load(pkg, orc, synth, tmp_path, name, B, strat):
+    """A model written with save_packed and read back with load_packed holds the same bits: every projection matrix out
+    of the streaming tiles, the logits of a few steps, a prompt and (12 streams) a step through the GEMM path."""
+    shape, tensors, m, ref = _pair(pkg, orc, synth, name, strat, max_batch=B)
+    path = str(tmp_path / "model.b200")
+    m.save_packed(path)
+    m2 = pkg.Model.load_packed(path, shape, strat[0], max_batch=B)
+    for pname in synth.param_names(shape):
+        if pname.endswith(orc.MATRIX_SUFFIXES):
+            K, N = np.asarray(tensors[pname]).shape
+            assert np.array_equal(m.unpack_matrix(pname, K, N), m2.unpack_matrix(pname, K, N)), pname
+    for t in (3, 7, 3):
+        assert np.array_equal(m.run(t), m2.run(t))
+    prompt = [int(t) for t in synth.token_ids(shape, 40, seed=6)]
+    assert np.array_equal(m.run(prompt), m2.run(prompt))
+    if B > 8:
+        ids = synth.token_ids(shape, B, seed=4)
+        assert np.array_equal(m.decode(ids), m2.decode(ids))
+    with open(path, "r+b") as f:          # a foreign header is refused, not half loaded
+        f.write(b"NOTAFILE")
+    with pytest.raises(pkg.FrB200Error):
+        pkg.Model.load_packed(path, shape, strat[0])
+    m.close()
+    m2.close()
