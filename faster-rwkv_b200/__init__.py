@@ -62,6 +62,7 @@ SIGNATURES = {
     "fr_b200_decode": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "fr_b200_decode_greedy": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "fr_b200_logits_device": (_i, [_vp, ctypes.POINTER(_vp)]),
+    "fr_b200_logits_add": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
     "fr_b200_sample": (_i, [_vp, _i, ctypes.c_float, _i, ctypes.c_float, _vp, _vp, _vp]),
     "fr_b200_vocab_padded": (_i, [_vp]),
     "fr_b200_run_seq": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
@@ -235,6 +236,12 @@ class Model:
         check(lib().fr_b200_sample(self._h, batch, temperature, top_k, top_p, _np_ptr(u), _np_ptr(out), None),
               "fr_b200_sample")
         return out
+
+    def logits_add(self, streams, tokens, deltas) -> None:
+        """logits[streams[i]][tokens[i]] += deltas[i] on the device (penalties / biases before `sample`, chat.cpp:57-75)."""
+        s, t = np.ascontiguousarray(streams, np.int32), np.ascontiguousarray(tokens, np.int32)
+        d = np.ascontiguousarray(deltas, np.float32)
+        check(lib().fr_b200_logits_add(self._h, len(s), _np_ptr(s), _np_ptr(t), _np_ptr(d), None), "fr_b200_logits_add")
 
     def decode_profile(self, ids: Sequence[int]) -> np.ndarray:
         """One decode step; returns the [n_ctas, n_phases, 8] trace described at fr_b200_decode_profile in include/fr_b200.h."""

@@ -25,7 +25,7 @@ def build(force: bool = False) -> str:
         raise RuntimeError(f"reference tree not found at {REF}")
     os.makedirs(OUT, exist_ok=True)
     exe = os.path.join(OUT, "fr_b200_run")
-    srcs = [os.path.join(REF, f) for f in ("model.cpp", "tensor.cpp", "utils.cpp")]
+    srcs = [os.path.join(REF, f) for f in ("model.cpp", "tensor.cpp", "utils.cpp", "sampler.cpp")]
     for d in ("kernels/cpu", "kernels/default", "kernels/shape"):
         srcs += sorted(glob.glob(os.path.join(REF, d, "*.cpp")))
     srcs.append(os.path.join(REF, "kernels/export-ncnn/kernels.cpp"))

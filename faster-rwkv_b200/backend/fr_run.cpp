@@ -17,6 +17,7 @@
 
 #include <kernels/kernels.h>
 #include <model.h>
+#include <sampler.h>
 
 // --ops-test: the body of the reference's tests/test_ops.cpp:9-16 on the registered CUDA operators: fill_(1) then
 // scalar_div_(2) must leave 0.5 in every element.  Prints "ops_test ok".
@@ -39,8 +40,35 @@ static int ops_test() {
   return 0;
 }
 
+// --sample logits.bin V rows temperature top_k top_p seed draws: the reference's own Sampler (sampler.cpp:38-101, with its
+// CPU softmax) on `rows` rows of V fp32 logits; for every row the generator is seeded with `seed` and `draws` tokens
+// are drawn from the same logits.  Prints one line "sample <row> <id> <id> ..." per row.
+static int sample_mode(int argc, char **argv) {
+  if (argc < 10) { std::fprintf(stderr, "usage: --sample logits.bin V rows temperature top_k top_p seed draws\n"); return 2; }
+  try {
+    const int V = std::atoi(argv[3]), rows = std::atoi(argv[4]), top_k = std::atoi(argv[6]), seed = std::atoi(argv[8]), draws = std::atoi(argv[9]);
+    const float temperature = (float)std::atof(argv[5]), top_p = (float)std::atof(argv[7]);
+    std::ifstream in(argv[2], std::ios::binary);
+    if (!in.good()) { std::fprintf(stderr, "error: cannot open %s\n", argv[2]); return 1; }
+    rwkv::Sampler sampler;
+    for (int r = 0; r < rows; ++r) {
+      rwkv::Tensor logits = rwkv::Tensor::Empty({V}, rwkv::DType::kFloat32, rwkv::Device::kCPU);
+      in.read(reinterpret_cast<char *>(logits.data_ptr<float>()), (std::streamsize)V * 4);
+      sampler.set_seed(seed);
+      std::printf("sample %d", r);
+      for (int d = 0; d < draws; ++d) std::printf(" %d", sampler.Sample(logits, temperature, top_k, top_p));
+      std::printf("\n");
+    }
+  } catch (const std::exception &e) {
+    std::fprintf(stderr, "error: %s\n", e.what());
+    return 1;
+  }
+  return 0;
+}
+
 int main(int argc, char **argv) {
   if (argc >= 2 && !std::strcmp(argv[1], "--ops-test")) return ops_test();
+  if (argc >= 2 && !std::strcmp(argv[1], "--sample")) return sample_mode(argc, argv);
   if (argc < 5) {
     std::fprintf(stderr, "usage: %s model.fr strategy out.bin [--seq] ids...\n", argv[0]);
     return 2;

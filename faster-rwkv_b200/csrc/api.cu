@@ -89,6 +89,7 @@ struct fr_b200_model {
   // greedy runs of many streams: two decode steps captured as a CUDA graph and replayed (the step is ~170 launches)
   GreedyCtl *d_ctl = nullptr;
   uint8_t *d_sample = nullptr; size_t sample_bytes = 0;   // scratch of fr_b200_sample
+  uint8_t *d_adj = nullptr; size_t adj_bytes = 0;         // staging of fr_b200_logits_add
   cudaStream_t gstream = nullptr;
   cudaEvent_t gev = nullptr;
   cudaGraphExec_t gexec = nullptr;
@@ -447,6 +448,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   if (m->gstream) cudaStreamDestroy(m->gstream);
   if (m->d_ctl) cudaFree(m->d_ctl);
   if (m->d_sample) cudaFree(m->d_sample);
+  if (m->d_adj) cudaFree(m->d_adj);
   if (m->d_hist) cudaFree(m->d_hist);
   delete m;
 }
@@ -913,6 +915,33 @@ int fr_b200_sample(fr_b200_model *m, int batch, float temperature, int top_k, fl
   m->launches += 4;
   CU(cudaMemcpyAsync(ids, d_ids, (size_t)batch * 4, cudaMemcpyDefault, st));
   if (is_host_ptr(ids)) CU(cudaStreamSynchronize(st));
+  return FR_B200_OK;
+}
+
+int fr_b200_logits_add(fr_b200_model *m, int n, const int32_t *streams, const int32_t *tokens, const float *deltas, void *stream) {
+  if (!m || n < 0 || (n > 0 && (!streams || !tokens || !deltas))) return fail(FR_B200_E_ARG, "bad argument");
+  if (!m->finalized) return fail(FR_B200_E_STATE, "finalize the model first");
+  if (n == 0) return FR_B200_OK;
+  for (int i = 0; i < n; ++i)
+    if (streams[i] < 0 || streams[i] >= m->cfg.max_batch || tokens[i] < 0 || tokens[i] >= m->V)
+      return fail(FR_B200_E_ARG, "stream or token id out of range");
+  CU(cudaSetDevice(m->device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t piece = align256((size_t)n * 4);
+  if (m->adj_bytes < 3 * piece) {
+    CU(cudaStreamSynchronize(st));
+    if (m->d_adj) cudaFree(m->d_adj);
+    m->d_adj = nullptr; m->adj_bytes = 0;
+    CU(cudaMalloc((void **)&m->d_adj, 3 * piece));
+    m->adj_bytes = 3 * piece;
+  }
+  CU(cudaMemcpyAsync(m->d_adj, streams, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(m->d_adj + piece, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(m->d_adj + 2 * piece, deltas, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+  CU(launch_logits_add(m->d_out, m->Vpad, reinterpret_cast<const int32_t *>(m->d_adj), reinterpret_cast<const int32_t *>(m->d_adj + piece),
+                       reinterpret_cast<const float *>(m->d_adj + 2 * piece), n, st));
+  CU(cudaStreamSynchronize(st));   // the host arrays were pageable: they may be reused once this returns
+  m->launches++;
   return FR_B200_OK;
 }
 

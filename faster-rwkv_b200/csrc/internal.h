@@ -189,6 +189,7 @@ cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st);
 size_t sample_scratch_bytes(int rows, int V);
 cudaError_t launch_sample_rows(const float *logits, int rows, int V, int ld, float temperature, int top_k, float top_p,
                                const float *u, int32_t *out, void *scratch, size_t scratch_bytes, cudaStream_t st);
+cudaError_t launch_logits_add(float *logits, int ld, const int32_t *stream, const int32_t *token, const float *delta, int n, cudaStream_t st);
 struct GreedyCtl {           // device-side cursor of a greedy run through the GEMM path
   int32_t *hist;             // [n_tokens][rows] sampled ids
   int step;                  // next row of hist

@@ -49,30 +49,81 @@ __global__ void segment_offsets_kernel(int rows, int V, int *off) {
   if (i <= rows) off[i] = i * V;
 }
 
-// one thread per row walks the sorted probabilities in order, exactly as the reference's loops do
-__global__ void pick_rows_kernel(const float *sorted_p, const int32_t *sorted_id, int V, float temperature, int top_k, float top_p,
-                                 const float *u, int32_t *out, int rows) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= rows) return;
+// Block-wide exclusive prefix sum of one value per thread (256 threads); total = the sum over the block.
+__device__ __forceinline__ float block_excl_scan(float v, float *sh, float &total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  __syncthreads();                 // sh may still be read from the previous call
+  if (lane == 31) sh[warp] = inc;
+  __syncthreads();
+  float base = 0.f, tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    if (w < warp) base += sh[w];
+    tot += sh[w];
+  }
+  total = tot;
+  return base + inc - v;
+}
+
+// One CTA per row over the sorted probabilities: the reference's three loops (top-p prefix, temperature weights, the
+// inverse-CDF walk: sampler.cpp:59-66, 86-93, 22-30) each become a per-thread walk over a contiguous segment plus a
+// block scan of the segment sums.  Running sums therefore differ from the reference's strictly serial ones by fp32
+// rounding only; a draw that lands within that distance of a threshold may resolve to the neighbouring entry.
+__global__ void __launch_bounds__(256) pick_rows_kernel(const float *sorted_p, const int32_t *sorted_id, int V, float temperature, int top_k,
+                                                        float top_p, const float *u, int32_t *out) {
+  __shared__ float sh[8];
+  __shared__ int cut;
+  const int row = blockIdx.x;
   const float *p = sorted_p + (size_t)row * V;
-  int len = V;
-  float cum = 0.f;
-  for (int i = 0; i < V; ++i) {
-    cum += p[i];
-    if (cum >= top_p) { len = i + 1; break; }
+  const int S = (V + 255) / 256, lo = min(V, (int)threadIdx.x * S), hi = min(V, lo + S);
+  if (threadIdx.x == 0) cut = V;
+  // top-p: the shortest prefix whose running sum reaches top_p
+  float seg = 0.f, total;
+  for (int i = lo; i < hi; ++i) seg += p[i];
+  float before = block_excl_scan(seg, sh, total);
+  if (before < top_p && before + seg >= top_p) {
+    float c = before;
+    for (int i = lo; i < hi; ++i) {
+      c += p[i];
+      if (c >= top_p) { atomicMin(&cut, i + 1); break; }
+    }
   }
+  __syncthreads();
+  int len = cut;
   if (top_k > 0) len = min(len, top_k);
+  __syncthreads();
+  // weights p ^ (1 / temperature) over the kept prefix, then the first entry whose running weight reaches u * total
   const float it = 1.f / fminf(fmaxf(temperature, 0.1f), 5.f);
-  float total = 0.f;
-  for (int i = 0; i < len; ++i) total += powf(p[i], it);
+  const int h2 = min(hi, len);
+  seg = 0.f;
+  for (int i = lo; i < h2; ++i) seg += powf(p[i], it);
+  before = block_excl_scan(seg, sh, total);
   const float rv = u[row] * total;
-  cum = 0.f;
-  int pick = len - 1;
-  for (int i = 0; i < len; ++i) {
-    cum += powf(p[i], it);
-    if (cum >= rv) { pick = i; break; }
+  if (threadIdx.x == 0) cut = len - 1;
+  __syncthreads();
+  if (lo < h2 && before < rv && before + seg >= rv) {
+    float c = before;
+    for (int i = lo; i < h2; ++i) {
+      c += powf(p[i], it);
+      if (c >= rv) { atomicMin(&cut, i); break; }
+    }
   }
-  out[row] = sorted_id[(size_t)row * V + pick];
+  if (threadIdx.x == 0 && rv <= 0.f) atomicMin(&cut, 0);   // u = 0: the first entry already reaches the draw
+  __syncthreads();
+  if (threadIdx.x == 0) out[row] = sorted_id[(size_t)row * V + cut];
+}
+
+// logits[stream[i]][token[i]] += delta[i]: the sparse adjustments a chat loop makes before sampling (frequency /
+// presence penalties and the end-of-text / newline biases of chat.cpp:57-75), without the logits leaving the device
+__global__ void logits_add_kernel(float *logits, int ld, const int32_t *stream, const int32_t *token, const float *delta, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) atomicAdd(logits + (size_t)stream[i] * ld + token[i], delta[i]);
 }
 
 }  // namespace
@@ -99,7 +150,12 @@ cudaError_t launch_sample_rows(const float *logits, int rows, int V, int ld, flo
   cudaError_t e = cub::DeviceSegmentedRadixSort::SortPairsDescending(temp, temp_bytes, probs, sorted_p, ids, sorted_id, (int)n, rows, off,
                                                                      off + 1, 0, 32, st);
   if (e != cudaSuccess) return e;
-  pick_rows_kernel<<<(rows + 63) / 64, 64, 0, st>>>(sorted_p, sorted_id, V, temperature, top_k, top_p, u, out, rows);
+  pick_rows_kernel<<<rows, 256, 0, st>>>(sorted_p, sorted_id, V, temperature, top_k, top_p, u, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_logits_add(float *logits, int ld, const int32_t *stream, const int32_t *token, const float *delta, int n, cudaStream_t st) {
+  if (n > 0) logits_add_kernel<<<(n + 255) / 256, 256, 0, st>>>(logits, ld, stream, token, delta, n);
   return cudaGetLastError();
 }
 

@@ -122,6 +122,11 @@ int fr_b200_decode_greedy(fr_b200_model *m, const int32_t *first_ids, int batch,
 int fr_b200_sample(fr_b200_model *m, int batch, float temperature, int top_k, float top_p, const float *uniform,
                    int32_t *ids, void *stream);
 
+/* logits[streams[i]][tokens[i]] += deltas[i] for i < n, on the logits the last decode left on the device: the sparse
+ * adjustments a chat loop makes before it samples -- frequency / presence penalties and the end-of-text / newline
+ * biases of chat.cpp:57-75 -- so that sampling can stay on the device.  streams, tokens, deltas: host arrays. */
+int fr_b200_logits_add(fr_b200_model *m, int n, const int32_t *streams, const int32_t *tokens, const float *deltas, void *stream);
+
 /* Device pointer of the [max_batch, vocab_padded] fp32 logits of the last decode (row stride =
  * fr_b200_vocab_padded()); valid until the next decode. */
 int fr_b200_logits_device(fr_b200_model *m, float **ptr);

@@ -63,3 +63,30 @@ def test_oracle_against_live_reference_cpu(orc, synth, tmp_path):
     m = orc.OracleModel(shape, tensors, synth.param_names(shape))
     got = np.stack([m.run(i) for i in ids])
     assert np.abs(got - want).max() < 5e-5
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(os.path.dirname(HERE), "oracle", "_ref", "fr_ref_run")),
+                    reason="needs oracle/_ref/fr_ref_run (built where the reference tree is)")
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 0.9), (0.7, 20, 0.95), (2.0, 0, 1.0), (1.0, 1, 0.3), (0.05, 0, 0.5)])
+def test_sampler_restatement_against_the_reference_sampler(tmp_path, temperature, top_k, top_p):
+    """oracle/sampler_ref.py against the reference's own Sampler::Sample (sampler.cpp + kernels/cpu/softmax.cpp, compiled
+    from their sources) at vocab 65536: seeded std::minstd_rand0 draws on seeded logits give the same token ids."""
+    from oracle.sampler_ref import minstd_uniforms, ref_sample
+    exe = os.path.join(os.path.dirname(HERE), "oracle", "_ref", "fr_ref_run")
+    rng = np.random.default_rng(11)
+    V, B, draws, seed = 65536, 3, 10, 7
+    logits = (rng.standard_normal((B, V)) * 6).astype(np.float32)
+    lf = str(tmp_path / "logits.bin")
+    logits.tofile(lf)
+    r = subprocess.run([exe, "--sample", lf, str(V), str(B), str(temperature), str(top_k), str(top_p), str(seed), str(draws)],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    theirs = np.array([[int(x) for x in line.split()[2:]] for line in r.stdout.splitlines() if line.startswith("sample")])
+    us = minstd_uniforms(seed, draws)
+    agree = 0
+    for b in range(B):
+        for d in range(draws):
+            want, margin = ref_sample(logits[b], temperature, top_k, top_p, np.float32(us[d]))
+            assert want == theirs[b, d] or margin <= 1e-5
+            agree += want == theirs[b, d]
+    assert agree >= B * draws - 2

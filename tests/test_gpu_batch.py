@@ -107,3 +107,28 @@ def test_prompts_of_any_model_use_the_rows_path(pkg, orc, synth, name, fmt, monk
     _close(got, ref.run_seq(ids), f"{name} {fmt} prompt")
     _close(m.run(3), ref.run(3), f"{name} {fmt} next token")
     m.close()
+
+
+def test_state_export_import_per_slot(pkg, orc, synth):
+    """Every stream slot of a 12-stream model exports and imports on its own: a slot's state moved to another slot
+    continues exactly as the original does, and the other slots are untouched."""
+    shape, m, ref = _pair(pkg, orc, synth, "tiny52", "fp16", 12)
+    ids = synth.token_ids(shape, 36, seed=13).reshape(3, 12)
+    for t in range(2):
+        m.decode(ids[t])
+    snap = [m.export_state(b) for b in range(12)]
+    m.import_state(snap[3], slot=9)                       # stream 9 becomes a copy of stream 3
+    nxt = ids[2].copy()
+    nxt[9] = nxt[3]
+    got = m.decode(nxt)
+    assert np.array_equal(got[9], got[3])
+    ref.reset()
+    for t in range(2):
+        ref.run(int(ids[t, 3]))
+    _close(got[9], ref.run(int(nxt[3])), "moved stream")
+    for b in (0, 5, 11):                                  # untouched slots: export -> reset -> import restores them
+        now = m.export_state(b)
+        m.reset_states(b)
+        m.import_state(now, slot=b)
+        assert np.array_equal(m.export_state(b), now)
+    m.close()

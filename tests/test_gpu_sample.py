@@ -1,36 +1,12 @@
 """Device-side sampling against a numpy restatement of Sampler::Sample (sampler.cpp:38-101) + the CPU softmax it
-calls (kernels/cpu/softmax.cpp:6-21): same logits, same uniform draw -> same token."""
+calls (kernels/cpu/softmax.cpp:6-21), oracle/sampler_ref.py, itself pinned against the reference's own sampler compiled
+from its sources: same logits, same uniform draw -> same token."""
 import numpy as np
 import pytest
 
+from oracle.sampler_ref import minstd_uniforms as _minstd_uniforms, ref_sample
+
 pytestmark = pytest.mark.gpu
-
-
-def ref_sample(logits, temperature, top_k, top_p, u):
-    """-> (token id, margin): margin = distance of the decisive running sums from their thresholds; a float32 sum
-    taken in another order can only flip the outcome when it is tiny."""
-    l = logits.astype(np.float32)
-    e = np.exp(l - l.max()).astype(np.float32)
-    p = (e / np.cumsum(e, dtype=np.float32)[-1]).astype(np.float32)
-    order = np.argsort(-p, kind="stable")
-    ps = p[order]
-    c = np.cumsum(ps, dtype=np.float32)
-    hit = np.nonzero(c >= np.float32(top_p))[0]
-    n = int(hit[0]) + 1 if len(hit) else len(ps)
-    margin = float(abs(c[n - 1] - top_p)) if len(hit) else 1.0
-    if n > 1:
-        margin = min(margin, float(abs(c[n - 2] - top_p)))
-    if top_k > 0:
-        n = min(n, top_k)
-    t = np.float32(min(max(temperature, 0.1), 5.0))
-    w = np.power(ps[:n], np.float32(1.0) / t).astype(np.float32)
-    cw = np.cumsum(w, dtype=np.float32)
-    rv = np.float32(u) * cw[-1]
-    j = int(np.nonzero(cw >= rv)[0][0])
-    margin = min(margin, float(abs(cw[j] - rv)) / float(cw[-1]))
-    if j > 0:
-        margin = min(margin, float(abs(cw[j - 1] - rv)) / float(cw[-1]))
-    return int(order[j]), margin
 
 
 @pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 0.9), (0.7, 20, 0.95), (2.0, 5, 1.0), (1.0, 1, 0.5),
@@ -67,4 +43,53 @@ def test_sample_single_stream_after_run(pkg, synth):
     want, margin = ref_sample(logits, 1.0, 0, 0.8, 0.37)
     got = m.sample(1, 1.0, 0, 0.8, [0.37])
     assert margin < 1e-5 or got[0] == want
+    m.close()
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 0.9), (0.7, 20, 0.95), (2.0, 0, 1.0), (1.0, 1, 0.3)])
+def test_sample_matches_the_reference_sampler_binary_at_full_vocab(pkg, synth, tmp_path, temperature, top_k, top_p):
+    """The reference's own Sampler::Sample + CPU softmax (sampler.cpp, kernels/cpu/softmax.cpp compiled from where they
+    lie into the driver binary, `--sample` mode) against fr_b200_sample on the same logits at vocab 65536, seeded
+    std::minstd_rand0 draws, with frequency / presence penalties applied on the device (fr_b200_logits_add) and on the
+    host copy alike (chat.cpp:57-61)."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "fr_ref_run")
+    if not os.path.exists(exe):
+        pytest.skip("reference sampler not built (needs the reference tree at build time)")
+    shape = synth.Shape("4", 1, 64, 64, 65536)
+    master = synth.generate(shape, seed=3, ln_random=True)
+    master["head.weight"] = master["head.weight"] * 6.0          # peaked logits, as a trained model's
+    tensors = synth.to_file_dtypes(shape, master, "fp16")
+    B, draws, seed = 4, 8, 42
+    m = pkg.Model(tensors, "cuda fp16", shape=shape, max_batch=B)
+    logits = m.decode(synth.token_ids(shape, B, seed=1)).copy()
+    # penalties: a few tokens per stream, logit -= frequency * occurrence + presence
+    rng = np.random.default_rng(5)
+    streams = np.repeat(np.arange(B), 3).astype(np.int32)
+    tokens = np.concatenate([np.argsort(-logits[b])[:3] for b in range(B)]).astype(np.int32)
+    deltas = -(0.2 * rng.integers(1, 4, len(tokens)) + 0.2).astype(np.float32)
+    m.logits_add(streams, tokens, deltas)
+    for s, t, d in zip(streams, tokens, deltas):
+        logits[s, t] += d
+    lf = str(tmp_path / "logits.bin")
+    logits.astype(np.float32).tofile(lf)
+    r = subprocess.run([exe, "--sample", lf, str(shape.vocab), str(B), str(temperature), str(top_k), str(top_p), str(seed), str(draws)],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    theirs = np.array([[int(x) for x in line.split()[2:]] for line in r.stdout.splitlines() if line.startswith("sample")])
+    assert theirs.shape == (B, draws)
+    us = _minstd_uniforms(seed, draws)
+    checked = 0
+    for d in range(draws):
+        got = m.sample(B, temperature, top_k, top_p, [us[d]] * B)
+        for b in range(B):
+            want, margin = ref_sample(logits[b], temperature, top_k, top_p, np.float32(us[d]))
+            assert want == theirs[b, d] or margin <= 1e-5       # the numpy restatement agrees with the reference binary
+            # the device sums up to 65536 weights in segments, the reference serially: a draw closer than 1e-4 (relative
+            # to the total) to a threshold may resolve to the neighbouring entry
+            if margin > 1e-4:
+                assert got[b] == theirs[b, d], (d, b, int(got[b]), int(theirs[b, d]), margin)
+                checked += 1
+    assert checked >= B * draws // 2
     m.close()
