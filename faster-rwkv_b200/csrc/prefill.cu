@@ -521,7 +521,7 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
 // nibbles [N, K/2] with fp16 group scales [N, K/32]: the bytes a step has to stream) and expanded to the K-major fp16
 // tile the tensor core wants inside the kernel, by four warps that do nothing else.  Per K slice of 64 inputs:
 //   warp 0      TMA: the packed 128-row weight tile (8 KB int8 / 4 KB int4) + the X tile(s) into a ring slot
-//   warps 6..9  expanders: packed tile -> 128 x 64 fp16 in the 128-byte-swizzled layout of a TMA-loaded tile
+//   warps 6..13 expanders (two threads per row): packed tile -> 128 x 64 fp16 in the 128-byte-swizzled layout of a TMA-loaded tile
 //               (int8: the integer code, exact in fp16, the row scale is applied to the accumulator;
 //                int4: hi = fp16(q * scale) and lo = q * scale - hi, an exact pair), double-buffered
 //   warp 1      MMA: acc += W_hi X_hi (+ W_hi X_lo) (+ W_lo X_hi)
@@ -529,7 +529,8 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
 // A ring slot is free again when the expanders have read its weight bytes and the MMAs its X tiles; an expanded
 // buffer when the MMAs that read it have retired.  Shared-memory writes of the expanders are made visible to the
 // tensor core's (asynchronous) reads with fence.proxy.async before the barrier arrive.
-constexpr int WQ_THREADS = 320;
+constexpr int WQ_EXP_WARPS = 8;
+constexpr int WQ_THREADS = 192 + 32 * WQ_EXP_WARPS;
 constexpr int WQ_NE = 2;   // expanded buffers
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -578,8 +579,8 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   const bool x_lo = g.A2 != nullptr;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 5); }   // 4 expander warps + the MMA commit
-    for (int e = 0; e < WQ_NE; ++e) { mbar_init(&a_full[e], 4); mbar_init(&a_empty[e], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], WQ_EXP_WARPS + 1); }   // expander warps + the MMA commit
+    for (int e = 0; e < WQ_NE; ++e) { mbar_init(&a_full[e], WQ_EXP_WARPS); mbar_init(&a_empty[e], 1); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -636,8 +637,9 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
       umma_commit(acc_full);
     }
   } else if (warp >= 6) {
-    // expanders: lane l of expander warp w owns row 32 w + l of the tile
-    const int row = (warp - 6) * 32 + lane;
+    // expanders: two threads per row of the tile, each expands half of the row's 64 inputs
+    const int et = (int)threadIdx.x - 192;
+    const int row = et >> 1, half = et & 1;
     const int ch = tile_n * GBM + row;                      // output channel of this row
     const uint32_t swz = (uint32_t)(row & 7);
     const uint32_t erow = (uint32_t)row * 128u;             // byte offset of the row inside an expanded tile
@@ -655,10 +657,11 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
       const uint32_t src = tiles + (uint32_t)s * STAGE_BYTES + (uint32_t)row * ROW_B;
       const uint32_t dst = etiles + (uint32_t)e * E_BYTES + erow;
       if (FMT == FMT_INT8) {
-        // four 16-byte pieces of 16 codes; lanes start at different pieces so that a quarter warp touches 8 banks groups
+        // two 16-byte pieces of 16 codes per thread; neighbouring rows take theirs in opposite order, which spreads a
+        // quarter warp's stores over all eight 16-byte columns of the swizzled rows
 #pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
-          const uint32_t piece = (uint32_t)(pp + lane) & 3u;
+        for (int pp = 0; pp < 2; ++pp) {
+          const uint32_t piece = (uint32_t)half * 2u + ((uint32_t)(pp + row) & 1u);
           const uint4 w = lds128(src + piece * 16u);
           const uint32_t M = 0x64646464u, OFF = 0x64806480u;    // 1024 + (code + 128) - 1152 = code
           const uint32_t wx = w.x ^ 0x80808080u, wy = w.y ^ 0x80808080u, wz = w.z ^ 0x80808080u, ww = w.w ^ 0x80808080u;
@@ -670,10 +673,9 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
           sts128(dst + (((piece * 2u + 1u) ^ swz) << 4), o1);
         }
       } else {
-        // two 16-byte pieces of 32 nibbles = the two scale groups of the slice
-#pragma unroll
-        for (int pp = 0; pp < 2; ++pp) {
-          const uint32_t piece = (uint32_t)(pp + lane) & 1u;
+        // one 16-byte piece of 32 nibbles per thread = one of the two scale groups of the slice
+        {
+          const uint32_t piece = (uint32_t)half;
           const uint4 w = lds128(src + piece * 16u);
           const uint32_t s16 = piece ? (sc >> 16) : (sc & 0xffffu);
           const uint32_t s2 = s16 | (s16 << 16);
@@ -1434,8 +1436,18 @@ cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
   grp.tile_start[n] = tiles;
   const int m_tiles = (M + bn - 1) / bn;
   grp.split = 1;
+  grp.stage_bytes = 8192u + ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
+  const uint32_t ebytes = WQ_NE * (fmt == FMT_INT4 ? 2u : 1u) * G_A_BYTES;
+  // two CTAs per SM where a ring of >= 2 slots fits beside the expanded buffers in half an SM's shared memory (few rows:
+  // the step is a chain of short GEMMs, and a second CTA hides the hand-overs between the kernel's roles), else one CTA
+  // with as deep a ring as fits
+  int stages = (int)(((110u << 10) - ebytes) / grp.stage_bytes);
+  const bool two_per_sm = stages >= 2;
+  if (!two_per_sm) stages = (int)(((200u << 10) - ebytes) / grp.stage_bytes);
+  grp.stages = std::max(2, std::min(stages, WT_MAX_STAGES));
+  const size_t smem = 1024 + ebytes + (size_t)grp.stages * grp.stage_bytes + 1024;
   const int sms = device_sm_count();
-  const int slots = bn <= 64 ? 2 * sms : sms;
+  const int slots = two_per_sm ? 2 * sms : sms;
   if (raw_ok) {
     const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 4));
     float best = 0.f;
@@ -1445,13 +1457,6 @@ cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
       if (sp == 1 || cost < best) { best = cost; grp.split = sp; }
     }
   }
-  grp.stage_bytes = 8192u + ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
-  const uint32_t ebytes = WQ_NE * (fmt == FMT_INT4 ? 2u : 1u) * G_A_BYTES;
-  // two CTAs per SM with rings of >= 3 slots where they fit, else one CTA with as deep a ring as fits
-  int stages = (int)(((100u << 10) - ebytes) / grp.stage_bytes);
-  if (stages < 3) stages = (int)(((200u << 10) - ebytes) / grp.stage_bytes);
-  grp.stages = std::max(2, std::min(stages, WT_MAX_STAGES));
-  const size_t smem = 1024 + ebytes + (size_t)grp.stages * grp.stage_bytes + 1024;
   dim3 grid(tiles, m_tiles, grp.split);
   cudaError_t e = cudaErrorInvalidValue;
 #define FRB_WQ(BNV) (fmt == FMT_INT8 ? launch_gemm_wq_t<BNV, FMT_INT8>(maps, grp, grid, smem, st) : launch_gemm_wq_t<BNV, FMT_INT4>(maps, grp, grid, smem, st))
