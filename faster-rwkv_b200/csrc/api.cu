@@ -95,6 +95,8 @@ struct fr_b200_model {
   cudaGraphExec_t gexec = nullptr;
   int g_batch = 0; unsigned g_par = 0; const void *g_seq = nullptr;   // what the captured graph was built for
   float *d_lnvec = nullptr;           // ln_out of the last prompt token
+  cudaStream_t seq_streams[4] = {nullptr, nullptr, nullptr, nullptr};   // long prompts: one stream per piece of rows
+  std::vector<cudaEvent_t> seq_events;                                  // [piece][layer] + one start event
   // scratch for uploads
   void *d_scratch[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t scratch_bytes[4] = {0, 0, 0, 0};
@@ -446,6 +448,8 @@ void fr_b200_destroy(fr_b200_model *m) {
   if (m->gexec) cudaGraphExecDestroy(m->gexec);
   if (m->gev) cudaEventDestroy(m->gev);
   if (m->gstream) cudaStreamDestroy(m->gstream);
+  for (cudaEvent_t ev : m->seq_events) cudaEventDestroy(ev);
+  for (cudaStream_t sq : m->seq_streams) if (sq) cudaStreamDestroy(sq);
   if (m->d_ctl) cudaFree(m->d_ctl);
   if (m->d_sample) cudaFree(m->d_sample);
   if (m->d_adj) cudaFree(m->d_adj);
@@ -973,14 +977,24 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
                o_lo2 = take(batch_mode ? TC * 2 : 0), o_lo3 = take(batch_mode ? TC * 2 : 0), o_ynlo = take(batch_mode ? TC * 2 : 0),
                o_kklo = take(batch_mode ? TF * 2 : 0), o_glo = take(batch_mode ? TC * 2 : 0),
                o_raw = take(T <= GEMM_SMALL_M ? (size_t)GEMM_SPLIT_MAX * T * std::max(4 * C, F + C) * 4 : 0);   // split-K slabs
-  // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
-  int n_chunks = 1, chunk_len = T;
-  if (!batch_mode && m->v5) {
-    n_chunks = std::max(1, std::min(T / 32, (8 * device_sm_count() + H - 1) / H));
-    chunk_len = (T + n_chunks - 1) / n_chunks;
-    n_chunks = (T + chunk_len - 1) / chunk_len;
+  // Long prompts are cut into pieces of rows that run on streams of their own, a layer apart: piece p's layer l needs
+  // piece p's layer l - 1 (its stream order) and the recurrent state piece p - 1 left after layer l (an event), nothing
+  // else -- the token shift crosses the cut through the stored shift state, like two prompts fed one after the other.
+  // The tail wave of one piece's GEMM, its state scan and its row kernels then overlap the other piece's GEMMs.
+  int n_pieces = 1;
+  if (!batch_mode && T >= 2048) {
+    n_pieces = 2;
+    if (const char *e = getenv("FR_B200_SEQ_PIECES")) n_pieces = std::max(1, std::min(atoi(e), 4));
+    n_pieces = std::min(n_pieces, T / 512);
   }
-  const size_t o_e = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0), o_sin = take(n_chunks > 1 ? (size_t)H * n_chunks * 4096 * 4 : 0);
+  const int piece_rows = ((T + n_pieces - 1) / n_pieces + 255) / 256 * 256;   // whole 256-row GEMM tiles per piece
+  n_pieces = (T + piece_rows - 1) / piece_rows;
+  // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
+  const int Tp = std::min(T, piece_rows);
+  int max_chunks = 1;
+  if (!batch_mode && m->v5) max_chunks = std::max(1, std::min(Tp / 32, (8 * device_sm_count() + H - 1) / H));
+  const size_t scan_bytes = max_chunks > 1 ? (size_t)H * max_chunks * 4096 * 4 : 0;
+  const size_t o_e = take(scan_bytes * n_pieces), o_sin = take(scan_bytes * n_pieces);
   if (m->seq_bytes < off) {
     CU(cudaStreamSynchronize(st));
     if (m->d_seq) cudaFree(m->d_seq);
@@ -990,25 +1004,26 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   }
   uint8_t *B = m->d_seq;
   int32_t *d_ids = (int32_t *)(B + o_ids);
-  float *x = (float *)(B + o_x), *r = (float *)(B + o_r), *k = (float *)(B + o_k), *v = (float *)(B + o_v), *y = (float *)(B + o_y);
-  __half *op[4] = {(__half *)(B + o_op0), (__half *)(B + o_op1), (__half *)(B + o_op2), (__half *)(B + o_op3)};
-  __half *g = (__half *)(B + o_g), *yn = (__half *)(B + o_yn), *kk = (__half *)(B + o_kk), *rr = g;   // rr reuses g
-  __half *lo0 = (__half *)(B + o_lo0), *lo1 = (__half *)(B + o_lo1);
+  float *x = (float *)(B + o_x), *r_all = (float *)(B + o_r), *k_all = (float *)(B + o_k), *v_all = (float *)(B + o_v), *y_all = (float *)(B + o_y);
+  __half *op_all[4] = {(__half *)(B + o_op0), (__half *)(B + o_op1), (__half *)(B + o_op2), (__half *)(B + o_op3)};
+  __half *g_all = (__half *)(B + o_g), *yn_all = (__half *)(B + o_yn), *kk_all = (__half *)(B + o_kk);   // (the ffn receptance reuses g)
+  __half *lo0_all = (__half *)(B + o_lo0), *lo1_all = (__half *)(B + o_lo1);
   // batch mode keeps every GEMM input as a hi + lo pair: the steps are bound by weight bytes, not flops, and the
   // per-stream error must not depend on how many streams share the step
-  __half *lo2 = batch_mode ? (__half *)(B + o_lo2) : nullptr, *lo3 = batch_mode ? (__half *)(B + o_lo3) : nullptr;
-  __half *yn_lo = batch_mode ? (__half *)(B + o_ynlo) : nullptr, *kk_lo = batch_mode ? (__half *)(B + o_kklo) : nullptr;
-  __half *g_lo = batch_mode ? (__half *)(B + o_glo) : nullptr, *rr_lo = g_lo;   // like rr reuses g
+  __half *lo2_all = batch_mode ? (__half *)(B + o_lo2) : nullptr, *lo3_all = batch_mode ? (__half *)(B + o_lo3) : nullptr;
+  __half *ynlo_all = batch_mode ? (__half *)(B + o_ynlo) : nullptr, *kklo_all = batch_mode ? (__half *)(B + o_kklo) : nullptr;
+  __half *glo_all = batch_mode ? (__half *)(B + o_glo) : nullptr;
+  cudaStream_t st_main = st;
   if (ids != d_ids) CU(cudaMemcpyAsync(d_ids, ids, (size_t)T * 4, cudaMemcpyDefault, st));
   CU(launch_gather_emb(m->d_emb, m->emb_dtype == FR_B200_T_F32, d_ids, T, C, x, st));
   auto vp = [&](const std::string &n) -> const float * { return m->d_vecs + m->vecs[n].off; };
   const bool quant = m->fmt != FMT_FP16;
-  auto mk = [&](const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
+  auto mk = [&](int rows, const __half *A, const std::string &w, int N, int K, int epi, void *out, const void *aux0, const void *aux1,
                 float scale, const __half *A2 = nullptr) -> GemmArgs {
     GemmArgs ga;
     memset(&ga, 0, sizeof(ga));
     const MatrixSlot &ms = m->mats[w];
-    ga.A = A; ga.A2 = A2; ga.M = T;
+    ga.A = A; ga.A2 = A2; ga.M = rows;
     if (quant) {
       ga.Wq = m->d_qcopy + ms.q_off; ga.wfmt = m->fmt;
       if (m->fmt == FMT_INT4) ga.wq_scale = m->d_qscale + ms.qs_off;
@@ -1020,19 +1035,54 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     ga.scale = scale; ga.status = m->out_status();
     return ga;
   };
-  const int mt = T > 128 ? 2 : 1;   // 256-row tiles once the rows fill them
+  const int mt = Tp > 128 ? 2 : 1;   // 256-row tiles once the rows fill them
   // few rows: every GEMM of a launch gets its own run of split-K slabs
   auto give_raw = [&](GemmArgs *grp, int n) {
     if (T > GEMM_SMALL_M) return;
     float *p = (float *)(B + o_raw);
     for (int i = 0; i < n; ++i) { grp[i].raw = p; p += (size_t)GEMM_SPLIT_MAX * T * grp[i].N; }
   };
-  const int par = (int)m->par[batch_mode ? 0 : slot];
+  const int par0 = (int)m->par[batch_mode ? 0 : slot];
   const int nvec = m->v5 ? (m->gate ? 4 : 3) : 3;
   uint8_t *st0 = m->d_state + (batch_mode ? 0 : (size_t)slot * m->state_stride);
-  for (int l = 0; l < m->L; ++l) {
+  // streams and events of the pieces (one piece: everything on the caller's stream)
+  if (n_pieces > 1) {
+    for (int pc = 0; pc < n_pieces; ++pc)
+      if (!m->seq_streams[pc]) CU(cudaStreamCreateWithFlags(&m->seq_streams[pc], cudaStreamNonBlocking));
+    while ((int)m->seq_events.size() < n_pieces * (m->L + 1)) {
+      cudaEvent_t ev;
+      CU(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+      m->seq_events.push_back(ev);
+    }
+    cudaEvent_t start = m->seq_events[n_pieces * m->L];          // everything before the layers (ids, embedding rows)
+    CU(cudaEventRecord(start, st));
+    for (int pc = 0; pc < n_pieces; ++pc) CU(cudaStreamWaitEvent(m->seq_streams[pc], start, 0));
+  }
+  float *const x_all = x;
+  for (int l = 0; l < m->L; ++l)
+  for (int pc = 0; pc < n_pieces; ++pc) {
     const std::string b = "blocks." + std::to_string(l) + ".", a = b + "att.", f = b + "ffn.";
     uint8_t *stb = st0 + (size_t)l * m->layer_stride;
+    // this piece's rows of every activation buffer, its stream, its copy of the shift states (they alternate piece by
+    // piece exactly as they alternate token by token) and its scan scratch
+    const int t0 = pc * piece_rows, T = std::min(R, t0 + piece_rows) - t0;
+    const size_t rc = (size_t)t0 * C, rf = (size_t)t0 * F;
+    cudaStream_t st = n_pieces > 1 ? m->seq_streams[pc] : st_main;
+    const int par = par0 ^ (pc & 1);
+    float *x = x_all + rc, *r = r_all + rc, *k = k_all + rc, *v = v_all + rc, *y = y_all + rc;
+    __half *op[4] = {op_all[0] + rc, op_all[1] + rc, op_all[2] + rc, op_all[3] + rc};
+    __half *g = g_all + rc, *yn = yn_all + rc, *kk = kk_all + rf, *rr = g;
+    __half *lo0 = lo0_all + rc, *lo1 = lo1_all + rc;
+    __half *lo2 = lo2_all ? lo2_all + rc : nullptr, *lo3 = lo3_all ? lo3_all + rc : nullptr;
+    __half *yn_lo = ynlo_all ? ynlo_all + rc : nullptr, *kk_lo = kklo_all ? kklo_all + rf : nullptr;
+    __half *g_lo = glo_all ? glo_all + rc : nullptr, *rr_lo = g_lo;
+    int n_chunks = 1, chunk_len = T;
+    if (!batch_mode && m->v5) {
+      n_chunks = std::max(1, std::min(T / 32, (8 * device_sm_count() + H - 1) / H));
+      chunk_len = (T + n_chunks - 1) / n_chunks;
+      n_chunks = (T + chunk_len - 1) / chunk_len;
+    }
+    if (n_pieces > 1 && pc > 0) CU(cudaStreamWaitEvent(st, m->seq_events[(pc - 1) * m->L + l], 0));   // the state after layer l of the rows before
     // ---- time mix ----
     SeqLnArgs la;
     memset(&la, 0, sizeof(la));
@@ -1049,11 +1099,11 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     CU(launch_ln_mix_seq(la, st));
     {
       // the attention projections in one launch; the two with a second pass over K first
-      GemmArgs grp[4] = {mk(op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0),
-                         mk(op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f, lo1),
-                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2),
-                         mk(op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2)};
-      if (m->gate) { grp[3] = mk(op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f, lo3); grp[3].out_lo = g_lo; }
+      GemmArgs grp[4] = {mk(T, op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0),
+                         mk(T, op[1], a + "value.weight", C, C, GEMM_EPI_F32, v, nullptr, nullptr, 1.f, lo1),
+                         mk(T, op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2),
+                         mk(T, op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2)};
+      if (m->gate) { grp[3] = mk(T, op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f, lo3); grp[3].out_lo = g_lo; }
       give_raw(grp, m->gate ? 4 : 3);
       CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st));
     }
@@ -1063,7 +1113,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       wa.r = r; wa.k = k; wa.v = v; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
       wa.state = reinterpret_cast<float *>(stb + off_mid(C, af)); wa.y = y; wa.T = T; wa.C = C;
       wa.per_head = m->cfg.version == FR_B200_V5_0;
-      wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e); wa.s_in = (float *)(B + o_sin);
+      wa.n_chunks = n_chunks; wa.chunk_len = chunk_len; wa.e_out = (float *)(B + o_e + scan_bytes * pc); wa.s_in = (float *)(B + o_sin + scan_bytes * pc);
       wa.batch_mode = batch_mode; wa.state_stride = m->state_stride / 4;
       CU(launch_wkv5_seq(wa, H, st));
       CU(launch_gn_gate_seq(y, vp(a + "ln_x.weight"), vp(a + "ln_x.bias"), m->gate ? g : nullptr, m->gate ? g_lo : nullptr, T, H, yn, yn_lo, st));
@@ -1075,7 +1125,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       CU(launch_wkv4_rows(wa, st));
     }
     {
-      GemmArgs go = mk(yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
+      GemmArgs go = mk(T, yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
       give_raw(&go, 1);
       // prompts: few tiles, 128-row tiles fill the SMs better (measured); streams: one pass over the weights for all rows
       CU(launch_gemm_group(&go, 1, batch_mode ? mt : 1, st));
@@ -1092,26 +1142,31 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     CU(launch_ln_mix_seq(la, st));
     const bool halve = af && (l + 1) % 6 == 0;   // x / 2 every 6 layers under fp16 activations (model_forward_seq.cpp:165-167)
     {
-      GemmArgs grp[2] = {mk(op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f, batch_mode ? lo0 : nullptr),
-                         mk(op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f, batch_mode ? lo1 : nullptr)};
+      GemmArgs grp[2] = {mk(T, op[0], f + "key.weight", F, C, GEMM_EPI_RELU2_F16, kk, nullptr, nullptr, 1.f, batch_mode ? lo0 : nullptr),
+                         mk(T, op[1], f + "receptance.weight", C, C, GEMM_EPI_SIGMOID_F16, rr, nullptr, nullptr, 1.f, batch_mode ? lo1 : nullptr)};
       grp[0].out_lo = kk_lo; grp[1].out_lo = rr_lo;
       give_raw(grp, 2);
       CU(launch_gemm_group(grp, 2, mt, st));
-      GemmArgs gv = mk(kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f, kk_lo);
+      GemmArgs gv = mk(T, kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f, kk_lo);
       gv.aux1_lo = rr_lo;
       give_raw(&gv, 1);
       CU(launch_gemm_group(&gv, 1, batch_mode ? mt : 1, st));
     }
     m->launches += m->v5 ? 9 : 7;
+    if (n_pieces > 1) CU(cudaEventRecord(m->seq_events[pc * m->L + l], st));
+  }
+  if (n_pieces > 1) {
+    // back on the caller's stream once every piece has finished its last layer
+    for (int pc = 0; pc < n_pieces; ++pc) CU(cudaStreamWaitEvent(st_main, m->seq_events[pc * m->L + m->L - 1], 0));
   }
   if (batch_mode) {
     // every row: ln_out, then the head as one more GEMM -> fp32 logits [R, Vpad]
     SeqLnArgs la;
     memset(&la, 0, sizeof(la));
-    la.x = x; la.ln_w = vp("ln_out.weight"); la.ln_b = vp("ln_out.bias"); la.op[0] = op[0]; la.op_lo[0] = lo0;
+    la.x = x; la.ln_w = vp("ln_out.weight"); la.ln_b = vp("ln_out.bias"); la.op[0] = op_all[0]; la.op_lo[0] = lo0_all;
     la.T = T; la.C = C; la.nvec = 0; la.act_fp16 = af; la.batch_mode = 1;
     CU(launch_ln_mix_seq(la, st));
-    GemmArgs gh = mk(op[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f, lo0);
+    GemmArgs gh = mk(T, op_all[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f, lo0_all);
     gh.ldo = m->Vpad;
     // (no split-K scratch for the head: it has a thousand column tiles of its own)
     CU(launch_gemm_group(&gh, 1, mt, st));
@@ -1138,7 +1193,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   if (!grid) return fail(FR_B200_E_UNSUPPORTED, "kernel does not fit");
   CU(launch_decode(p, 0, grid, smem, st));
   m->launches += 3;
-  m->par[slot] ^= 1u;
+  if (n_pieces & 1) m->par[slot] ^= 1u;   // every piece flipped the shift-state copies once
   return 0;
 }
 

@@ -139,10 +139,12 @@ def test_seq_mode_two_prompts_in_a_row(pkg, orc, synth, monkeypatch):
     m.close()
 
 
-def test_quantised_and_v4_models_keep_the_token_loop(pkg, orc, synth):
+def test_quantised_and_v4_models_match_the_oracle_on_prompts(pkg, orc, synth):
     """The reference has no seq kernel for RWKV-4 (model_forward_seq.cpp:111-112 throws) and none for quantised
-    weights; Run(vector) falls back to the token loop there and must still match the oracle."""
-    for name, strat, fdt, fmt in (("tiny4", "cuda fp16", "fp16", "fp16"), ("tiny52", "cuda int8", "fp32", "int8")):
+    weights.  Here short RWKV-4 fp16 prompts take the token loop, quantised models the GEMM path over their packed
+    row copies; either way Run(vector) must match the oracle's token loop."""
+    for name, strat, fdt, fmt in (("tiny4", "cuda fp16", "fp16", "fp16"), ("tiny52", "cuda int8", "fp32", "int8"),
+                                  ("tiny4b", "cuda int4", "fp32", "int4")):
         shape = synth.SHAPES[name]
         tensors = synth.to_file_dtypes(shape, synth.generate(shape, seed=11, ln_random=True), fdt)
         ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6 if fmt == "fp16" else 0,
@@ -151,3 +153,29 @@ def test_quantised_and_v4_models_keep_the_token_loop(pkg, orc, synth):
         m = pkg.Model(tensors, strat, shape=shape)
         _close(m.run(ids), ref.run_seq(ids), name)
         m.close()
+
+
+@pytest.mark.parametrize("name,strat,fdt,fmt,T,pieces", [("mid52", "cuda fp16", "fp16", "fp16", 2100, None),
+                                                         ("mid52", "cuda fp16", "fp16", "fp16", 2600, "3"),
+                                                         ("mid4", "cuda int8", "fp32", "int8", 2200, None),
+                                                         ("mid4", "cuda fp16", "fp16", "fp16", 2048, "4")])
+def test_long_prompts_in_pipelined_pieces(pkg, orc, synth, monkeypatch, name, strat, fdt, fmt, T, pieces):
+    """Prompts of 2048 tokens or more are cut into pieces of rows that run on streams of their own, one layer apart
+    (the token shift and the recurrent state cross the cut through the model state).  Logits, the recurrent state and
+    the token after the prompt must match the oracle's token loop, with the default two pieces and with three / four."""
+    if pieces:
+        monkeypatch.setenv("FR_B200_SEQ_PIECES", pieces)
+    shape = synth.SHAPES[name]
+    tensors = synth.to_file_dtypes(shape, synth.generate(shape, seed=11, ln_random=True), fdt)
+    ref = orc.OracleModel(shape, tensors, synth.param_names(shape), rescale_every=6 if fmt == "fp16" else 0,
+                          weight_format=fmt, state_fp16=fmt == "fp16")
+    ids = [int(t) for t in synth.token_ids(shape, T, seed=2)]
+    m = pkg.Model(tensors, strat, shape=shape)
+    _close(m.run(ids), ref.run_seq(ids), f"{name} {fmt} T={T}")
+    if str(shape.version).startswith("5"):
+        _state_close(m, ref, shape, f"{name} T={T}")
+    _close(m.run(7), ref.run(7), "token after the prompt")
+    # a second prompt on top of the first: the shift-state copies are where the next call expects them
+    ids2 = [int(t) for t in synth.token_ids(shape, 2048 + 300, seed=3)]
+    _close(m.run(ids2), ref.run_seq(ids2), "second long prompt")
+    m.close()
