@@ -141,7 +141,7 @@ struct GemmArgs {
 };
 constexpr int GEMM_GROUP_MAX = 4;
 constexpr int GEMM_SMALL_M = 1024;    // up to this many rows the GEMM puts the weights along the MMA rows (and splits K, given scratch)
-constexpr int GEMM_SPLIT_MAX = 8;
+constexpr int GEMM_SPLIT_MAX = 16;
 int device_sm_count();   // SMs of the current device
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);   // one GEMM; 256-row tiles when M > 128
 // n <= 4 GEMMs with equal M in one launch; mt = 128-row sub-tiles per CTA (1 or 2)

@@ -207,7 +207,9 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmArgs &g, int row, in
 // attention projections of a layer, or the two channel-mix projections that read the LayerNorm output.
 struct GemmGroup {
   int n;
-  int stages;                           // ring depth (2..4)
+  int stages;                           // ring depth (2..4); packed-weight GEMM: weight slots
+  int estages;                          // packed-weight GEMM: buffers (expanded weights + X; stage_bytes = the X part)
+  uint32_t wbox;                        // packed-weight GEMM: bytes per row of a weight slot (64 or 128)
   uint32_t stage_bytes;                 // bytes per ring slot: [A hi tiles][A lo tiles, if any problem has them][B tile]
   int split;                            // split-K factor (grid.z); > 1: CTAs write raw partial sums to GemmArgs::raw
   int dual;                             // 1: the slot has room for the low halves of A (128-row tiles);
@@ -519,19 +521,24 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
 // ------------------------------------------------------------------------------------------------
 // The few-row GEMM for quantised weights: the weight operand is read in its packed form (int8 codes [N, K], or int4
 // nibbles [N, K/2] with fp16 group scales [N, K/32]: the bytes a step has to stream) and expanded to the K-major fp16
-// tile the tensor core wants inside the kernel, by four warps that do nothing else.  Per K slice of 64 inputs:
-//   warp 0      TMA: the packed 128-row weight tile (8 KB int8 / 4 KB int4) + the X tile(s) into a ring slot
-//   warps 6..13 expanders (two threads per row): packed tile -> 128 x 64 fp16 in the 128-byte-swizzled layout of a TMA-loaded tile
+// tile the tensor core wants inside the kernel, by eight warps that do nothing else.  Per K slice of 64 inputs:
+//   warp 0      TMA: packed weights into a ring of slots of their own (128 rows x 32..128 bytes = 1, 2 or 4 slices
+//               per slot) and the X tile(s) into buffer kb % NE
+//   warps 6..13 expanders (two threads per row): packed slice -> 128 x 64 fp16 in the 128-byte-swizzled layout of a
+//               TMA-loaded tile, expanded buffer kb % NE
 //               (int8: the integer code, exact in fp16, the row scale is applied to the accumulator;
-//                int4: hi = fp16(q * scale) and lo = q * scale - hi, an exact pair), double-buffered
-//   warp 1      MMA: acc += W_hi X_hi (+ W_hi X_lo) (+ W_lo X_hi)
+//                int4: hi = fp16(q * scale) and lo = q * scale - hi, an exact pair)
+//   warp 1      MMA: acc += W_hi [X_hi | X_lo] (+ W_lo X_hi)
 //   warps 2..5  epilogue, as in gemm_wt_kernel
-// A ring slot is free again when the expanders have read its weight bytes and the MMAs its X tiles; an expanded
-// buffer when the MMAs that read it have retired.  Shared-memory writes of the expanders are made visible to the
-// tensor core's (asynchronous) reads with fence.proxy.async before the barrier arrive.
+// Buffer e (its X slot and its expanded weights) is free again when the MMAs that read it have retired: one commit
+// per slice.  A weight slot is free when the expanders have read its last slice.  Shared-memory writes of the
+// expanders are made visible to the tensor core's (asynchronous) reads with fence.proxy.async before the barrier
+// arrive.  The weights are constants, so their loads and their expansion do not wait for the kernels before this
+// one: under programmatic dependent launch the first slices are ready when X arrives.
+constexpr int WQ_MAX_E = 4;        // most buffers (expanded weights + X)
+constexpr int WQ_MAX_W = 8;        // deepest ring of packed weight slots
 constexpr int WQ_EXP_WARPS = 8;
 constexpr int WQ_THREADS = 192 + 32 * WQ_EXP_WARPS;
-constexpr int WQ_NE = 2;   // expanded buffers
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
@@ -545,30 +552,40 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
   return d;
 }
 
+// 72 registers: two CTAs share an SM whenever the launcher's shared-memory plan allows it
 template <int BN, int FMT>
-__global__ void __launch_bounds__(WQ_THREADS, 1)
+__global__ void __launch_bounds__(WQ_THREADS, 2)
 gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
   constexpr uint32_t X_BYTES = BN * GBK * 2;
-  constexpr uint32_t WQ_BYTES = FMT == FMT_INT8 ? GBM * GBK : GBM * GBK / 2;   // packed weight tile
-  constexpr uint32_t ROW_B = WQ_BYTES / GBM;                                   // packed bytes per row: 64 / 32
-  constexpr uint32_t E_BYTES = (FMT == FMT_INT4 ? 2u : 1u) * G_A_BYTES;        // expanded buffer: hi (+ lo)
+  constexpr uint32_t ROW_B = FMT == FMT_INT8 ? GBK : GBK / 2;                  // packed bytes per row and K slice: 64 / 32
+  constexpr uint32_t E_BYTES = (FMT == FMT_INT4 ? 2u : 1u) * G_A_BYTES;        // expanded weights: hi (+ lo)
+  // Up to 128 rows the hi and lo halves of X sit back to back in a buffer and are one B operand of 2 BN rows: one MMA
+  // gives W X_hi in accumulator columns [0, BN) and W X_lo in [BN, 2 BN), which the epilogue adds up.  An MMA with
+  // few columns costs about as much as a wide one (it reads the whole 128-row weight operand either way), so this
+  // takes a third (int4) or half (int8) of the MMAs off the issue thread.  At 256 rows the halves are passes of their own.
+  constexpr bool FUSE_LO = BN <= 128;
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  const int STAGES = grp.stages;
-  const uint32_t STAGE_BYTES = grp.stage_bytes;
-  const uint32_t X_OFF = 8192u, XLO_OFF = X_OFF + X_BYTES;   // the packed tile takes the first 8 KB of a slot
+  constexpr uint32_t IDESC2 = (1u << 4) | ((uint32_t)((2 * BN) >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = FUSE_LO ? 2 * BN : BN;
+  // weight slot: 128 rows x WB bytes = KSUB consecutive K slices of the tile; WB = 128 (swizzled like every 128-byte
+  // tile: whole lines for the TMA unit and for HBM) where shared memory allows, else 64 or 32 (plain rows)
+  const uint32_t WB = grp.wbox, WS_BYTES = GBM * WB;
+  const int KSUB = (int)(WB / ROW_B), KSH = KSUB == 4 ? 2 : KSUB == 2 ? 1 : 0;
+  const int NW = grp.stages, NE = grp.estages;
+  const uint32_t XS_BYTES = grp.stage_bytes;                                   // X part of a buffer: hi (+ lo)
   extern __shared__ uint8_t gsm_raw[];
   uint8_t *gsm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t *full = reinterpret_cast<uint64_t *>(gsm);
-  uint64_t *empty = full + WT_MAX_STAGES;
-  uint64_t *a_full = empty + WT_MAX_STAGES;
-  uint64_t *a_empty = a_full + WQ_NE;
-  uint64_t *acc_full = a_empty + WQ_NE;
+  uint64_t *wfull = reinterpret_cast<uint64_t *>(gsm);
+  uint64_t *wempty = wfull + WQ_MAX_W;
+  uint64_t *xfull = wempty + WQ_MAX_W;
+  uint64_t *a_full = xfull + WQ_MAX_E;
+  uint64_t *a_empty = a_full + WQ_MAX_E;
+  uint64_t *acc_full = a_empty + WQ_MAX_E;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  uint8_t *exp_base = gsm + 1024;                                   // WQ_NE expanded buffers, 1024-byte aligned
-  uint8_t *ring_base = exp_base + WQ_NE * E_BYTES;
-  const uint32_t tiles = smem_u32(ring_base), etiles = smem_u32(exp_base);
+  const uint32_t etiles = smem_u32(gsm + 1024);                                // NE expanded buffers, 1024-byte aligned
+  const uint32_t xtiles = etiles + (uint32_t)NE * E_BYTES;                     // NE X slots
+  const uint32_t wtiles = xtiles + (uint32_t)NE * XS_BYTES;                    // NW weight slots
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int pi = 0;
   while (pi + 1 < grp.n && (int)blockIdx.x >= grp.tile_start[pi + 1]) ++pi;
@@ -577,10 +594,12 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   const int num_k1 = g.K / GBK;
   const int kz0 = (int)((long long)blockIdx.z * num_k1 / grp.split), nkz = (int)((long long)(blockIdx.z + 1) * num_k1 / grp.split) - kz0;
   const bool x_lo = g.A2 != nullptr;
+  // this CTA's slices [kz0, kz0 + nkz) touch weight slots g0 .. g0 + ng - 1 of the matrix
+  const int g0 = kz0 >> KSH, ng = nkz > 0 ? ((kz0 + nkz - 1) >> KSH) - g0 + 1 : 0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], WQ_EXP_WARPS + 1); }   // expander warps + the MMA commit
-    for (int e = 0; e < WQ_NE; ++e) { mbar_init(&a_full[e], WQ_EXP_WARPS); mbar_init(&a_empty[e], 1); }
+    for (int s = 0; s < NW; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], WQ_EXP_WARPS); }
+    for (int e = 0; e < NE; ++e) { mbar_init(&xfull[e], 1); mbar_init(&a_full[e], WQ_EXP_WARPS); mbar_init(&a_empty[e], 1); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -594,35 +613,62 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
-  pdl_wait();   // operands and epilogue inputs come from the kernels before this one
+  // What the kernels before this one wrote (X, the epilogue's inputs and outputs) is touched only after pdl_wait():
+  // by the X loads and by the epilogue warps.
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < nkz; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
-        mbar_expect_tx(&full[s], WQ_BYTES + (x_lo ? 2u : 1u) * X_BYTES);
-        const uint32_t dst = tiles + (uint32_t)s * STAGE_BYTES;
-        const int kx = (kz0 + kb) * GBK;
-        tma_load_2d(dst, &maps.b[pi], (kz0 + kb) * (int)ROW_B, tile_n * GBM, &full[s]);
-        tma_load_2d(dst + X_OFF, &maps.a[pi], kx, m0, &full[s]);
-        if (x_lo) tma_load_2d(dst + XLO_OFF, &maps.a2[pi], kx, m0, &full[s]);
+      // one thread feeds both rings: whichever has a free slot gets its next tile
+      int kw = 0, kx = 0, idle = 0;
+      unsigned long long t0 = 0;
+      for (; kw < ng && kw < NW; ++kw) {
+        mbar_expect_tx(&wfull[kw], WS_BYTES);
+        tma_load_2d(wtiles + (uint32_t)kw * WS_BYTES, &maps.b[pi], (g0 + kw) * (int)WB, tile_n * GBM, &wfull[kw]);
+      }
+      pdl_wait();
+      while (kw < ng || kx < nkz) {
+        bool moved = false;
+        if (kw < ng && mbar_try(&wempty[kw % NW], ((kw / NW) & 1) ^ 1)) {
+          const int s = kw % NW;
+          mbar_expect_tx(&wfull[s], WS_BYTES);
+          tma_load_2d(wtiles + (uint32_t)s * WS_BYTES, &maps.b[pi], (g0 + kw) * (int)WB, tile_n * GBM, &wfull[s]);
+          ++kw;
+          moved = true;
+        }
+        if (kx < nkz && mbar_try(&a_empty[kx % NE], ((kx / NE) & 1) ^ 1)) {
+          const int e = kx % NE;
+          const uint32_t dst = xtiles + (uint32_t)e * XS_BYTES;
+          const int kc = (kz0 + kx) * GBK;
+          mbar_expect_tx(&xfull[e], (x_lo ? 2u : 1u) * X_BYTES);
+          tma_load_2d(dst, &maps.a[pi], kc, m0, &xfull[e]);
+          if (x_lo) tma_load_2d(dst + X_BYTES, &maps.a2[pi], kc, m0, &xfull[e]);
+          ++kx;
+          moved = true;
+        }
+        if (moved) { idle = 0; continue; }
+        if (idle == 0) t0 = globaltimer_ns();
+        if ((++idle & 63) == 0) {
+          if (*abort_flag) break;
+          if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(g.status, 0, ST_GEMM_TIMEOUT); break; }
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       for (int kb = 0; kb < nkz; ++kb) {
-        const int s = kb % STAGES, e = kb % WQ_NE;
-        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
-        if (!mbar_wait(&a_full[e], (kb / WQ_NE) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        const int e = kb % NE;
+        const uint32_t par = (uint32_t)(kb / NE) & 1u;
+        if (!mbar_wait(&xfull[e], par, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+        if (!mbar_wait(&a_full[e], par, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
         tc_fence_after();
-        const uint32_t base = tiles + (uint32_t)s * STAGE_BYTES, eb = etiles + (uint32_t)e * E_BYTES;
-        const uint64_t wd = umma_desc_k128(eb), xd = umma_desc_k128(base + X_OFF);
+        const uint32_t xb = xtiles + (uint32_t)e * XS_BYTES, eb = etiles + (uint32_t)e * E_BYTES;
+        const uint64_t wd = umma_desc_k128(eb), xd = umma_desc_k128(xb);
+        const bool wide = FUSE_LO && x_lo;
 #pragma unroll
         for (int k4 = 0; k4 < GBK / 16; ++k4)
-          umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, (kb | k4) != 0);
-        if (x_lo) {
-          const uint64_t xl = umma_desc_k128(base + XLO_OFF);
+          umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), wide ? IDESC2 : IDESC, (kb | k4) != 0);
+        if (x_lo && !wide) {
+          const uint64_t xl = umma_desc_k128(xb + X_BYTES);
 #pragma unroll
           for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xl + (uint64_t)(k4 * 2), IDESC, 1u);
         }
@@ -631,38 +677,65 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
 #pragma unroll
           for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wl + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, 1u);
         }
-        umma_commit(&empty[s]);
-        umma_commit(&a_empty[e]);
+        umma_commit(&a_empty[e]);   // X slot e and expanded buffer e are free once these MMAs have retired
       }
       umma_commit(acc_full);
     }
   } else if (warp >= 6) {
     // expanders: two threads per row of the tile, each expands half of the row's 64 inputs
     const int et = (int)threadIdx.x - 192;
-    const int row = et >> 1, half = et & 1;
+    const int row = et >> 1, part = et & 1;
     const int ch = tile_n * GBM + row;                      // output channel of this row
     const uint32_t swz = (uint32_t)(row & 7);
+    const uint32_t wswz = WB == 128u ? swz : 0u;
     const uint32_t erow = (uint32_t)row * 128u;             // byte offset of the row inside an expanded tile
-    const __half *gs = nullptr;                             // int4: this row's group scales
+    // int4: this row's group scales, two per K slice.  They come straight from global memory, 16 bytes (four slices)
+    // at a time and four slices ahead of their use, so that the expansion never waits for them; rows whose scales
+    // are not 16-byte aligned (K not a multiple of 256) take them slice by slice, one ahead.
+    const __half *gs = nullptr;
     if (FMT == FMT_INT4 && ch < g.N) gs = g.wq_scale + (size_t)ch * (g.K / 32);
+    const bool quads = FMT == FMT_INT4 && ((g.K / 32) & 7) == 0;
+    const int nquads = g.K / 256;
+    uint4 scq = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u), scq_next = scq;
     uint32_t sc_next = 0x3c003c00u;
-    if (FMT == FMT_INT4 && gs && nkz > 0) sc_next = *reinterpret_cast<const uint32_t *>(gs + (size_t)kz0 * 2);
-    bool live = true;
-    for (int kb = 0; kb < nkz && live; ++kb) {
-      const int s = kb % STAGES, e = kb % WQ_NE;
-      const uint32_t sc = sc_next;                          // scales of the two 32-input groups of this slice
-      if (FMT == FMT_INT4 && gs && kb + 1 < nkz) sc_next = *reinterpret_cast<const uint32_t *>(gs + (size_t)(kz0 + kb + 1) * 2);
-      if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) { live = false; break; }
-      if (!mbar_wait(&a_empty[e], ((kb / WQ_NE) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) { live = false; break; }
-      const uint32_t src = tiles + (uint32_t)s * STAGE_BYTES + (uint32_t)row * ROW_B;
+    if (FMT == FMT_INT4 && gs && nkz > 0) {
+      if (quads) {
+        scq = *reinterpret_cast<const uint4 *>(gs + (size_t)(kz0 >> 2) * 8);
+        if ((kz0 >> 2) + 1 < nquads) scq_next = *reinterpret_cast<const uint4 *>(gs + (size_t)((kz0 >> 2) + 1) * 8);
+      } else {
+        sc_next = *reinterpret_cast<const uint32_t *>(gs + (size_t)kz0 * 2);
+      }
+    }
+    for (int kb = 0; kb < nkz; ++kb) {
+      const int ks = kz0 + kb;
+      const int wj = (ks >> KSH) - g0, sub = ks & (KSUB - 1);
+      const int s = wj % NW, e = kb % NE;
+      uint32_t sc = sc_next;                                // scales of the two 32-input groups of this slice
+      if (FMT == FMT_INT4) {
+        if (quads) {
+          if (kb > 0 && (ks & 3) == 0) {
+            scq = scq_next;
+            if (gs && (ks >> 2) + 1 < nquads) scq_next = *reinterpret_cast<const uint4 *>(gs + (size_t)((ks >> 2) + 1) * 8);
+          }
+          const int qi = ks & 3;
+          sc = qi == 0 ? scq.x : qi == 1 ? scq.y : qi == 2 ? scq.z : scq.w;
+        } else if (gs && kb + 1 < nkz) {
+          sc_next = *reinterpret_cast<const uint32_t *>(gs + (size_t)(ks + 1) * 2);
+        }
+      }
+      if (!mbar_wait(&wfull[s], (uint32_t)(wj / NW) & 1u, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+      if (!mbar_wait(&a_empty[e], ((uint32_t)(kb / NE) & 1u) ^ 1u, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+      // 16-byte chunk c of the row's WB bytes is at (c ^ wswz) << 4
+      const uint32_t src = wtiles + (uint32_t)s * WS_BYTES + (uint32_t)row * WB;
+      const uint32_t c0 = (uint32_t)sub * (ROW_B / 16u);
       const uint32_t dst = etiles + (uint32_t)e * E_BYTES + erow;
       if (FMT == FMT_INT8) {
         // two 16-byte pieces of 16 codes per thread; neighbouring rows take theirs in opposite order, which spreads a
         // quarter warp's stores over all eight 16-byte columns of the swizzled rows
 #pragma unroll
         for (int pp = 0; pp < 2; ++pp) {
-          const uint32_t piece = (uint32_t)half * 2u + ((uint32_t)(pp + row) & 1u);
-          const uint4 w = lds128(src + piece * 16u);
+          const uint32_t piece = (uint32_t)part * 2u + ((uint32_t)(pp + row) & 1u);
+          const uint4 w = lds128(src + (((c0 + piece) ^ wswz) << 4));
           const uint32_t M = 0x64646464u, OFF = 0x64806480u;    // 1024 + (code + 128) - 1152 = code
           const uint32_t wx = w.x ^ 0x80808080u, wy = w.y ^ 0x80808080u, wz = w.z ^ 0x80808080u, ww = w.w ^ 0x80808080u;
           const uint4 o0 = make_uint4(hsub2_u32(prmt(wx, M, 0x4140), OFF), hsub2_u32(prmt(wx, M, 0x4342), OFF),
@@ -674,37 +747,38 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
         }
       } else {
         // one 16-byte piece of 32 nibbles per thread = one of the two scale groups of the slice
-        {
-          const uint32_t piece = (uint32_t)half;
-          const uint4 w = lds128(src + piece * 16u);
-          const uint32_t s16 = piece ? (sc >> 16) : (sc & 0xffffu);
-          const uint32_t s2 = s16 | (s16 << 16);
-          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        const uint4 w = lds128(src + (((c0 + (uint32_t)part) ^ wswz) << 4));
+        const uint32_t s16 = part ? (sc >> 16) : (sc & 0xffffu);
+        const uint32_t s2 = s16 | (s16 << 16);
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-          for (int wi = 0; wi < 4; ++wi) {
-            // 8 nibbles = inputs 8 wi .. 8 wi + 7 of the group -> one 16-byte chunk of hi and one of lo
-            uint32_t hi[4], lo[4];
+        for (int wi = 0; wi < 4; ++wi) {
+          // 8 nibbles = 8 consecutive inputs -> one 16-byte chunk of hi and one of lo
+          uint32_t hi[4], lo[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              // byte j -> {1024 + low nibble, 64 + high nibble} - {1032, 72} = {q_even, q_odd}
-              const uint32_t x = prmt(words[wi], 0u, 0x4040u + (uint32_t)j * 0x0101u);   // bytes [b_j, 0, b_j, 0]
-              const uint32_t qv = hsub2_u32(lop3_and_or(x, 0x00f0000fu, 0x54006400u), 0x54806408u);
-              hi[j] = hmul2_u32(qv, s2);
-              lo[j] = hfma2_u32(qv, s2, hi[j] ^ 0x80008000u);
-            }
-            const uint32_t chunk = (piece * 4u + (uint32_t)wi) ^ swz;
-            sts128(dst + (chunk << 4), make_uint4(hi[0], hi[1], hi[2], hi[3]));
-            sts128(dst + G_A_BYTES + (chunk << 4), make_uint4(lo[0], lo[1], lo[2], lo[3]));
+          for (int j = 0; j < 4; ++j) {
+            // byte j -> {1024 + low nibble, 64 + high nibble} - {1032, 72} = {q_even, q_odd}
+            const uint32_t x = prmt(words[wi], 0u, 0x4040u + (uint32_t)j * 0x0101u);   // bytes [b_j, 0, b_j, 0]
+            const uint32_t qv = hsub2_u32(lop3_and_or(x, 0x00f0000fu, 0x54006400u), 0x54806408u);
+            hi[j] = hmul2_u32(qv, s2);
+            lo[j] = hfma2_u32(qv, s2, hi[j] ^ 0x80008000u);
           }
+          const uint32_t chunk = ((uint32_t)part * 4u + (uint32_t)wi) ^ swz;
+          sts128(dst + (chunk << 4), make_uint4(hi[0], hi[1], hi[2], hi[3]));
+          sts128(dst + G_A_BYTES + (chunk << 4), make_uint4(lo[0], lo[1], lo[2], lo[3]));
         }
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&a_full[e]); mbar_arrive(&empty[s]); }
+      if (lane == 0) {
+        mbar_arrive(&a_full[e]);
+        if (sub == KSUB - 1 || kb == nkz - 1) mbar_arrive(&wempty[s]);   // last slice of the slot this CTA uses
+      }
     }
   } else {
     const int quad = warp & 3;
     const int ch = tile_n * GBM + quad * 32 + lane;
+    pdl_wait();
     const bool ok = mbar_wait(acc_full, 0, abort_flag, g.status, ST_GEMM_TIMEOUT);
     tc_fence_after();
     if (ok) {
@@ -714,6 +788,12 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
         uint32_t acc[32];
         __syncwarp();
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
+        if (FUSE_LO && x_lo) {
+          uint32_t part[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(BN + c0), part);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __uint_as_float(part[i]));
+        }
         if (ch < g.N) {
           if (grp.split > 1) {
             float *dst = g.raw + ((size_t)blockIdx.z * g.M + m0 + c0) * g.N + ch;
@@ -816,7 +896,8 @@ bool make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows)
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// [rows, row_bytes] bytes row-major -> tensor map with a (box_bytes x 128 rows) box, no swizzle, zero fill outside
+// [rows, row_bytes] bytes row-major -> tensor map with a (box_bytes x 128 rows) box, zero fill outside; 128-byte boxes
+// are swizzled, narrower ones are plain rows
 bool make_map_bytes(CUtensorMap *map, const void *base, int rows, int row_bytes, int box_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
@@ -825,8 +906,8 @@ bool make_map_bytes(CUtensorMap *map, const void *base, int rows, int row_bytes,
   const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)GBM};
   const cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            CU_TENSOR_MAP_INTERLEAVE_NONE, box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -1403,6 +1484,23 @@ cudaError_t launch_gemm_wq_t(const GemmMaps &maps, const GemmGroup &grp, dim3 gr
   return cudaGetLastError();
 }
 
+// shared-memory plan of the packed-weight GEMM inside `avail` bytes: ne buffers (expanded weights + X slot, released
+// together) and nw weight slots of `wbox`-byte rows; the weight ring grows first
+struct WqPlan { int ne, nw; uint32_t wbox; bool ok; };
+WqPlan wq_plan(long long avail, long long buf_bytes, uint32_t wbox, int want_ne, int want_nw) {
+  WqPlan p{2, 2, wbox, false};
+  const long long ws = (long long)GBM * wbox;
+  if (avail - 2 * buf_bytes - 2 * ws < 0) return p;
+  p.ok = true;
+  for (bool grown = true; grown;) {
+    grown = false;
+    const long long left = avail - p.ne * buf_bytes - p.nw * ws;
+    if (p.nw < want_nw && left >= ws) { ++p.nw; grown = true; continue; }
+    if (p.ne < want_ne && left >= buf_bytes) { ++p.ne; grown = true; }
+  }
+  return p;
+}
+
 // quantised weights in packed form (GemmArgs::Wq): any number of rows, walked in tiles of up to 256 along grid.y
 cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
   const int M = probs[0].M, fmt = probs[0].wfmt;
@@ -1420,11 +1518,6 @@ cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
     if (fmt == FMT_INT4 && !g.wq_scale) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.Wq) & 15) || (reinterpret_cast<uintptr_t>(g.A2) & 15))
       return cudaErrorInvalidValue;
-    const int row_bytes = fmt == FMT_INT8 ? g.K : g.K / 2;
-    if (!make_map(&maps.a[i], g.A, g.M, g.K, bn) || !make_map_bytes(&maps.b[i], g.Wq, g.N, row_bytes, fmt == FMT_INT8 ? GBK : GBK / 2))
-      return cudaErrorNotSupported;
-    if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, bn)) return cudaErrorNotSupported;
-    maps.b2[i] = maps.b[i];
     grp.p[i] = g;
     grp.tile_start[i] = tiles;
     tiles += (g.N + GBM - 1) / GBM;
@@ -1432,31 +1525,49 @@ cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
     raw_ok = raw_ok && g.raw != nullptr && (g.N & 3) == 0 && (g.ldo & 3) == 0;
     if (g.A2) grp.dual |= 1;
   }
-  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; maps.b2[i] = maps.b2[0]; }
   grp.tile_start[n] = tiles;
   const int m_tiles = (M + bn - 1) / bn;
   grp.split = 1;
-  grp.stage_bytes = 8192u + ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
-  const uint32_t ebytes = WQ_NE * (fmt == FMT_INT4 ? 2u : 1u) * G_A_BYTES;
-  // two CTAs per SM where a ring of >= 2 slots fits beside the expanded buffers in half an SM's shared memory (few rows:
-  // the step is a chain of short GEMMs, and a second CTA hides the hand-overs between the kernel's roles), else one CTA
-  // with as deep a ring as fits
-  int stages = (int)(((110u << 10) - ebytes) / grp.stage_bytes);
-  const bool two_per_sm = stages >= 2;
-  if (!two_per_sm) stages = (int)(((200u << 10) - ebytes) / grp.stage_bytes);
-  grp.stages = std::max(2, std::min(stages, WT_MAX_STAGES));
-  const size_t smem = 1024 + ebytes + (size_t)grp.stages * grp.stage_bytes + 1024;
-  const int sms = device_sm_count();
-  const int slots = two_per_sm ? 2 * sms : sms;
+  grp.stage_bytes = ((grp.dual & 1) ? 2u : 1u) * (uint32_t)bn * GBK * 2;
+  const long long buf_bytes = (long long)(fmt == FMT_INT4 ? 2u : 1u) * G_A_BYTES + grp.stage_bytes;
+  const uint32_t row_b = fmt == FMT_INT8 ? GBK : GBK / 2;
+  // Two CTAs per SM where two or three buffers and a weight ring fit in half an SM's shared memory (up to 64 rows) --
+  // the step is a chain of short GEMMs, and a second CTA (of this kernel or, launched early, of the next) hides the
+  // hand-overs between the kernel's roles: a quarter of the step time at 32 rows; else one CTA with everything as
+  // deep as fits.  Weight slots are as wide as the plan allows.
+  WqPlan pl{};
+  bool two_per_sm = false;
+  for (uint32_t wb = 128; wb >= row_b && !two_per_sm; wb >>= 1) {
+    pl = wq_plan(110ll << 10, buf_bytes, wb, 3, wb == 128 ? 3 : wb == 64 ? 4 : 8);
+    two_per_sm = pl.ok;
+  }
+  if (!two_per_sm) pl = wq_plan(225ll << 10, buf_bytes, 128, WQ_MAX_E, 4);
+  if (!pl.ok) return cudaErrorInvalidValue;
+  for (int i = 0; i < n; ++i) {
+    const GemmArgs &g = probs[i];
+    const int row_bytes = fmt == FMT_INT8 ? g.K : g.K / 2;
+    if (!make_map(&maps.a[i], g.A, g.M, g.K, bn) || !make_map_bytes(&maps.b[i], g.Wq, g.N, row_bytes, (int)pl.wbox))
+      return cudaErrorNotSupported;
+    if (!make_map(&maps.a2[i], g.A2 ? g.A2 : g.A, g.M, g.K, bn)) return cudaErrorNotSupported;
+    maps.b2[i] = maps.b[i];
+  }
+  for (int i = n; i < GEMM_GROUP_MAX; ++i) { maps.a[i] = maps.a[0]; maps.a2[i] = maps.a2[0]; maps.b[i] = maps.b[0]; maps.b2[i] = maps.b2[0]; }
+  const int slots = (two_per_sm ? 2 : 1) * device_sm_count();
   if (raw_ok) {
-    const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 4));
+    // split-K: the fewest waves of CTAs, each at least two K slices long; a slice costs 1, a wave's start and end 2,
+    // a slab in the finishing pass a quarter
+    const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 2));
     float best = 0.f;
     for (int sp = 1; sp <= max_split; ++sp) {
       const int waves = (ctas * sp + slots - 1) / slots;
-      const float cost = (float)waves * (float)((min_k1 + sp - 1) / sp + 2) + 0.5f * (float)sp;
+      const float cost = (float)waves * (float)((min_k1 + sp - 1) / sp + 2) + 0.25f * (float)sp;
       if (sp == 1 || cost < best) { best = cost; grp.split = sp; }
     }
   }
+  grp.stages = pl.nw;
+  grp.estages = pl.ne;
+  grp.wbox = pl.wbox;
+  const size_t smem = 1024 + (size_t)pl.ne * buf_bytes + (size_t)pl.nw * GBM * pl.wbox + 1024;
   dim3 grid(tiles, m_tiles, grp.split);
   cudaError_t e = cudaErrorInvalidValue;
 #define FRB_WQ(BNV) (fmt == FMT_INT8 ? launch_gemm_wq_t<BNV, FMT_INT8>(maps, grp, grid, smem, st) : launch_gemm_wq_t<BNV, FMT_INT4>(maps, grp, grid, smem, st))
