@@ -406,7 +406,11 @@ __global__ void __launch_bounds__(G_THREADS, 2)
 gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmGroup grp) {
   constexpr uint32_t X_BYTES = BN * GBK * 2;
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  // up to 128 rows the hi and lo tiles of X, back to back in the slot, are one B operand of 2 BN rows (accumulator
+  // columns [0, BN) and [BN, 2 BN), added up by the epilogue): an MMA with few columns costs about as much as a wide one
+  constexpr bool FUSE_LO = BN <= 128;
+  constexpr uint32_t IDESC2 = (1u << 4) | ((uint32_t)((2 * BN) >> 3) << 17) | ((uint32_t)(GBM >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = FUSE_LO ? 2 * BN : BN;
   const int STAGES = grp.stages;
   const uint32_t STAGE_BYTES = grp.stage_bytes;
   const uint32_t X_OFF = ((grp.dual & 2) ? 2u : 1u) * G_A_BYTES, XLO_OFF = X_OFF + X_BYTES;
@@ -442,18 +446,33 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
-  pdl_wait();   // operands and epilogue inputs come from the kernels before this one
+  // The weights are constants: the ring's first round of weight tiles is on its way before the kernels ahead of this
+  // one have finished.  What they wrote (X, the epilogue's inputs and outputs) is touched only after pdl_wait(): by
+  // the X loads and by the epilogue warps.
 
   if (warp == 0) {
     if (lane == 0) {
+      const uint32_t w_bytes = (w_lo ? 2u : 1u) * G_A_BYTES, x_bytes = (x_lo ? 2u : 1u) * X_BYTES;
+      const int pre = nkz < STAGES ? nkz : STAGES;
+      for (int kb = 0; kb < pre; ++kb) {
+        mbar_expect_tx_only(&full[kb], w_bytes);
+        const uint32_t dst = tiles + (uint32_t)kb * STAGE_BYTES;
+        tma_load_2d(dst, &maps.b[pi], (kz0 + kb) * GBK, tile_n * GBM, &full[kb]);
+        if (w_lo) tma_load_2d(dst + G_A_BYTES, &maps.b2[pi], (kz0 + kb) * GBK, tile_n * GBM, &full[kb]);
+      }
+      pdl_wait();
       for (int kb = 0; kb < nkz; ++kb) {
         const int s = kb % STAGES;
-        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
-        mbar_expect_tx(&full[s], (w_lo ? 2u : 1u) * G_A_BYTES + (x_lo ? 2u : 1u) * X_BYTES);
         const uint32_t dst = tiles + (uint32_t)s * STAGE_BYTES;
         const int kx = (kz0 + kb) * GBK;
-        tma_load_2d(dst, &maps.b[pi], kx, tile_n * GBM, &full[s]);
-        if (w_lo) tma_load_2d(dst + G_A_BYTES, &maps.b2[pi], kx, tile_n * GBM, &full[s]);
+        if (kb >= pre) {
+          if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1, abort_flag, g.status, ST_GEMM_TIMEOUT)) break;
+          mbar_expect_tx(&full[s], w_bytes + x_bytes);
+          tma_load_2d(dst, &maps.b[pi], kx, tile_n * GBM, &full[s]);
+          if (w_lo) tma_load_2d(dst + G_A_BYTES, &maps.b2[pi], kx, tile_n * GBM, &full[s]);
+        } else {
+          mbar_expect_tx(&full[s], x_bytes);
+        }
         tma_load_2d(dst + X_OFF, &maps.a[pi], kx, m0, &full[s]);
         if (x_lo) tma_load_2d(dst + XLO_OFF, &maps.a2[pi], kx, m0, &full[s]);
       }
@@ -466,10 +485,11 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
         tc_fence_after();
         const uint32_t base = tiles + (uint32_t)s * STAGE_BYTES;
         const uint64_t wd = umma_desc_k128(base), xd = umma_desc_k128(base + X_OFF);
+        const bool wide = FUSE_LO && x_lo;
 #pragma unroll
         for (int k4 = 0; k4 < GBK / 16; ++k4)
-          umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), IDESC, (kb | k4) != 0);
-        if (x_lo) {
+          umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xd + (uint64_t)(k4 * 2), wide ? IDESC2 : IDESC, (kb | k4) != 0);
+        if (x_lo && !wide) {
           const uint64_t xl = umma_desc_k128(base + XLO_OFF);
 #pragma unroll
           for (int k4 = 0; k4 < GBK / 16; ++k4) umma_f16(tmem_base, wd + (uint64_t)(k4 * 2), xl + (uint64_t)(k4 * 2), IDESC, 1u);
@@ -486,6 +506,7 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   } else {
     const int quad = warp & 3;
     const int ch = tile_n * GBM + quad * 32 + lane;
+    pdl_wait();
     const bool ok = mbar_wait(acc_full, 0, abort_flag, g.status, ST_GEMM_TIMEOUT);
     tc_fence_after();
     if (ok) {
@@ -495,6 +516,12 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
         uint32_t acc[32];
         __syncwarp();
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, acc);
+        if (FUSE_LO && x_lo) {
+          uint32_t part[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(BN + c0), part);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __uint_as_float(part[i]));
+        }
         if (ch < g.N) {
           if (grp.split > 1) {
             float *dst = g.raw + ((size_t)blockIdx.z * g.M + m0 + c0) * g.N + ch;
@@ -1448,11 +1475,11 @@ cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
   const int slots = bn <= 64 ? 2 * sms : sms;
   if (raw_ok) {
     // cost of a split, in K slices of one CTA: waves x (slices per CTA + fill and drain) + the slabs it adds
-    const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 4));
+    const int ctas = tiles * m_tiles, max_split = std::max(1, std::min(GEMM_SPLIT_MAX, min_k1 / 2));
     float best = 0.f;
     for (int sp = 1; sp <= max_split; ++sp) {
       const int waves = (ctas * sp + slots - 1) / slots;
-      const float cost = (float)waves * (float)((min_k1 + sp - 1) / sp + 2) + 0.5f * (float)sp;
+      const float cost = (float)waves * (float)((min_k1 + sp - 1) / sp + 2) + 0.25f * (float)sp;
       if (sp == 1 || cost < best) { best = cost; grp.split = sp; }
     }
   }
