@@ -1059,6 +1059,17 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     for (int pc = 0; pc < n_pieces; ++pc) CU(cudaStreamWaitEvent(m->seq_streams[pc], start, 0));
   }
   float *const x_all = x;
+  // Batch mode: a projection that was split over K leaves its slabs to the row kernel that follows it (the WKV step
+  // after key / value / receptance, the LayerNorm after the two projections that add to x) instead of a finishing
+  // pass of its own: three launches fewer per layer.
+  struct Pending { const float *raw; const __half *cscale, *r, *r_lo; float scale; int split; } pend_x = {nullptr, nullptr, nullptr, nullptr, 1.f, 1};
+  auto take_pending = [&](SeqLnArgs &la, float *xrows) {
+    if (pend_x.split > 1) {
+      la.pend_raw = pend_x.raw; la.pend_cscale = pend_x.cscale; la.pend_r = pend_x.r; la.pend_r_lo = pend_x.r_lo;
+      la.pend_scale = pend_x.scale; la.pend_split = pend_x.split; la.x_wr = xrows;
+    }
+    pend_x.split = 1;
+  };
   for (int l = 0; l < m->L; ++l)
   for (int pc = 0; pc < n_pieces; ++pc) {
     const std::string b = "blocks." + std::to_string(l) + ".", a = b + "att.", f = b + "ffn.";
@@ -1096,7 +1107,11 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     // k and v build the recurrent state, which keeps growing with the prompt: their projections take the
     // activations as hi + lo fp16 pairs (a second pass over K), like every decode matvec does
     la.op_lo[0] = lo0; la.op_lo[1] = lo1; la.op_lo[2] = lo2; la.op_lo[3] = lo3;
+    take_pending(la, x);
     CU(launch_ln_mix_seq(la, st));
+    int kvr_split = 1;
+    const __half *kvr_cs[3] = {nullptr, nullptr, nullptr};
+    const float *kvr_raw[3] = {nullptr, nullptr, nullptr};
     {
       // the attention projections in one launch; the two with a second pass over K first
       GemmArgs grp[4] = {mk(T, op[0], a + "key.weight", C, C, GEMM_EPI_F32, k, nullptr, nullptr, 1.f, lo0),
@@ -1105,7 +1120,9 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
                          mk(T, op[2], a + "receptance.weight", C, C, GEMM_EPI_F32, r, nullptr, nullptr, 1.f, lo2)};
       if (m->gate) { grp[3] = mk(T, op[3], a + "gate.weight", C, C, GEMM_EPI_SILU_F16, g, nullptr, nullptr, 1.f, lo3); grp[3].out_lo = g_lo; }
       give_raw(grp, m->gate ? 4 : 3);
-      CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st));
+      const bool defer = batch_mode && !m->v5;
+      CU(launch_gemm_group(grp, m->gate ? 4 : 3, mt, st, defer ? &kvr_split : nullptr));
+      for (int i = 0; i < 3; ++i) { kvr_cs[i] = grp[i].col_scale; kvr_raw[i] = grp[i].raw; }
     }
     if (m->v5) {
       SeqWkvArgs wa;
@@ -1122,13 +1139,20 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       memset(&wa, 0, sizeof(wa));
       wa.k = k; wa.v = v; wa.r = r; wa.decay = vp(a + "time_decay"); wa.first = vp(a + "time_first");
       wa.state = stb + off_mid(C, af); wa.state_stride = m->state_stride; wa.out = yn; wa.out_lo = yn_lo; wa.T = T; wa.C = C; wa.batch_mode = batch_mode;
+      if (kvr_split > 1) {
+        wa.split = kvr_split;
+        wa.raw_k = kvr_raw[0]; wa.raw_v = kvr_raw[1]; wa.raw_r = kvr_raw[2];
+        wa.cs_k = kvr_cs[0]; wa.cs_v = kvr_cs[1]; wa.cs_r = kvr_cs[2];
+      }
       CU(launch_wkv4_rows(wa, st));
     }
     {
       GemmArgs go = mk(T, yn, a + "output.weight", C, C, GEMM_EPI_ADD_F32, x, x, nullptr, 1.f, yn_lo);
       give_raw(&go, 1);
       // prompts: few tiles, 128-row tiles fill the SMs better (measured); streams: one pass over the weights for all rows
-      CU(launch_gemm_group(&go, 1, batch_mode ? mt : 1, st));
+      int sp = 1;
+      CU(launch_gemm_group(&go, 1, batch_mode ? mt : 1, st, batch_mode ? &sp : nullptr));
+      if (sp > 1) pend_x = {go.raw, go.col_scale, nullptr, nullptr, go.scale, sp};
     }
     // ---- channel mix ----
     memset(&la, 0, sizeof(la));
@@ -1139,6 +1163,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     la.sx_rd = stb + off_ffn_sx(C, H, m->v5, af, par); la.sx_wr = stb + off_ffn_sx(C, H, m->v5, af, par ^ 1);
     la.T = T; la.C = C; la.nvec = 2; la.act_fp16 = af;
     la.batch_mode = batch_mode; la.state_stride = m->state_stride;
+    take_pending(la, x);
     CU(launch_ln_mix_seq(la, st));
     const bool halve = af && (l + 1) % 6 == 0;   // x / 2 every 6 layers under fp16 activations (model_forward_seq.cpp:165-167)
     {
@@ -1150,7 +1175,9 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
       GemmArgs gv = mk(T, kk, f + "value.weight", C, F, GEMM_EPI_MULADD_F32, x, x, rr, halve ? 0.5f : 1.f, kk_lo);
       gv.aux1_lo = rr_lo;
       give_raw(&gv, 1);
-      CU(launch_gemm_group(&gv, 1, batch_mode ? mt : 1, st));
+      int sp = 1;
+      CU(launch_gemm_group(&gv, 1, batch_mode ? mt : 1, st, batch_mode ? &sp : nullptr));
+      if (sp > 1) pend_x = {gv.raw, gv.col_scale, rr, rr_lo, gv.scale, sp};
     }
     m->launches += m->v5 ? 9 : 7;
     if (n_pieces > 1) CU(cudaEventRecord(m->seq_events[pc * m->L + l], st));
@@ -1165,6 +1192,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     memset(&la, 0, sizeof(la));
     la.x = x; la.ln_w = vp("ln_out.weight"); la.ln_b = vp("ln_out.bias"); la.op[0] = op_all[0]; la.op_lo[0] = lo0_all;
     la.T = T; la.C = C; la.nvec = 0; la.act_fp16 = af; la.batch_mode = 1;
+    take_pending(la, x);
     CU(launch_ln_mix_seq(la, st));
     GemmArgs gh = mk(T, op_all[0], "head.weight", m->V, C, GEMM_EPI_F32, m->d_out, nullptr, nullptr, 1.f, lo0_all);
     gh.ldo = m->Vpad;

@@ -145,7 +145,7 @@ constexpr int GEMM_SPLIT_MAX = 16;
 int device_sm_count();   // SMs of the current device
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st);   // one GEMM; 256-row tiles when M > 128
 // n <= 4 GEMMs with equal M in one launch; mt = 128-row sub-tiles per CTA (1 or 2)
-cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st);
+cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st, int *defer_split = nullptr);
 // row kernels of seq mode
 struct SeqLnArgs {
   const float *x;            // [T, C] residual stream
@@ -158,6 +158,14 @@ struct SeqLnArgs {
   int T, C, nvec, act_fp16;
   int batch_mode;            // rows are streams: shift states are per row, state_stride bytes apart
   size_t state_stride;
+  // optional (pend_split > 1, batch mode): the projection before this LayerNorm has not been finished -- its
+  // split-K slabs [pend_split][T][C] are summed here and x = (x + [r *] sum) * pend_scale is stored to x_wr first
+  const float *pend_raw;
+  const __half *pend_cscale;          // its per-column scales, or null
+  const __half *pend_r, *pend_r_lo;   // [T, C] factor of the sum (channel mix), or null (time mix: plain add)
+  float pend_scale;
+  int pend_split;
+  float *x_wr;
 };
 struct SeqWkvArgs {
   const float *r, *k, *v;    // [T, C]
@@ -178,6 +186,10 @@ struct Wkv4Args {
   __half *out;               // [rows, C] sigmoid(r) * wkv
   __half *out_lo;            // optional: its fp16 rounding remainder
   int T, C, batch_mode;      // seq: T rows of one stream; batch: T streams, one row each
+  // optional (split > 1): k, v, r are still split-K slabs [split][T][C] (+ per-column scales), summed in the kernel
+  const float *raw_k, *raw_v, *raw_r;
+  const __half *cs_k, *cs_v, *cs_r;
+  int split;
 };
 cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st);
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st);

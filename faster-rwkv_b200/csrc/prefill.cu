@@ -1069,7 +1069,42 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
       if (from_row) pv[j] = xr[i4 - n4];
     }
   }
-  const float2 st = stats_from_regs(xv, n4, a.x[(size_t)t * C], C, red);
+  float piv = a.x[(size_t)t * C];
+  if (a.pend_split > 1) {
+    // the projection before this LayerNorm left its split-K slabs: sum them (in slab order, like gemm_finish_kernel),
+    // apply its epilogue x = (x + [r *] sum) * scale, store the finished row and normalise it from the registers
+    __shared__ float piv_s;
+#pragma unroll
+    for (int j = 0; j < LN_MAX4; ++j) {
+      const int i4 = threadIdx.x + j * 256;
+      if (i4 >= n4) continue;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int z = 0; z < a.pend_split; ++z) {
+        const float4 p = *reinterpret_cast<const float4 *>(a.pend_raw + ((size_t)z * a.T + t) * C + (size_t)i4 * 4);
+        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+      }
+      if (a.pend_cscale) {
+        const __half *cs = a.pend_cscale + (size_t)i4 * 4;
+        v.x *= __half2float(cs[0]); v.y *= __half2float(cs[1]); v.z *= __half2float(cs[2]); v.w *= __half2float(cs[3]);
+      }
+      float r[4] = {1.f, 1.f, 1.f, 1.f};
+      if (a.pend_r) {
+        const size_t o = (size_t)t * C + (size_t)i4 * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          r[i] = __half2float(a.pend_r[o + i]);
+          if (a.pend_r_lo) r[i] += __half2float(a.pend_r_lo[o + i]);
+        }
+      }
+      xv[j] = make_float4((xv[j].x + r[0] * v.x) * a.pend_scale, (xv[j].y + r[1] * v.y) * a.pend_scale,
+                          (xv[j].z + r[2] * v.z) * a.pend_scale, (xv[j].w + r[3] * v.w) * a.pend_scale);
+      reinterpret_cast<float4 *>(a.x_wr + (size_t)t * C)[i4] = xv[j];
+      if (i4 == 0) piv_s = xv[j].x;
+    }
+    __syncthreads();
+    piv = piv_s;
+  }
+  const float2 st = stats_from_regs(xv, n4, piv, C, red);
   float2 sp = make_float2(0.f, 0.f);
   if (from_row) sp = stats_from_regs(pv, n4, a.x[(size_t)(t - 1) * C], C, red);
   const uint8_t *srd = reinterpret_cast<const uint8_t *>(a.sx_rd) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
@@ -1131,7 +1166,19 @@ __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
   const int t0 = a.batch_mode ? b : 0, t1 = a.batch_mode ? b + 1 : a.T;
   for (int t = t0; t < t1; ++t) {
     const size_t o = (size_t)t * a.C + c;
-    const float k = a.k[o], v = a.v[o], r = 1.f / (1.f + expf(-a.r[o]));
+    float k, v, rp;
+    if (a.split > 1) {
+      // the projections left their split-K slabs: sum them here, in slab order like gemm_finish_kernel
+      k = 0.f; v = 0.f; rp = 0.f;
+      for (int z = 0; z < a.split; ++z) {
+        const size_t zo = ((size_t)z * a.T + t) * a.C + c;
+        k += a.raw_k[zo]; v += a.raw_v[zo]; rp += a.raw_r[zo];
+      }
+      if (a.cs_k) { k *= __half2float(a.cs_k[c]); v *= __half2float(a.cs_v[c]); rp *= __half2float(a.cs_r[c]); }
+    } else {
+      k = a.k[o]; v = a.v[o]; rp = a.r[o];
+    }
+    const float r = 1.f / (1.f + expf(-rp));
     float ww = u + k;
     float pm = fmaxf(pp, ww);
     float e1 = expf(pp - pm), e2 = expf(ww - pm);
@@ -1437,7 +1484,7 @@ bool wt_enabled() {
 }
 
 // up to GEMM_SMALL_M rows: weights along the MMA rows (gemm_wt_kernel), split-K into slabs when scratch was given
-cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
+cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st, int *defer_split) {
   const int M = probs[0].M;
   // (measured at 200 .. 512 rows: 256-row X tiles beat two passes with 128-row tiles by 10 %)
   const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -1496,7 +1543,8 @@ cudaError_t launch_gemm_wt(const GemmArgs *probs, int n, cudaStream_t st) {
                   : bn == 128 ? launch_gemm_wt_t<128>(maps, grp, grid, smem, st)
                               : launch_gemm_wt_t<256>(maps, grp, grid, smem, st);
   if (e != cudaSuccess) return e;
-  if (grp.split > 1) {
+  if (defer_split) *defer_split = grp.split;
+  if (grp.split > 1 && !defer_split) {
     int max_n = 0;
     for (int i = 0; i < n; ++i) max_n = std::max(max_n, probs[i].N);
     launch_k(gemm_finish_kernel, dim3(dim3((M * (max_n / 4) + 255) / 256, n)), dim3(256), 0, st, grp);
@@ -1529,7 +1577,7 @@ WqPlan wq_plan(long long avail, long long buf_bytes, uint32_t wbox, int want_ne,
 }
 
 // quantised weights in packed form (GemmArgs::Wq): any number of rows, walked in tiles of up to 256 along grid.y
-cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
+cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st, int *defer_split) {
   const int M = probs[0].M, fmt = probs[0].wfmt;
   if (fmt != FMT_INT8 && fmt != FMT_INT4) return cudaErrorInvalidValue;
   const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -1601,7 +1649,8 @@ cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
   e = bn == 32 ? FRB_WQ(32) : bn == 64 ? FRB_WQ(64) : bn == 128 ? FRB_WQ(128) : FRB_WQ(256);
 #undef FRB_WQ
   if (e != cudaSuccess) return e;
-  if (grp.split > 1) {
+  if (defer_split) *defer_split = grp.split;
+  if (grp.split > 1 && !defer_split) {
     int max_n = 0;
     for (int i = 0; i < n; ++i) max_n = std::max(max_n, probs[i].N);
     launch_k(gemm_finish_kernel, dim3(dim3((M * (max_n / 4) + 255) / 256, n)), dim3(256), 0, st, grp);
@@ -1610,11 +1659,14 @@ cudaError_t launch_gemm_wq(const GemmArgs *probs, int n, cudaStream_t st) {
 }
 }  // namespace
 
-cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st) {
+// defer_split (optional): the caller's next kernel sums the split-K slabs itself (ln_mix_seq_kernel, wkv4_rows_kernel);
+// it receives the split that was chosen, 1 meaning that the outputs are already complete.
+cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t st, int *defer_split) {
   if (n < 1 || n > GEMM_GROUP_MAX || (mt != 1 && mt != 2)) return cudaErrorInvalidValue;
   const int M = probs[0].M;
-  if (probs[0].Wq) return launch_gemm_wq(probs, n, st);
-  if (M <= GEMM_SMALL_M && wt_enabled()) return launch_gemm_wt(probs, n, st);
+  if (defer_split) *defer_split = 1;
+  if (probs[0].Wq) return launch_gemm_wq(probs, n, st, defer_split);
+  if (M <= GEMM_SMALL_M && wt_enabled()) return launch_gemm_wt(probs, n, st, defer_split);
   // few rows (batched decode): narrow N tiles and split-K, so that a few hundred CTAs stream the weights
   const bool narrow = M <= GEMM_SMALL_M;
   const int bn = narrow ? 64 : 256;
@@ -1657,7 +1709,8 @@ cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t
   if (narrow) e = mt == 1 ? launch_gemm_t<1, 64>(maps, grp, grid, smem, st) : launch_gemm_t<2, 64>(maps, grp, grid, smem, st);
   else e = mt == 1 ? launch_gemm_t<1, 256>(maps, grp, grid, smem, st) : launch_gemm_t<2, 256>(maps, grp, grid, smem, st);
   if (e != cudaSuccess) return e;
-  if (grp.split > 1) {
+  if (defer_split) *defer_split = grp.split;
+  if (grp.split > 1 && !defer_split) {
     int max_n = 0;
     for (int i = 0; i < n; ++i) max_n = std::max(max_n, probs[i].N);
     launch_k(gemm_finish_kernel, dim3(dim3((M * (max_n / 4) + 255) / 256, n)), dim3(256), 0, st, grp);
@@ -1666,7 +1719,7 @@ cudaError_t launch_gemm_group(const GemmArgs *probs, int n, int mt, cudaStream_t
 }
 
 cudaError_t launch_gemm_f16(const GemmArgs &g, cudaStream_t st) {
-  return launch_gemm_group(&g, 1, g.M > GBM ? 2 : 1, st);   // no raw scratch: no split-K
+  return launch_gemm_group(&g, 1, g.M > GBM ? 2 : 1, st, nullptr);   // no raw scratch: no split-K
 }
 
 }  // namespace frb
