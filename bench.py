@@ -416,6 +416,9 @@ def main():
     ap.add_argument("--phase-budget", action="store_true", help="print the per-phase budget of the batch-1 kernel (c1)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ref-gpu", action="store_true")
+    ap.add_argument("--steps-only", action="store_true",
+                    help="build the model of --workload/--weights/--batch, run --warmup + --steps greedy decode steps and "
+                         "print their mean time; nothing else runs (for profiler captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -458,6 +461,19 @@ def main():
     if args.prefill_only:
         if rank == 0:
             print(json.dumps({"metric": "prefill_tokens_per_s", "n_gpus": 1, "data": "synthetic", **prefill_leg(pkg, local_rank)}))
+        return
+    if args.steps_only:
+        if rank == 0:
+            import torch
+            torch.cuda.set_device(local_rank)
+            n = args.batch or 1
+            m = build_model(pkg, shape, fmt, n, local_rank)
+            ids = synth.token_ids(shape, n, seed=0)
+            ms, _, launches = timed_greedy(torch, torch.cuda.synchronize, m, ids, args.steps, args.warmup)
+            print(json.dumps({"metric": "decode_step_ms", "workload": args.workload, "weights": fmt, "streams": n,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+                              "gpu_launches": int(launches)}))
+            drop(m)
         return
     if args.phase_budget:
         if rank == 0:

@@ -84,6 +84,7 @@ struct fr_b200_model {
   uint8_t *d_qcopy = nullptr;    size_t qcopy_bytes = 0;
   __half *d_qscale = nullptr;    size_t qscale_halfs = 0;
   bool row_copies = true;        // keep the copies the GEMM path needs (FR_B200_ROW_COPIES=0: decode-only model)
+  bool rows_planned = false;     // some batch up to max_batch is decoded by the GEMM path
   uint8_t *d_seq = nullptr;      size_t seq_bytes = 0; int seq_T = 0;
   PhaseDev *d_head_phase = nullptr;   // the head as a stand-alone matvec phase
   // greedy runs of many streams: two decode steps captured as a CUDA graph and replayed (the step is ~170 launches)
@@ -220,7 +221,16 @@ void plan(fr_b200_model *m) {
   // a prompt's head is a matvec over the last token), made at load for RWKV-5.x and for max_batch > 8, else on the
   // first long prompt; int8 / int4 models keep the packed codes row-major [N, K] / [N, K/2] (+ scales), the same
   // bytes as the streaming tiles, which the GEMM expands in shared memory.
-  const bool big = m->cfg.max_batch > MAX_B;
+  // (also when the persistent kernel cannot carry max_batch streams of a model this wide: its shared memory holds the
+  // activation vectors of every stream, e.g. 8 streams x 8192 channel-mix inputs do not fit)
+  bool big = m->cfg.max_batch > MAX_B;
+  if (!big) {
+    int optin = 0;
+    if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, m->device) == cudaSuccess)
+      for (int mode = 1; mode <= decode_mode(m->cfg.max_batch); ++mode)
+        if (decode_smem_bytes(fmt, mode, C, F, m->v5 ? 5 : 4, 2, 1) > (size_t)optin) big = true;
+  }
+  m->rows_planned = big;
   for (auto &kv : m->mats) {
     MatrixSlot &ms = kv.second;
     if (fmt == FMT_FP16) {
@@ -415,7 +425,7 @@ int fr_b200_create(const fr_b200_config *cfg, fr_b200_model **out) {
   if (!rc) rc = alloc((void **)&m->d_out, m->out_bytes());
   if (!rc) rc = alloc((void **)&m->d_amax, (size_t)B * 8);
   // fp16 W^T copies now for RWKV-5.x (seq kernels) and for models that decode more than 8 streams; else on demand
-  if (!rc && m->plain_halfs && m->row_copies && (m->v5 || cfg->max_batch > MAX_B)) rc = alloc((void **)&m->d_plain, m->plain_halfs * 2);
+  if (!rc && m->plain_halfs && m->row_copies && (m->v5 || m->rows_planned)) rc = alloc((void **)&m->d_plain, m->plain_halfs * 2);
   if (!rc && m->qcopy_bytes) rc = alloc((void **)&m->d_qcopy, m->qcopy_bytes);
   if (!rc && m->qscale_halfs) rc = alloc((void **)&m->d_qscale, m->qscale_halfs * 2);
   if (!rc && m->pscale_halfs) rc = alloc((void **)&m->d_pscale, m->pscale_halfs * 2);
@@ -579,7 +589,7 @@ int fr_b200_finalize(fr_b200_model *m) {
     for (int s = want; s >= 2; --s)
       if (decode_smem_bytes(m->fmt, mode, m->C, m->F, ver, s, m->d_vecs16 != nullptr) <= (size_t)optin) { st = s; break; }
     if (st == 0) {
-      if (m->cfg.max_batch > MAX_B && mode > 0) { m->n_stages[mode] = 0; continue; }   // such batches take the GEMM path
+      if (m->rows_planned && mode > 0) { m->n_stages[mode] = 0; continue; }   // such batches take the GEMM path
       return fail(FR_B200_E_UNSUPPORTED, "model too wide for shared memory at this batch size (max_batch " +
                                              std::to_string(m->cfg.max_batch) + ")");
     }
@@ -659,7 +669,7 @@ int ensure_row_copies(fr_b200_model *m) {
 bool rows_path_built(const fr_b200_model *m) { return m->d_plain || m->d_qcopy; }
 int rows_decode_check(fr_b200_model *m, const int32_t *ids_host, int batch, cudaStream_t st) {
   if (m->fmt == FMT_FP16 && !m->mats["head.weight"].has_plain)
-    return fail(FR_B200_E_UNSUPPORTED, "this batch size needs a model created with max_batch > 8");
+    return fail(FR_B200_E_UNSUPPORTED, "this batch size needs the GEMM path, which the model was created without");
   {
     int rc = ensure_row_copies(m);
     if (rc) return rc;

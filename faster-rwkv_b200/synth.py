@@ -60,6 +60,7 @@ SHAPES: Dict[str, Shape] = {
     "tiny50": Shape("5", 2, 128, 448, 96, n_head=2),
     "mid4": Shape("4", 7, 256, 1024, 512),
     "mid52": Shape("5.2", 3, 256, 1024, 512, n_head=4),
+    "wide4": Shape("4", 2, 256, 8192, 512),   # channel-mix width of c1: 8 streams of it exceed the persistent kernel
 }
 
 

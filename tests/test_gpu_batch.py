@@ -44,6 +44,23 @@ def test_many_streams_match_oracle(pkg, orc, synth, name, fmt, B):
     m.close()
 
 
+@pytest.mark.parametrize("fmt", ["fp16", "int4"])
+def test_eight_streams_of_a_wide_model_take_the_gemm_path(pkg, orc, synth, fmt):
+    """A model whose channel-mix width does not leave room for 8 streams in the persistent kernel's shared memory
+    (8 x 8192 inputs) is still created with max_batch = 8: batches of 5..8 are decoded by the GEMM path, 1..4 by the
+    persistent kernel, on the same state."""
+    shape, m, ref = _pair(pkg, orc, synth, "wide4", fmt, 8)
+    ids = synth.token_ids(shape, 3 * 8, seed=21).reshape(3, 8)
+    got = [m.decode(ids[0]), m.decode(ids[1]), m.decode(ids[2][:3])]   # 8, 8, then 3 streams
+    for b in (0, 2, 7):
+        ref.reset()
+        for t in range(3):
+            if t == 2 and b >= 3:
+                break
+            _close(got[t][b], ref.run(int(ids[t, b])), f"wide4 {fmt} stream {b} step {t}")
+    m.close()
+
+
 def test_small_and_large_batches_share_state(pkg, orc, synth):
     """The persistent kernel (<= 8 streams) and the GEMM path (> 8) read and write the same state slots, and streams
     that are decoded together need not have seen the same number of tokens (continuous batching: a stream joins a
