@@ -172,7 +172,12 @@ void init_model(Model *model, Device device, const std::string &path, const std:
   cfg.max_batch = 1;
   cfg.device = 0;
   // Model::SaveStateFile reads the state tensors with memcpy (model.cpp:110): hand out addresses the host can read
-  cfg.host_visible_state = 1;
+  // managed state memory, so that the unchanged Model::SaveStateFile (a plain memcpy of data_ptr(), model.cpp:110)
+  // works; FR_B200_HOST_STATE=0 keeps the state in ordinary device memory (state files then need the C ABI's export)
+  {
+    const char *hs = std::getenv("FR_B200_HOST_STATE");
+    cfg.host_visible_state = (hs && std::atoi(hs) == 0) ? 0 : 1;
+  }
 
   auto ex = std::make_shared<Extra>();
   FRB_CALL(fr_b200_create(&cfg, &ex->h));

@@ -55,9 +55,12 @@ typedef struct fr_b200_config {
   int weight_format;  /* FR_B200_W_* */
   int act_fp16;       /* 1: "cuda fp16" semantics — fp16 token-shift states and x /= 2 every 6 layers
                          (kernels/default/model_forward.cpp:173-175); 0: fp32 activations ("int8"/"int4") */
-  int max_batch;      /* stream slots, 1..4096.  Up to 8 streams per call run in the persistent kernel; a model created
-                       * with max_batch > 8 also keeps every projection as fp16 W^T (dequantised for int8 / int4) and
-                       * decodes larger batches through tensor-core GEMMs, one row per stream */
+  int max_batch;      /* stream slots, 1..4096.  Up to 8 streams per call run in the persistent kernel where its shared
+                       * memory can hold their activation vectors (up to 4 at n_ffn = 8192); larger batches are decoded
+                       * by tensor-core GEMMs, one row per stream.  For that path fp16 models created with
+                       * max_batch > 8 (or too wide for max_batch streams in the persistent kernel) keep every
+                       * projection a second time as fp16 W^T; int8 / int4 models always keep a row-major copy of the
+                       * packed codes, the same bytes again, which the GEMM expands in shared memory */
   int device;         /* CUDA device ordinal */
   int host_visible_state; /* 1: the recurrent state lives in managed memory, so the device addresses fr_b200_state_tensor
                            * hands out can also be read by the host between calls.  The reference's Model::SaveStateFile
