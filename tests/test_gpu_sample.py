@@ -4,7 +4,7 @@ from its sources: same logits, same uniform draw -> same token."""
 import numpy as np
 import pytest
 
-from oracle.sampler_ref import minstd_uniforms as _minstd_uniforms, ref_sample
+from oracle.sampler_ref import minstd_uniforms as _minstd_uniforms, pick_distance, ref_sample
 
 pytestmark = pytest.mark.gpu
 
@@ -87,9 +87,15 @@ def test_sample_matches_the_reference_sampler_binary_at_full_vocab(pkg, synth, t
             want, margin = ref_sample(logits[b], temperature, top_k, top_p, np.float32(us[d]))
             assert want == theirs[b, d] or margin <= 1e-5       # the numpy restatement agrees with the reference binary
             # the device sums up to 65536 weights in segments, the reference serially: a draw closer than 1e-4 (relative
-            # to the total) to a threshold may resolve to the neighbouring entry
+            # to the total) to a threshold may resolve to a neighbouring entry -- never further away than that
             if margin > 1e-4:
                 assert got[b] == theirs[b, d], (d, b, int(got[b]), int(theirs[b, d]), margin)
                 checked += 1
-    assert checked >= B * draws // 2
+            else:
+                dist = pick_distance(logits[b], temperature, top_k, top_p, np.float32(us[d]), int(got[b]))
+                assert dist <= 1e-4, (d, b, int(got[b]), int(theirs[b, d]), margin, dist)
+    # a flat distribution over the whole vocabulary (temperature 2, no cuts) gives every token ~1e-5 of the weight: all of
+    # its draws are "near a threshold" and are covered by the distance check alone
+    flat = top_k == 0 and top_p >= 1.0 and temperature > 1.0
+    assert flat or checked >= B * draws // 2
     m.close()
