@@ -1015,10 +1015,11 @@ __global__ void gather_emb_kernel(const void *emb, int emb_f32, const int32_t *i
 // row writes its new one.  nvec == 0: plain LayerNorm into op[0] (ln_out before the head).
 // Each thread keeps its float4 pieces of the row (and of the row before) in registers: x is read once.
 constexpr int LN_MAX4 = 8;   // float4 per thread: n_embd <= 8192
+template <int NJ>
 __device__ __forceinline__ float2 stats_from_regs(const float4 *v, int n4, float piv, int C, float *red) {
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-  for (int j = 0; j < LN_MAX4; ++j) {
+  for (int j = 0; j < NJ; ++j) {
     if ((int)threadIdx.x + j * 256 < n4) {
       const float d0 = v[j].x - piv, d1 = v[j].y - piv, d2 = v[j].z - piv, d3 = v[j].w - piv;
       s1 += (d0 + d1) + (d2 + d3);
@@ -1053,6 +1054,8 @@ __device__ __forceinline__ float4 load_act_f4(const void *p, int i4, int act_fp1
 }
 __device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }
 
+// NJ = float4 pieces of a row per thread (2, 4 or 8: n_embd up to 2048, 4096, 8192)
+template <int NJ>
 __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
   pdl_trigger();
   pdl_wait();
@@ -1060,9 +1063,9 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
   const int t = blockIdx.x, C = a.C, n4 = C >> 2;
   const float4 *xr = reinterpret_cast<const float4 *>(a.x + (size_t)t * C);
   const bool from_row = !a.batch_mode && t > 0 && a.nvec > 0;
-  float4 xv[LN_MAX4], pv[LN_MAX4];
+  float4 xv[NJ], pv[NJ];
 #pragma unroll
-  for (int j = 0; j < LN_MAX4; ++j) {
+  for (int j = 0; j < NJ; ++j) {
     const int i4 = threadIdx.x + j * 256;
     if (i4 < n4) {
       xv[j] = xr[i4];
@@ -1074,15 +1077,32 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
     // the projection before this LayerNorm left its split-K slabs: sum them (in slab order, like gemm_finish_kernel),
     // apply its epilogue x = (x + [r *] sum) * scale, store the finished row and normalise it from the registers
     __shared__ float piv_s;
+    float4 acc[NJ];
 #pragma unroll
-    for (int j = 0; j < LN_MAX4; ++j) {
+    for (int j = 0; j < NJ; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const size_t zs = (size_t)a.T * C;
+    constexpr int ZB = NJ <= 2 ? 8 : 4;   // slabs per batch: NJ x ZB 16-byte loads in flight per thread
+    for (int z0 = 0; z0 < a.pend_split; z0 += ZB) {
+      float4 p[NJ][ZB];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const int i4 = threadIdx.x + j * 256;
+        const float *slab = a.pend_raw + (size_t)t * C + (size_t)i4 * 4;
+#pragma unroll
+        for (int i = 0; i < ZB; ++i)
+          if (i4 < n4 && z0 + i < a.pend_split) p[j][i] = *reinterpret_cast<const float4 *>(slab + (size_t)(z0 + i) * zs);
+      }
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int i = 0; i < ZB; ++i)   // in slab order
+          if (z0 + i < a.pend_split) { acc[j].x += p[j][i].x; acc[j].y += p[j][i].y; acc[j].z += p[j][i].z; acc[j].w += p[j][i].w; }
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
       const int i4 = threadIdx.x + j * 256;
       if (i4 >= n4) continue;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int z = 0; z < a.pend_split; ++z) {
-        const float4 p = *reinterpret_cast<const float4 *>(a.pend_raw + ((size_t)z * a.T + t) * C + (size_t)i4 * 4);
-        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-      }
+      float4 v = acc[j];
       if (a.pend_cscale) {
         const __half *cs = a.pend_cscale + (size_t)i4 * 4;
         v.x *= __half2float(cs[0]); v.y *= __half2float(cs[1]); v.z *= __half2float(cs[2]); v.w *= __half2float(cs[3]);
@@ -1104,13 +1124,13 @@ __global__ void __launch_bounds__(256) ln_mix_seq_kernel(SeqLnArgs a) {
     __syncthreads();
     piv = piv_s;
   }
-  const float2 st = stats_from_regs(xv, n4, piv, C, red);
+  const float2 st = stats_from_regs<NJ>(xv, n4, piv, C, red);
   float2 sp = make_float2(0.f, 0.f);
-  if (from_row) sp = stats_from_regs(pv, n4, a.x[(size_t)(t - 1) * C], C, red);
+  if (from_row) sp = stats_from_regs<NJ>(pv, n4, a.x[(size_t)(t - 1) * C], C, red);
   const uint8_t *srd = reinterpret_cast<const uint8_t *>(a.sx_rd) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
   uint8_t *swr = reinterpret_cast<uint8_t *>(a.sx_wr) + (a.batch_mode ? (size_t)t * a.state_stride : 0);
 #pragma unroll
-  for (int j = 0; j < LN_MAX4; ++j) {
+  for (int j = 0; j < NJ; ++j) {
     const int i4 = threadIdx.x + j * 256;
     if (i4 >= n4) continue;
     const float4 w = reinterpret_cast<const float4 *>(a.ln_w)[i4], b = reinterpret_cast<const float4 *>(a.ln_b)[i4];
@@ -1421,7 +1441,10 @@ cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, 
   return cudaGetLastError();
 }
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
-  launch_k(ln_mix_seq_kernel, dim3(a.T), dim3(256), 0, st, a);
+  const int n4 = a.C >> 2;
+  if (n4 <= 2 * 256) launch_k(ln_mix_seq_kernel<2>, dim3(a.T), dim3(256), 0, st, a);
+  else if (n4 <= 4 * 256) launch_k(ln_mix_seq_kernel<4>, dim3(a.T), dim3(256), 0, st, a);
+  else launch_k(ln_mix_seq_kernel<LN_MAX4>, dim3(a.T), dim3(256), 0, st, a);
   return cudaGetLastError();
 }
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
