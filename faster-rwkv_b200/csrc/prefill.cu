@@ -92,6 +92,10 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// the tensor maps are launch parameters: their first use would be a cold fetch in front of the first tile
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 
@@ -431,6 +435,11 @@ gemm_wt_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   const int kz0 = (int)((long long)blockIdx.z * num_k1 / grp.split), nkz = (int)((long long)(blockIdx.z + 1) * num_k1 / grp.split) - kz0;
   const bool x_lo = g.A2 != nullptr, w_lo = g.Bt2 != nullptr;
 
+  if (threadIdx.x == 64) {
+    prefetch_tmap(&maps.b[pi]); prefetch_tmap(&maps.a[pi]);
+    if (x_lo) prefetch_tmap(&maps.a2[pi]);
+    if (w_lo) prefetch_tmap(&maps.b2[pi]);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
@@ -624,6 +633,7 @@ gemm_wq_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ Ge
   // this CTA's slices [kz0, kz0 + nkz) touch weight slots g0 .. g0 + ng - 1 of the matrix
   const int g0 = kz0 >> KSH, ng = nkz > 0 ? ((kz0 + nkz - 1) >> KSH) - g0 + 1 : 0;
 
+  if (threadIdx.x == 64) { prefetch_tmap(&maps.b[pi]); prefetch_tmap(&maps.a[pi]); if (x_lo) prefetch_tmap(&maps.a2[pi]); }
   if (threadIdx.x == 0) {
     for (int s = 0; s < NW; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], WQ_EXP_WARPS); }
     for (int e = 0; e < NE; ++e) { mbar_init(&xfull[e], 1); mbar_init(&a_full[e], WQ_EXP_WARPS); mbar_init(&a_empty[e], 1); }
@@ -857,9 +867,19 @@ __global__ void __launch_bounds__(256) gemm_finish_kernel(const __grid_constant_
   if (idx >= g.M * n4) return;
   const int row = idx / n4, col = (idx - row * n4) * 4;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int z = 0; z < split; ++z) {
-    const float4 p = *reinterpret_cast<const float4 *>(g.raw + ((size_t)z * g.M + row) * g.N + col);
-    v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+  {
+    const float *slab = g.raw + (size_t)row * g.N + col;
+    const size_t zs = (size_t)g.M * g.N;
+    constexpr int ZB = 8;   // 8 loads in flight before the first add
+    for (int z0 = 0; z0 < split; z0 += ZB) {
+      float4 p[ZB];
+#pragma unroll
+      for (int i = 0; i < ZB; ++i)
+        if (z0 + i < split) p[i] = *reinterpret_cast<const float4 *>(slab + (size_t)(z0 + i) * zs);
+#pragma unroll
+      for (int i = 0; i < ZB; ++i)   // in slab order
+        if (z0 + i < split) { v.x += p[i].x; v.y += p[i].y; v.z += p[i].z; v.w += p[i].w; }
+    }
   }
   if (g.col_scale) {
     v.x *= __half2float(g.col_scale[col]); v.y *= __half2float(g.col_scale[col + 1]);
@@ -1190,9 +1210,19 @@ __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
     if (a.split > 1) {
       // the projections left their split-K slabs: sum them here, in slab order like gemm_finish_kernel
       k = 0.f; v = 0.f; rp = 0.f;
-      for (int z = 0; z < a.split; ++z) {
-        const size_t zo = ((size_t)z * a.T + t) * a.C + c;
-        k += a.raw_k[zo]; v += a.raw_v[zo]; rp += a.raw_r[zo];
+      const size_t zs = (size_t)a.T * a.C;
+      constexpr int ZB = 8;   // 3 x 8 loads in flight before the first add
+      for (int z0 = 0; z0 < a.split; z0 += ZB) {
+        float pk[ZB], pv[ZB], pr[ZB];
+#pragma unroll
+        for (int i = 0; i < ZB; ++i)
+          if (z0 + i < a.split) {
+            const size_t zo = (size_t)(z0 + i) * zs + o;
+            pk[i] = a.raw_k[zo]; pv[i] = a.raw_v[zo]; pr[i] = a.raw_r[zo];
+          }
+#pragma unroll
+        for (int i = 0; i < ZB; ++i)   // in slab order
+          if (z0 + i < a.split) { k += pk[i]; v += pv[i]; rp += pr[i]; }
       }
       if (a.cs_k) { k *= __half2float(a.cs_k[c]); v *= __half2float(a.cs_v[c]); rp *= __half2float(a.cs_r[c]); }
     } else {
