@@ -867,19 +867,9 @@ __global__ void __launch_bounds__(256) gemm_finish_kernel(const __grid_constant_
   if (idx >= g.M * n4) return;
   const int row = idx / n4, col = (idx - row * n4) * 4;
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-  {
-    const float *slab = g.raw + (size_t)row * g.N + col;
-    const size_t zs = (size_t)g.M * g.N;
-    constexpr int ZB = 8;   // 8 loads in flight before the first add
-    for (int z0 = 0; z0 < split; z0 += ZB) {
-      float4 p[ZB];
-#pragma unroll
-      for (int i = 0; i < ZB; ++i)
-        if (z0 + i < split) p[i] = *reinterpret_cast<const float4 *>(slab + (size_t)(z0 + i) * zs);
-#pragma unroll
-      for (int i = 0; i < ZB; ++i)   // in slab order
-        if (z0 + i < split) { v.x += p[i].x; v.y += p[i].y; v.z += p[i].z; v.w += p[i].w; }
-    }
+  for (int z = 0; z < split; ++z) {
+    const float4 p = *reinterpret_cast<const float4 *>(g.raw + ((size_t)z * g.M + row) * g.N + col);
+    v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
   }
   if (g.col_scale) {
     v.x *= __half2float(g.col_scale[col]); v.y *= __half2float(g.col_scale[col + 1]);
@@ -1210,19 +1200,9 @@ __global__ void __launch_bounds__(256) wkv4_rows_kernel(Wkv4Args a) {
     if (a.split > 1) {
       // the projections left their split-K slabs: sum them here, in slab order like gemm_finish_kernel
       k = 0.f; v = 0.f; rp = 0.f;
-      const size_t zs = (size_t)a.T * a.C;
-      constexpr int ZB = 8;   // 3 x 8 loads in flight before the first add
-      for (int z0 = 0; z0 < a.split; z0 += ZB) {
-        float pk[ZB], pv[ZB], pr[ZB];
-#pragma unroll
-        for (int i = 0; i < ZB; ++i)
-          if (z0 + i < a.split) {
-            const size_t zo = (size_t)(z0 + i) * zs + o;
-            pk[i] = a.raw_k[zo]; pv[i] = a.raw_v[zo]; pr[i] = a.raw_r[zo];
-          }
-#pragma unroll
-        for (int i = 0; i < ZB; ++i)   // in slab order
-          if (z0 + i < a.split) { k += pk[i]; v += pv[i]; rp += pr[i]; }
+      for (int z = 0; z < a.split; ++z) {
+        const size_t zo = ((size_t)z * a.T + t) * a.C + c;
+        k += a.raw_k[zo]; v += a.raw_v[zo]; rp += a.raw_r[zo];
       }
       if (a.cs_k) { k *= __half2float(a.cs_k[c]); v *= __half2float(a.cs_v[c]); rp *= __half2float(a.cs_r[c]); }
     } else {
