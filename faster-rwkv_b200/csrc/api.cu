@@ -1004,7 +1004,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
   // state scan (seq mode, RWKV-5): enough chunks to cover the SMs a few times over, none shorter than 32 tokens
   const int Tp = std::min(T, piece_rows);
   int max_chunks = 1;
-  if (!batch_mode && m->v5) max_chunks = std::max(1, std::min(Tp / 32, (8 * device_sm_count() + H - 1) / H));
+  if (!batch_mode && m->v5) max_chunks = std::max(1, std::min(Tp / 32, std::max(1, wkv5_scan_slots() / H)));
   const size_t scan_bytes = max_chunks > 1 ? (size_t)H * max_chunks * 4096 * 4 : 0;
   const size_t o_e = take(scan_bytes * n_pieces), o_sin = take(scan_bytes * n_pieces);
   if (m->seq_bytes < off) {
@@ -1101,7 +1101,7 @@ int rows_forward(fr_b200_model *m, bool batch_mode, int slot, const int32_t *ids
     __half *g_lo = glo_all ? glo_all + rc : nullptr, *rr_lo = g_lo;
     int n_chunks = 1, chunk_len = T;
     if (!batch_mode && m->v5) {
-      n_chunks = std::max(1, std::min(T / 32, (8 * device_sm_count() + H - 1) / H));
+      n_chunks = std::max(1, std::min(T / 32, std::max(1, wkv5_scan_slots() / (H * n_pieces))));   // the pieces run side by side
       chunk_len = (T + n_chunks - 1) / n_chunks;
       n_chunks = (T + chunk_len - 1) / chunk_len;
     }

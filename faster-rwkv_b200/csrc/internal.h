@@ -194,6 +194,7 @@ struct Wkv4Args {
 cudaError_t launch_gather_emb(const void *emb, int emb_f32, const int32_t *ids, int T, int C, float *x, cudaStream_t st);
 cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st);
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st);
+int wkv5_scan_slots();   // resident (head, chunk) CTAs of the scan on this device
 cudaError_t launch_gn_gate_seq(const float *y, const float *lnx_w, const float *lnx_b, const __half *g, const __half *g_lo, int T,
                                int H, __half *out, __half *out_lo, cudaStream_t st);
 cudaError_t launch_wkv4_rows(const Wkv4Args &a, cudaStream_t st);

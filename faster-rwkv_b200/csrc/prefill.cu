@@ -1292,6 +1292,30 @@ __device__ __forceinline__ void wkv_stage(float (*sr)[64], float (*sk)[64], floa
 // 64 threads per CTA: thread (jg, iq) owns value columns jg, jg + 16, jg + 32, jg + 48 and key rows 16 iq .. 16 iq + 15,
 // i.e. 64 state entries in registers; the r / k values it reads from shared memory serve four columns each.
 constexpr int WKV_THREADS = 64;
+// Packed fp32 pairs (fma.rn.f32x2 / mul.rn.f32x2: two fp32 operations per instruction on sm_100).  The scan is bound
+// by the issue rate of its multiply-adds, so the state is kept as pairs over neighbouring key rows: k, r and the decay
+// then come out of shared memory already paired, and only v needs a broadcast pair per token.
+__device__ __forceinline__ unsigned long long pack_f2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(unsigned long long v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long mul_f2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// y_t[j] = sum_i r_i (u_i k_i v_j + s_ij) = v_j (sum_i r_i u_i k_i) + sum_i r_i s_ij;  s_ij <- w_i s_ij + k_i v_j.
+// Thread (jg, iq) owns key rows iq*16 .. +15 of value columns jg + 16 q (q = 0..3): 32 pairs.
 template <int MODE>
 __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
   pdl_trigger();
@@ -1301,16 +1325,17 @@ __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
   const int jg = threadIdx.x >> 2, iq = threadIdx.x & 3;
   // batch mode: blockIdx.y is the stream, its one token is row c, its state lies state_stride floats further
   const int t_begin = a.batch_mode ? c : c * a.chunk_len, t_end = a.batch_mode ? c + 1 : min(a.T, t_begin + a.chunk_len);
-  float s[4][16], w[16], u[16];
+  unsigned long long s2[4][8], w2[8], u2[8];   // pairs over key rows (iq*16 + 2 p, + 2 p + 1)
   float *Sown = a.state + (a.batch_mode ? (size_t)c * a.state_stride : 0) + (size_t)h * 4096;
   const float *Sin = a.n_chunks == 1 ? Sown : a.s_in + ((size_t)h * a.n_chunks + c) * 4096;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int ii = iq * 16 + i;
+  for (int p = 0; p < 8; ++p) {
+    const int ii = iq * 16 + 2 * p;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) s[q][i] = MODE == 0 ? 0.f : Sin[ii * 64 + jg + 16 * q];
-    w[i] = a.per_head ? a.decay[h] : a.decay[h * 64 + ii];
-    u[i] = a.per_head ? a.first[h] : a.first[h * 64 + ii];
+    for (int q = 0; q < 4; ++q)
+      s2[q][p] = MODE == 0 ? 0ull : pack_f2(Sin[ii * 64 + jg + 16 * q], Sin[(ii + 1) * 64 + jg + 16 * q]);
+    w2[p] = a.per_head ? pack_f2(a.decay[h], a.decay[h]) : pack_f2(a.decay[h * 64 + ii], a.decay[h * 64 + ii + 1]);
+    u2[p] = a.per_head ? pack_f2(a.first[h], a.first[h]) : pack_f2(a.first[h * 64 + ii], a.first[h * 64 + ii + 1]);
   }
   int buf = 0;
   if (t_begin < t_end) wkv_stage(sr[0], sk[0], sv[0], a, h, t_begin, min(WKV_TT, t_end - t_begin), MODE == 2);
@@ -1325,27 +1350,40 @@ __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      float vj[4], y[4] = {0.f, 0.f, 0.f, 0.f};
+      float vj[4];
+      unsigned long long v2[4], y2[4] = {0ull, 0ull, 0ull, 0ull}, ruk2 = 0ull;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) vj[q] = sv[buf][tt][jg + 16 * q];
+      for (int q = 0; q < 4; ++q) {
+        vj[q] = sv[buf][tt][jg + 16 * q];
+        v2[q] = pack_f2(vj[q], vj[q]);
+      }
 #pragma unroll
-      for (int i = 0; i < 16; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4 *>(&sk[buf][tt][iq * 16 + i]);
-        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (MODE == 2) r4 = *reinterpret_cast<const float4 *>(&sr[buf][tt][iq * 16 + i]);
-        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w};
+      for (int p = 0; p < 8; p += 2) {
+        // four key rows = two pairs per 16-byte load
+        const ulonglong2 k4 = *reinterpret_cast<const ulonglong2 *>(&sk[buf][tt][iq * 16 + 2 * p]);
+        ulonglong2 r4 = make_ulonglong2(0ull, 0ull);
+        if (MODE == 2) r4 = *reinterpret_cast<const ulonglong2 *>(&sr[buf][tt][iq * 16 + 2 * p]);
+        const unsigned long long kk[2] = {k4.x, k4.y}, rr[2] = {r4.x, r4.y};
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
+        for (int e = 0; e < 2; ++e) {
+          if (MODE == 2) ruk2 = fma_f2(mul_f2(rr[e], u2[p + e]), kk[e], ruk2);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float x = kk[e] * vj[q];
-            if (MODE == 2) y[q] += rr[e] * (u[i + e] * x + s[q][i + e]);
-            s[q][i + e] = s[q][i + e] * w[i + e] + x;
+            if (MODE == 2) y2[q] = fma_f2(rr[e], s2[q][p + e], y2[q]);
+            s2[q][p + e] = fma_f2(s2[q][p + e], w2[p + e], mul_f2(kk[e], v2[q]));
           }
+        }
       }
       if (MODE == 2) {
+        float ra, rb;
+        unpack_f2(ruk2, ra, rb);
+        const float ruk = ra + rb;
+        float y[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
+          float ya, yb;
+          unpack_f2(y2[q], ya, yb);
+          y[q] = fmaf(vj[q], ruk, ya + yb);
           y[q] += __shfl_xor_sync(0xffffffffu, y[q], 1);
           y[q] += __shfl_xor_sync(0xffffffffu, y[q], 2);
         }
@@ -1361,9 +1399,15 @@ __global__ void __launch_bounds__(WKV_THREADS) wkv5_seq_kernel(SeqWkvArgs a) {
   if (MODE == 0 || a.n_chunks == 1) {
     float *S = MODE == 0 ? a.e_out + ((size_t)h * a.n_chunks + c) * 4096 : Sown;
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
+    for (int p = 0; p < 8; ++p)
 #pragma unroll
-      for (int q = 0; q < 4; ++q) S[(iq * 16 + i) * 64 + jg + 16 * q] = s[q][i];
+      for (int q = 0; q < 4; ++q) {
+        float lo, hi;
+        unpack_f2(s2[q][p], lo, hi);
+        const int ii = iq * 16 + 2 * p;
+        S[ii * 64 + jg + 16 * q] = lo;
+        S[(ii + 1) * 64 + jg + 16 * q] = hi;
+      }
   }
 }
 
@@ -1457,6 +1501,18 @@ cudaError_t launch_ln_mix_seq(const SeqLnArgs &a, cudaStream_t st) {
   else launch_k(ln_mix_seq_kernel<LN_MAX4>, dim3(a.T), dim3(256), 0, st, a);
   return cudaGetLastError();
 }
+// CTAs of the readout pass of the scan that are resident at once on the device: one wave of (head, chunk) pairs is what
+// a prompt should be cut into (a second, partly filled wave costs as much as a full one)
+int wkv5_scan_slots() {
+  static int slots = 0;
+  if (!slots) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, wkv5_seq_kernel<2>, WKV_THREADS, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+    slots = per_sm * device_sm_count();
+  }
+  return slots;
+}
+
 cudaError_t launch_wkv5_seq(const SeqWkvArgs &a, int H, cudaStream_t st) {
   if (a.batch_mode) {
     launch_k(wkv5_seq_kernel<2>, dim3(dim3(H, a.T)), dim3(WKV_THREADS), 0, st, a);   // n_chunks == 1: every stream reads and writes its own state
