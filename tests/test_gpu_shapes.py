@@ -16,7 +16,7 @@ recurrent state within 1e-2 max-abs and 1e-3 relative L2.
       against the oracle's token loop, then 64 decode steps
   c4  RWKV-4 14B-shaped at full width (C5120 F20480 V50277) with 7 of its 40 layers (one halving of the residual
       stream happens), int8: 32 tokens at batch 1
-The measured distances go to gpurun_out/parity_shapes.json beside the assertions.
+The measured distances go to parity_shapes.json in the run's output directory beside the assertions.
 """
 import dataclasses
 import json
