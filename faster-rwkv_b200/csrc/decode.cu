@@ -536,33 +536,110 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
   if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // trace
 }
 
-// LayerNorm + token-shift mix, any number of streams and any width: a statistics pass (which also waits
-// for the data) and a second pass over x.
+// LayerNorm + token-shift mix, any number of streams and any width: a statistics pass (which also waits for the
+// data) and a second pass over x.  Every CTA needs the whole operand of every stream, so the prologue's length is
+// the number of dependent round trips to L2 it makes: each pass asks for the words of all streams and of all its
+// slots (and the second one for the parameters and shift states as well) before it looks at any of them; with up
+// to four streams of a model that fits the slots, x stays in registers between the passes.
+__device__ __forceinline__ uint4 ex_load_raw4(const exch_t *src) {
+  uint4 w;
+  asm volatile("ld.relaxed.gpu.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
+  return w;
+}
+__device__ __forceinline__ bool ex_decode4(const uint4 &w, unsigned tag, float4 &v) {
+  v = make_float4(ex_value(w.x), ex_value(w.y), ex_value(w.z), ex_value(w.w));
+  return ((w.x & 0xffu) | ((w.y & 0xffu) << 8) | ((w.z & 0xffu) << 16) | (w.w << 24)) == tag * 0x01010101u;
+}
+
+// x[b][4 * i4s[j] ..] for every stream b < B and every used slot j, all requested before any is examined; words that
+// have not arrived are asked for again (bounded like every wait)
+template <int SB, int JB>
+__device__ __forceinline__ void batch_x4(Ctx &cx, const exch_t *xsrc, bool layer0, unsigned tag, const int (&i4s)[JB],
+                                         const bool (&use)[JB], float4 (&v)[SB][JB]) {
+  const DecodeParams &p = *cx.p;
+  if (layer0) {   // embedding rows: plain loads, always there
+#pragma unroll
+    for (int b = 0; b < SB; ++b)
+#pragma unroll
+      for (int j = 0; j < JB; ++j)
+        if (b < p.B && use[j]) try_x4(p, xsrc, true, b, i4s[j], tag, v[b][j]);
+    return;
+  }
+  unsigned pending = 0;
+#pragma unroll
+  for (int b = 0; b < SB; ++b)
+#pragma unroll
+    for (int j = 0; j < JB; ++j)
+      if (b < p.B && use[j]) pending |= 1u << (b * JB + j);
+  Poll poll;
+  while (pending) {
+    // the raw words land in v itself and are decoded in place: no second set of registers
+#pragma unroll
+    for (int b = 0; b < SB; ++b)
+#pragma unroll
+      for (int j = 0; j < JB; ++j)
+        if ((pending >> (b * JB + j)) & 1u) {
+          const uint4 w = ex_load_raw4(xsrc + (size_t)b * p.C + (size_t)i4s[j] * 4);
+          v[b][j] = make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w));
+        }
+#pragma unroll
+    for (int b = 0; b < SB; ++b)
+#pragma unroll
+      for (int j = 0; j < JB; ++j)
+        if ((pending >> (b * JB + j)) & 1u) {
+          const uint4 w = make_uint4(__float_as_uint(v[b][j].x), __float_as_uint(v[b][j].y), __float_as_uint(v[b][j].z),
+                                     __float_as_uint(v[b][j].w));
+          float4 t;
+          if (ex_decode4(w, tag, t)) { v[b][j] = t; pending &= ~(1u << (b * JB + j)); }
+        }
+    if (pending && !poll.keep_waiting(cx)) break;
+  }
+}
+
 template <int NB, int NT>
 __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, const exch_t *xsrc, bool layer0, unsigned xtag, const float *ln_w,
                                              const float *ln_b, const float *const *mix, int nvec, const uint8_t *sx_rd,
                                              uint8_t *sx_wr, int sx_item0) {
   constexpr int SB = n_streams<NB, NT>();
+  constexpr int JB = SB > 4 ? 1 : 2;   // slots per thread and round: SB x JB 16-byte loads in flight
   const DecodeParams &p = *cx.p;
   const int n4 = p.C >> 2;
   const float inv = 1.f / (float)p.C;
+  const bool fits = n4 <= JB * NCONS;   // one round covers the vector: x stays in registers
   if (!layer0) wait_sentinels(cx, xsrc, p.C, xtag);
   float s1[SB], s2[SB], piv[SB], mean[SB], rstd[SB];
-#pragma unroll
-  for (int b = 0; b < SB; ++b) {
-    s1[b] = s2[b] = 0.f;
-    piv[b] = b < p.B ? wait_x4(cx, xsrc, layer0, b, 0, xtag).x : 0.f;
-  }
-  for (int i4 = cx.tid; i4 < n4; i4 += NCONS) {
+  float4 xv[SB][JB];
+  {
+    const int i0[JB] = {};
+    bool u0[JB] = {};
+    u0[0] = true;
+    float4 pv[SB][JB];
+    batch_x4<SB, JB>(cx, xsrc, layer0, xtag, i0, u0, pv);
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
-      if (b < p.B) {
-        const float4 v = wait_x4(cx, xsrc, layer0, b, i4, xtag);
-        const float d0 = v.x - piv[b], d1 = v.y - piv[b], d2 = v.z - piv[b], d3 = v.w - piv[b];
-        s1[b] += (d0 + d1) + (d2 + d3);
-        s2[b] += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
-      }
+      s1[b] = s2[b] = 0.f;
+      piv[b] = b < p.B ? pv[b][0].x : 0.f;
     }
+  }
+  for (int base = 0; base < n4; base += JB * NCONS) {
+    int i4s[JB];
+    bool use[JB];
+#pragma unroll
+    for (int j = 0; j < JB; ++j) {
+      i4s[j] = base + j * NCONS + cx.tid;
+      use[j] = i4s[j] < n4;
+    }
+    batch_x4<SB, JB>(cx, xsrc, layer0, xtag, i4s, use, xv);
+#pragma unroll
+    for (int b = 0; b < SB; ++b)
+#pragma unroll
+      for (int j = 0; j < JB; ++j)
+        if (b < p.B && use[j]) {
+          const float4 v = xv[b][j];
+          const float d0 = v.x - piv[b], d1 = v.y - piv[b], d2 = v.z - piv[b], d3 = v.w - piv[b];
+          s1[b] += (d0 + d1) + (d2 + d3);
+          s2[b] += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        }
   }
 #pragma unroll
   for (int b = 0; b < SB; ++b) {
@@ -594,23 +671,39 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, con
     mean[b] = piv[b] + m;
     rstd[b] = rsqrtf(var + 1e-5f);
   }
-  for (int base = 0; base < n4; base += NCONS) {
-    if (base + (cx.tid & ~31) >= n4) break;   // warp-uniform
-    const bool valid = base + cx.tid < n4;
-    const int i4 = valid ? base + cx.tid : cx.lane & 7;
-    float4 mx4[4];
-    const float4 gw = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4);
-    const float4 gb = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4);
+  for (int base = 0; base < n4; base += JB * NCONS) {
+    // every lane of a warp that has any data makes the calls (the operand stores may shuffle); lanes past the end
+    // work on a dummy index and store nothing
+    int i4s[JB];
+    bool use[JB], valid[JB];
 #pragma unroll
-    for (int v = 0; v < 4; ++v)
-      if (v < nvec) mx4[v] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4);
+    for (int j = 0; j < JB; ++j) {
+      const int i4 = base + j * NCONS + cx.tid;
+      use[j] = base + j * NCONS + (cx.tid & ~31) < n4;   // warp-uniform
+      valid[j] = i4 < n4;
+      i4s[j] = valid[j] ? i4 : cx.lane & 7;
+    }
+    if (!fits) batch_x4<SB, JB>(cx, xsrc, layer0, xtag, i4s, use, xv);   // already there: the statistics pass waited
 #pragma unroll
-    for (int b = 0; b < SB; ++b) {
-      if (b >= p.B) break;
-      const float4 xv = wait_x4(cx, xsrc, layer0, b, i4, xtag);  // already there: the statistics pass waited
-      float4 sx = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (nvec > 0) sx = load_act4(sx_rd + (size_t)b * p.state_stride, i4, p.act_fp16);
-      ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4, b, xv, mean[b], rstd[b], gw, gb, mx4, sx, valid);
+    for (int j = 0; j < JB; ++j) {
+      if (!use[j]) continue;
+      // one round trip for this slot's parameters and every stream's shift state
+      float4 mx4[4], sxv[SB];
+      const float4 gw = __ldg(reinterpret_cast<const float4 *>(ln_w) + i4s[j]);
+      const float4 gb = __ldg(reinterpret_cast<const float4 *>(ln_b) + i4s[j]);
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        if (v < nvec) mx4[v] = __ldg(reinterpret_cast<const float4 *>(mix[v]) + i4s[j]);
+#pragma unroll
+      for (int b = 0; b < SB; ++b) {
+        sxv[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < p.B && nvec > 0) sxv[b] = load_act4(sx_rd + (size_t)b * p.state_stride, i4s[j], p.act_fp16);
+      }
+#pragma unroll
+      for (int b = 0; b < SB; ++b) {
+        if (b >= p.B) break;
+        ln_emit<NB, NT>(cx, ph, nvec, sx_wr, sx_item0, i4s[j], b, xv[b][j], mean[b], rstd[b], gw, gb, mx4, sxv[b], valid[j]);
+      }
     }
   }
   bar_sync(BAR_CONS, NCONS);
