@@ -226,6 +226,16 @@ __device__ __forceinline__ bool ex_try4(const exch_t *src, unsigned tag, float4 
   return ((a & 0xffu) | ((b & 0xffu) << 8) | ((c & 0xffu) << 16) | (d << 24)) == tag * 0x01010101u;
 }
 
+__device__ __forceinline__ uint4 ex_load_raw4(const exch_t *src) {
+  uint4 w;
+  asm volatile("ld.relaxed.gpu.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
+  return w;
+}
+__device__ __forceinline__ bool ex_decode4(const uint4 &w, unsigned tag, float4 &v) {
+  v = make_float4(ex_value(w.x), ex_value(w.y), ex_value(w.z), ex_value(w.w));
+  return ((w.x & 0xffu) | ((w.y & 0xffu) << 8) | ((w.z & 0xffu) << 16) | (w.w << 24)) == tag * 0x01010101u;
+}
+
 // Bounded polling: gives up after WAIT_LIMIT_NS (or as soon as another thread of the CTA gave up).
 struct Poll {
   unsigned long long t0;
@@ -263,14 +273,24 @@ __device__ __forceinline__ float4 ex_wait4(Ctx &cx, const exch_t *src, unsigned 
 // still checks every tag.  Keeps 148 CTAs from hammering the whole vector while they wait.
 __device__ __forceinline__ void wait_sentinels(Ctx &cx, const exch_t *src, int K, unsigned tag) {
   const int per = K / ROWS, n = cx.p->B * per;
+  constexpr int SR = 8;   // sentinels asked for together: one round trip, then the tags are looked at
   Poll poll;
   bool ok;
   do {
     ok = true;
-    for (int idx = cx.tid; idx < n; idx += NCONS) {
-      const int b = idx / per, t = idx - b * per;
-      float v;
-      ok = ex_try1(src + (size_t)b * K + (size_t)t * ROWS, tag, v) && ok;
+    for (int base = cx.tid; base < n; base += SR * NCONS) {
+      exch_t w[SR];
+#pragma unroll
+      for (int r = 0; r < SR; ++r) {
+        const int idx = base + r * NCONS;
+        if (idx < n) {
+          const int b = idx / per, t = idx - b * per;
+          w[r] = ex_load_raw(src + (size_t)b * K + (size_t)t * ROWS);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < SR; ++r)
+        if (base + r * NCONS < n) ok = ex_ready(w[r], tag) && ok;
     }
   } while (!ok && poll.keep_waiting(cx));
   bar_sync(BAR_CONS, NCONS);
@@ -541,16 +561,6 @@ __device__ __forceinline__ void prologue_ln_one(Ctx &cx, const PhaseDev &ph, con
 // the number of dependent round trips to L2 it makes: each pass asks for the words of all streams and of all its
 // slots (and the second one for the parameters and shift states as well) before it looks at any of them; with up
 // to four streams of a model that fits the slots, x stays in registers between the passes.
-__device__ __forceinline__ uint4 ex_load_raw4(const exch_t *src) {
-  uint4 w;
-  asm volatile("ld.relaxed.gpu.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
-  return w;
-}
-__device__ __forceinline__ bool ex_decode4(const uint4 &w, unsigned tag, float4 &v) {
-  v = make_float4(ex_value(w.x), ex_value(w.y), ex_value(w.z), ex_value(w.w));
-  return ((w.x & 0xffu) | ((w.y & 0xffu) << 8) | ((w.z & 0xffu) << 16) | (w.w << 24)) == tag * 0x01010101u;
-}
-
 // x[b][4 * i4s[j] ..] for every stream b < B and every used slot j, all requested before any is examined; words that
 // have not arrived are asked for again (bounded like every wait)
 template <int SB, int JB>
@@ -725,7 +735,7 @@ __device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, int pi,
 template <int NB, int NT>
 __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, unsigned tag) {
   constexpr int SB = n_streams<NB, NT>();
-  constexpr int VR = 8;   // slots polled together
+  constexpr int VR = 4;   // slots polled together
   const DecodeParams &p = *cx.p;
   const int n4 = K >> 2;
   const size_t plane = (size_t)K * NB;
@@ -739,12 +749,22 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
     for (int r = 0; r < VR; ++r)
       if (base + r * NCONS < total) pending |= 1u << r;
     do {
+      // all pending slots are requested before any tag is looked at; the raw words land in v and are decoded in place
 #pragma unroll
       for (int r = 0; r < VR; ++r) {
         if (pending & (1u << r)) {
           const int s = base + r * NCONS;
           const int b = s / n4, i4 = s - b * n4;
-          if (ex_try4(src + (size_t)b * K + (size_t)i4 * 4, tag, v[r])) pending &= ~(1u << r);
+          const uint4 w = ex_load_raw4(src + (size_t)b * K + (size_t)i4 * 4);
+          v[r] = make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w));
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < VR; ++r) {
+        if (pending & (1u << r)) {
+          const uint4 w = make_uint4(__float_as_uint(v[r].x), __float_as_uint(v[r].y), __float_as_uint(v[r].z), __float_as_uint(v[r].w));
+          float4 t;
+          if (ex_decode4(w, tag, t)) { v[r] = t; pending &= ~(1u << r); }
         }
       }
     } while (pending && poll.keep_waiting(cx));
