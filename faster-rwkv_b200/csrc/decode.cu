@@ -271,11 +271,21 @@ __device__ __forceinline__ float4 ex_wait4(Ctx &cx, const exch_t *src, unsigned 
 // little of it as possible: writers store 16 consecutive words (one row block) with one warp instruction,
 // so polling the first word of every block tells when the block has landed.  The full read that follows
 // still checks every tag.  Keeps 148 CTAs from hammering the whole vector while they wait.
+template <int SB>
 __device__ __forceinline__ void wait_sentinels(Ctx &cx, const exch_t *src, int K, unsigned tag) {
   const int per = K / ROWS, n = cx.p->B * per;
   constexpr int SR = 8;   // sentinels asked for together: one round trip, then the tags are looked at
   Poll poll;
   bool ok;
+  if constexpr (SB == 1) {   // a few words per thread: the plain sweep is the faster one (measured)
+    do {
+      ok = true;
+      for (int idx = cx.tid; idx < n; idx += NCONS) {
+        float v;
+        ok = ex_try1(src + (size_t)idx * ROWS, tag, v) && ok;
+      }
+    } while (!ok && poll.keep_waiting(cx));
+  } else {
   do {
     ok = true;
     for (int base = cx.tid; base < n; base += SR * NCONS) {
@@ -293,6 +303,7 @@ __device__ __forceinline__ void wait_sentinels(Ctx &cx, const exch_t *src, int K
         if (base + r * NCONS < n) ok = ex_ready(w[r], tag) && ok;
     }
   } while (!ok && poll.keep_waiting(cx));
+  }
   bar_sync(BAR_CONS, NCONS);
 }
 
@@ -616,7 +627,7 @@ __device__ __forceinline__ void prologue_ln_mix(Ctx &cx, const PhaseDev &ph, con
   const int n4 = p.C >> 2;
   const float inv = 1.f / (float)p.C;
   const bool fits = n4 <= JB * NCONS;   // one round covers the vector: x stays in registers
-  if (!layer0) wait_sentinels(cx, xsrc, p.C, xtag);
+  if (!layer0) wait_sentinels<SB>(cx, xsrc, p.C, xtag);
   float s1[SB], s2[SB], piv[SB], mean[SB], rstd[SB];
   float4 xv[SB][JB];
   {
@@ -735,11 +746,11 @@ __device__ __forceinline__ void prologue_ln(Ctx &cx, const PhaseDev &ph, int pi,
 template <int NB, int NT>
 __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, unsigned tag) {
   constexpr int SB = n_streams<NB, NT>();
-  constexpr int VR = 4;   // slots polled together
+  constexpr int VR = SB == 1 ? 8 : 4;   // slots polled together
   const DecodeParams &p = *cx.p;
   const int n4 = K >> 2;
   const size_t plane = (size_t)K * NB;
-  if ((long long)n4 * p.B > (long long)VR * NCONS) wait_sentinels(cx, src, K, tag);
+  if ((long long)n4 * p.B > (long long)VR * NCONS) wait_sentinels<SB>(cx, src, K, tag);
   const int total = n4 * p.B;   // slot index s -> stream s / n4, float4 s % n4
   for (int base = cx.tid; (base & ~31) < total; base += VR * NCONS) {   // warp-uniform: the stores below shuffle
     float4 v[VR];
@@ -748,7 +759,18 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
 #pragma unroll
     for (int r = 0; r < VR; ++r)
       if (base + r * NCONS < total) pending |= 1u << r;
-    do {
+    if constexpr (SB == 1) {   // one stream: the compiler keeps these eight requests in flight together as written (measured)
+      do {
+#pragma unroll
+        for (int r = 0; r < VR; ++r) {
+          if (pending & (1u << r)) {
+            const int s = base + r * NCONS;
+            if (ex_try4(src + (size_t)s * 4, tag, v[r])) pending &= ~(1u << r);
+          }
+        }
+      } while (pending && poll.keep_waiting(cx));
+    } else {
+    while (pending) {
       // all pending slots are requested before any tag is looked at; the raw words land in v and are decoded in place
 #pragma unroll
       for (int r = 0; r < VR; ++r) {
@@ -767,7 +789,9 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
           if (ex_decode4(w, tag, t)) { v[r] = t; pending &= ~(1u << r); }
         }
       }
-    } while (pending && poll.keep_waiting(cx));
+      if (pending && !poll.keep_waiting(cx)) break;
+    }
+    }
     if (p.prof && cx.tid == 0) cx.pc[2] = clock64();  // trace
 #pragma unroll
     for (int r = 0; r < VR; ++r) {
@@ -783,7 +807,6 @@ __device__ __forceinline__ void prologue_vec(Ctx &cx, const exch_t *src, int K, 
   if (p.prof && cx.tid == 0) cx.pc[3] = clock64();  // trace
   bar_sync(BAR_CONS, NCONS);
   if (p.prof && cx.tid == 0) cx.pc[4] = clock64();  // trace
-  (void)SB;
 }
 
 // plain fp32 vector [B][K] (stand-alone matvec) -> operand vector 0
@@ -814,7 +837,7 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const PhaseDev &ph, un
   const DecodeParams &p = *cx.p;
   const size_t plane = (size_t)p.C * NB;
   const int n4 = p.C >> 2;  // 16 float4 per head -> 16 consecutive threads share a head
-  wait_sentinels(cx, p.o5, p.C, otag);
+  wait_sentinels<n_streams<NB, NT>()>(cx, p.o5, p.C, otag);
   for (int base = 0; base < n4; base += NCONS) {
     const int i4 = base + cx.tid;
     const bool ok = i4 < n4;
