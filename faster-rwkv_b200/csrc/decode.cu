@@ -363,23 +363,6 @@ __device__ __forceinline__ void store_operand4(__half *vec, size_t plane_halfs, 
   }
 }
 
-// Residual stream of stream b, elements 4*i4 .. 4*i4+3: the embedding row at layer 0, else the
-// exchange vector x written by phase `tag` (waits for it).
-__device__ __forceinline__ float4 wait_x4(Ctx &cx, const exch_t *xsrc, bool layer0, int b, int i4, unsigned tag) {
-  const DecodeParams &p = *cx.p;
-  if (layer0) {
-    if (p.emb_f32)
-      return __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.emb) + (size_t)token_id(p, b) * p.C) + i4);
-    const __half *row = reinterpret_cast<const __half *>(p.emb) + (size_t)token_id(p, b) * p.C;
-    const uint2 u = __ldg(reinterpret_cast<const uint2 *>(row) + i4);
-    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
-    const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
-    return make_float4(a.x, a.y, c.x, c.y);
-  }
-  return ex_wait4(cx, xsrc + (size_t)b * p.C + (size_t)i4 * 4, tag);
-}
-
-
 // Element 4*i4.. of the residual stream of stream b without waiting: the embedding row at layer 0
 // (always there), else one attempt at the tagged words.
 __device__ __forceinline__ bool try_x4(const DecodeParams &p, const exch_t *xsrc, bool layer0, int b, int i4, unsigned tag, float4 &v) {
