@@ -75,9 +75,8 @@ struct fr_b200_model {
   uint8_t *h_out = nullptr;      // pinned mirror of d_out
   unsigned long long *d_hist = nullptr; size_t hist_n = 0;   // packed arg-max words of decode_greedy, [tokens][batch]
   unsigned long long *d_amax = nullptr;   // packed arg-max words of a single decode, [max_batch]
-  // seq mode (RWKV-5.x with fp16 weights): plain copies of the projection matrices, activation buffers for seq_T tokens
-  __half *d_plain = nullptr;     size_t plain_halfs = 0;   // fp16: W^T; int8: the integer codes as fp16; int4: hi(q * scale)
-  __half *d_plain2 = nullptr;    // int4: lo(q * scale), what fp16 rounding of the dequantised weight lost
+  // GEMM path: row copies of the projection matrices, activation buffers for seq_T rows
+  __half *d_plain = nullptr;     size_t plain_halfs = 0;   // fp16 models: W^T [out, in]
   __half *d_pscale = nullptr;    size_t pscale_halfs = 0;  // int8: per output row scales, per matrix
   // int8 / int4: every projection a second time in its packed interchange form, row-major (one row per output
   // channel): what the few-row GEMM streams for prompts and for decode of more than 8 streams
@@ -451,7 +450,7 @@ void fr_b200_destroy(fr_b200_model *m) {
   cudaSetDevice(m->device);
   free_scratch(m);
   void *ptrs[] = {m->d_weights, m->d_rscale, m->d_vecs, m->d_vecs16, m->d_emb, m->d_state, m->d_x, m->d_xa, m->d_rwkv, m->d_kk, m->d_rr,
-                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_plain2, m->d_pscale, m->d_qcopy, m->d_qscale, m->d_seq, m->d_head_phase, m->d_lnvec};
+                  m->d_v5buf, m->d_out, m->d_layers, m->d_phases, m->d_amax, m->d_plain, m->d_pscale, m->d_qcopy, m->d_qscale, m->d_seq, m->d_head_phase, m->d_lnvec};
   for (void *p : ptrs)
     if (p) cudaFree(p);
   if (m->h_out) cudaFreeHost(m->h_out);

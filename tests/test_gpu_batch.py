@@ -1,6 +1,7 @@
 """GPU parity of decode for more than 8 streams at once (the batched decode the reference lacks): one row per stream
 through the tensor-core GEMM path, every weight format and model version, against the CPU oracle run stream by
-stream.  Models created with max_batch > 8 keep fp16 (dequantised) W^T copies; their prompts use the same path."""
+stream.  fp16 models created for such batches keep W^T copies, quantised models a row-major copy of their packed
+codes (expanded inside the GEMM); their prompts use the same path."""
 import numpy as np
 import pytest
 
