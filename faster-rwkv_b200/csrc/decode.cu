@@ -827,8 +827,19 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const PhaseDev &ph, un
 #pragma unroll
     for (int b = 0; b < SB; ++b) {
       if (b >= p.B) break;
-      float4 v = make_float4(0, 0, 0, 0);
-      if (ok) v = ex_wait4(cx, p.o5 + (size_t)b * p.C + (size_t)i4 * 4, otag);
+      // the readout, the gate and the GroupNorm parameters are requested together; what has not arrived is waited
+      // for afterwards
+      float4 v = make_float4(0, 0, 0, 0), gw = v, gb = v, g = v;
+      if (ok) {
+        const exch_t *op = p.o5 + (size_t)b * p.C + (size_t)i4 * 4, *gp = p.g5 + (size_t)b * p.C + (size_t)i4 * 4;
+        const uint4 ow = ex_load_raw4(op);
+        uint4 gwd = make_uint4(0u, 0u, 0u, 0u);
+        if (p.version >= 51) gwd = ex_load_raw4(gp);
+        gw = __ldg(reinterpret_cast<const float4 *>(ph.aux0) + i4);
+        gb = __ldg(reinterpret_cast<const float4 *>(ph.aux1) + i4);
+        if (!ex_decode4(ow, otag, v)) v = ex_wait4(cx, op, otag);
+        if (p.version >= 51 && !ex_decode4(gwd, gtag, g)) g = ex_wait4(cx, gp, gtag);
+      }
       float s = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -840,14 +851,9 @@ __device__ __forceinline__ void prologue_gn_gate(Ctx &cx, const PhaseDev &ph, un
       const float rstd = rsqrtf(q * (1.f / 64.f) + 1e-5f);
       float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
       if (ok) {
-        const float4 gw = __ldg(reinterpret_cast<const float4 *>(ph.aux0) + i4);
-        const float4 gb = __ldg(reinterpret_cast<const float4 *>(ph.aux1) + i4);
         y = make_float4(d0 * rstd * gw.x + gb.x, d1 * rstd * gw.y + gb.y, d2 * rstd * gw.z + gb.z,
                         d3 * rstd * gw.w + gb.w);
-        if (p.version >= 51) {
-          const float4 g = ex_wait4(cx, p.g5 + (size_t)b * p.C + (size_t)i4 * 4, gtag);
-          y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w;
-        }
+        if (p.version >= 51) { y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w; }
       }
       store_operand4<NB>(cx.sm.xs, plane, (ok ? i4 : cx.lane & 7) * 4, b, y.x, y.y, y.z, y.w, ok);
     }
@@ -1118,9 +1124,16 @@ __device__ __forceinline__ void phase_wkv5(Ctx &cx, const PhaseDev &ph, int pi) 
     float *S = reinterpret_cast<float *>(stb + off_mid(C, p.act_fp16)) + (size_t)h * 4096;
     float4 *sp = reinterpret_cast<float4 *>(S + i * 64 + j0 + jq);
     float4 s = *sp;
-    const float ki = ex_wait1(cx, p.k5 + (size_t)b * C + h * 64 + i, in_tag);
-    const float ri = ex_wait1(cx, p.r5 + (size_t)b * C + h * 64 + i, in_tag);
-    const float4 vj = ex_wait4(cx, p.v5 + (size_t)b * C + h * 64 + j0 + jq, in_tag);
+    // k, r and v are requested together (a wait that checks its answer before the next request goes out costs a
+    // round trip to L2 each); whatever has not arrived is waited for afterwards
+    const exch_t *kp = p.k5 + (size_t)b * C + h * 64 + i, *rp = p.r5 + (size_t)b * C + h * 64 + i;
+    const exch_t *vp = p.v5 + (size_t)b * C + h * 64 + j0 + jq;
+    const exch_t kw = ex_load_raw(kp), rw = ex_load_raw(rp);
+    const uint4 vw = ex_load_raw4(vp);
+    const float ki = ex_ready(kw, in_tag) ? ex_value(kw) : ex_wait1(cx, kp, in_tag);
+    const float ri = ex_ready(rw, in_tag) ? ex_value(rw) : ex_wait1(cx, rp, in_tag);
+    float4 vj;
+    if (!ex_decode4(vw, in_tag, vj)) vj = ex_wait4(cx, vp, in_tag);
     const float u = p.version == 50 ? __ldg(ph.aux0 + h) : __ldg(ph.aux0 + h * 64 + i);
     const float w = p.version == 50 ? __ldg(ph.aux1 + h) : __ldg(ph.aux1 + h * 64 + i);
     const float a0 = ki * vj.x, a1 = ki * vj.y, a2 = ki * vj.z, a3 = ki * vj.w;
